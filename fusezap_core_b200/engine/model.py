@@ -1,0 +1,139 @@
+"""The model: parts built from a `ModelSpec`, bound to loaded tensors. It holds no sizes of its own.
+
+`load_model(path, dtype, device, max_len)` mirrors the reference's entry (fusezap/serve/models/__init__.py:9-13):
+config.json -> registry -> parts -> safetensors by name. The output matrix is the stored one unless the model ties its
+embeddings or the checkpoint has none, then the embedding table (fusezap/serve/models/llama.py:362-367).
+"""
+from __future__ import annotations
+from dataclasses import replace
+from typing import Any
+
+import torch
+
+from ..cache import KVNeed
+from ..config import ModelSpec, describe, read_config_json
+from ..parts import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, build
+from ..weights import ParamSpec, load_weights
+from ..weights.loader import TORCH_DTYPE
+
+
+def build_layers(spec: ModelSpec) -> list[Any]:
+    layers = []
+    for ls in spec.layers:
+        mixer = build(MIXERS, "mixer", ls.mixer)
+        ffn = build(FEED_FORWARDS, "feed-forward", ls.ffn)
+        if ls.block.kind not in BLOCKS:
+            raise NotImplementedError(f"block kind {ls.block.kind!r} is not registered (have {sorted(BLOCKS)})")
+        layers.append(BLOCKS[ls.block.kind](mixer, ffn, lambda ls=ls: build(NORMS, "norm", ls.norm), **ls.block.params))
+    return layers
+
+
+def declared_tensors(spec: ModelSpec, layers: list[Any] | None = None) -> dict[str, ParamSpec]:
+    """Every tensor name the model reads, in a fixed order, with its shape. Optional groups get the layer's prefix."""
+    layers = layers if layers is not None else build_layers(spec)
+    out: dict[str, ParamSpec] = {spec.embed_name: ParamSpec((spec.vocab_size, spec.hidden_size))}
+    for ls, block in zip(spec.layers, layers):
+        for k, p in block.tensors().items():
+            out[ls.prefix + k] = replace(p, group=ls.prefix + p.group) if p.group else p
+    final = build(NORMS, "norm", spec.final_norm)
+    stem = spec.final_norm_name.rsplit(".", 1)[0]
+    for k, p in final.tensors().items():
+        out[f"{stem}.{k}"] = p
+    if spec.lm_head_name:
+        out[spec.lm_head_name] = ParamSpec((spec.vocab_size, spec.hidden_size), group="lm_head", ignore=spec.tie_embeddings)
+    return out
+
+
+def optional_groups_to_write(typed: Any, spec: ModelSpec) -> set[str]:
+    expected = declared_tensors(spec)
+    if hasattr(typed, "random_optional_groups"):
+        return set(typed.random_optional_groups(expected))
+    return set() if spec.tie_embeddings else {"lm_head"}
+
+
+class DecoderModel:
+    def __init__(self, spec: ModelSpec, typed: Any = None):
+        spec.validate()
+        self.spec, self.config = spec, typed
+        self.layers = build_layers(spec)
+        self.final_norm = build(NORMS, "norm", spec.final_norm)
+        self.positions = {name: build(POSITIONS, "position encoding", p) for name, p in spec.positions.items()}
+        for n, e in enumerate(spec.schedule):
+            pn = self.layers[e.layer].mixer.position_name()
+            if pn is not None and pn not in self.positions:
+                raise ValueError(f"layer {e.layer} names position encoding {pn!r}, the model has {sorted(self.positions)}")
+        self.embed: torch.Tensor | None = None
+        self.lm_head: torch.Tensor | None = None
+        self.dtype: str | None = None
+        self.device: torch.device | None = None
+        self.max_len = 0
+
+    # ---- what the cache manager must provide
+    def cache_needs(self) -> dict[int, KVNeed]:
+        needs: dict[int, KVNeed] = {}
+        for e in self.spec.schedule:
+            need = self.layers[e.layer].mixer.cache_need()
+            if need is None:
+                continue
+            if e.cache in needs and needs[e.cache] != need:
+                raise ValueError(f"cache slot {e.cache} is used by layers with different needs: {needs[e.cache]} and {need}")
+            needs[e.cache] = need
+        return needs
+
+    def state_needs(self) -> dict[tuple[int, str], tuple[int, ...]]:
+        return {(n, name): tuple(shape) for n, e in enumerate(self.spec.schedule)
+                for name, shape in self.layers[e.layer].mixer.state_need().items()}
+
+    def expected_tensors(self) -> dict[str, ParamSpec]:
+        return declared_tensors(self.spec, self.layers)
+
+    # ---- tensors in
+    def bind(self, tensors: dict[str, torch.Tensor], ops: Any, dtype: str, device: torch.device, max_len: int) -> "DecoderModel":
+        spec = self.spec
+        self.dtype, self.device, self.max_len = dtype, torch.device(device), max_len
+        self.embed = tensors[spec.embed_name]
+        head = None if spec.tie_embeddings or not spec.lm_head_name else tensors.get(spec.lm_head_name)
+        self.lm_head = head if head is not None else self.embed
+        for ls, block in zip(spec.layers, self.layers):
+            block.bind({k[len(ls.prefix):]: v for k, v in tensors.items() if k.startswith(ls.prefix)}, ops)
+        stem = spec.final_norm_name.rsplit(".", 1)[0] + "."
+        self.final_norm.bind({k[len(stem):]: v for k, v in tensors.items() if k.startswith(stem)}, ops)
+        for p in self.positions.values():
+            p.prepare(max_len, self.device)
+        return self
+
+    def weight_bytes(self) -> int:
+        """Bytes of every distinct tensor a step reads once (the decode roofline's weight term)."""
+        seen: dict[int, int] = {}
+        def add(t):
+            if isinstance(t, torch.Tensor):
+                seen[t.data_ptr()] = t.numel() * t.element_size()
+        for block in self.layers:
+            stack = [block]
+            while stack:
+                o = stack.pop()
+                for v in vars(o).values():
+                    if isinstance(v, torch.Tensor):
+                        add(v)
+                    elif hasattr(v, "bind") and hasattr(v, "tensors"):
+                        stack.append(v)
+        add(self.lm_head)
+        for v in vars(self.final_norm).values():
+            add(v)
+        return sum(seen.values())
+
+
+def load_model(path: str, dtype: str = "bfloat16", device: str | torch.device = "cuda:0", max_len: int | None = None,
+               ops: Any = None) -> DecoderModel:
+    """A model folder (config.json + safetensors) -> a bound model. `ops`: the kernel table; default: the CUDA kernels
+    of `dtype` (building them at the first call), which refuse to run anywhere but on a GPU."""
+    if dtype not in TORCH_DTYPE:
+        raise ValueError(f"dtype {dtype!r} is not one of {sorted(TORCH_DTYPE)}")
+    typed, spec = describe(read_config_json(path))
+    model = DecoderModel(spec, typed)
+    if ops is None:
+        from ..kernels import cuda_ops
+        ops = cuda_ops(dtype, device)
+    tensors = load_weights(path, model.expected_tensors(), device, dtype)
+    model.ops = ops
+    return model.bind(tensors, ops, dtype, torch.device(device), max_len or spec.max_position)
