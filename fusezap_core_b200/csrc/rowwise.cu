@@ -1,0 +1,326 @@
+// Row kernels of the step: embedding gather, residual add + RMSNorm, rotation + paged cache write, SwiGLU, argmax,
+// temperature sampling. One block per token row (or a grid-stride loop for the elementwise one). Every reduction is in
+// 32-bit with an order fixed by the row length and the block size only.
+//
+// What each computes follows the reference's serve kernels (fusezap/serve/cuda.py:161-258 RMSNorm, :284-315 SwiGLU,
+// :317-427 rotation with cache write, :431-479 argmax, :547-575 step inputs); the residual stream is kept in float32
+// here, so the norm rounds once where the reference rounds x + d, y and w*y separately.
+#include "common.cuh"
+#include <math.h>
+
+// ------------------------------------------------------------------------------------------------ embedding
+template <typename T>
+__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tokens, float* __restrict__ x,
+                             int D, int V, int* err) {
+  const int n = blockIdx.x;
+  const int tok = tokens[n];
+  float* xr = x + (size_t)n * D;
+  if (tok < 0 || tok >= V) {
+    if (threadIdx.x == 0) atomicOr(err, FZ_ERR_TOKEN_RANGE);
+    for (int d = threadIdx.x; d < D; d += blockDim.x) xr[d] = 0.f;
+    return;
+  }
+  const T* tr = table + (size_t)tok * D;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) xr[d] = Cvt<T>::to_f(tr[d]);
+}
+
+FZ_API int fz_embed(const void* table, int table_dtype, const int* tokens, float* x, int N, int D, int V, int* err,
+                    cudaStream_t stream) {
+  if (N <= 0) return FZ_OK;
+  if (table_dtype == FZ_F32)
+    embed_kernel<float><<<N, 256, 0, stream>>>((const float*)table, tokens, x, D, V, err);
+  else if (table_dtype == FZ_BF16)
+    embed_kernel<__nv_bfloat16><<<N, 256, 0, stream>>>((const __nv_bfloat16*)table, tokens, x, D, V, err);
+  else
+    return FZ_BAD_DTYPE;
+  FZ_LAUNCH_CHECK();
+  return FZ_OK;
+}
+
+// ------------------------------------------------------------------------------------------------ add + RMSNorm
+// rows == nullptr: x[n] += delta[n] (in place), h[n] = w * x[n] * rsqrt(mean(x[n]^2) + eps), one block per row n.
+// rows != nullptr: block r reads row rows[r] (x + delta, x untouched) and writes h[r]; rows[r] < 0 gives zeros.
+template <typename TW, typename TH>
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, const TW* __restrict__ w,
+                                   TH* __restrict__ h, const int* __restrict__ rows, int n_src, int D, float eps,
+                                   int* err) {
+  __shared__ float scratch[32];
+  const int r = blockIdx.x;
+  int src = r;
+  TH* hr = h + (size_t)r * D;
+  if (rows != nullptr) {
+    src = rows[r];
+    if (src < 0 || src >= n_src) {
+      if (src >= n_src && threadIdx.x == 0) atomicOr(err, FZ_ERR_ROW_RANGE);
+      for (int d = threadIdx.x; d < D; d += blockDim.x) hr[d] = Cvt<TH>::from_f(0.f);
+      return;
+    }
+  }
+  float* xr = x + (size_t)src * D;
+  const float* dr = delta ? delta + (size_t)src * D : nullptr;
+  const bool write_x = rows == nullptr && dr != nullptr;
+  float ss = 0.f;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float v = xr[d];
+    if (dr) v += dr[d];
+    if (write_x) xr[d] = v;
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float scale = 1.0f / sqrtf(ss * (1.0f / (float)D) + eps);
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float v = xr[d];
+    if (dr && !write_x) v += dr[d];
+    hr[d] = Cvt<TH>::from_f(Cvt<TW>::to_f(w[d]) * (v * scale));
+  }
+}
+
+FZ_API int fz_add_rmsnorm(float* x, const float* delta, const void* w, int w_dtype, void* h, int h_dtype,
+                          const int* rows, int n_out, int n_src, int D, float eps, int* err, cudaStream_t stream) {
+  if (n_out <= 0) return FZ_OK;
+#define FZ_NORM(TW, TH) add_rmsnorm_kernel<TW, TH><<<n_out, 256, 0, stream>>>(x, delta, (const TW*)w, (TH*)h, rows, n_src, D, eps, err)
+  if (w_dtype == FZ_F32 && h_dtype == FZ_F32) FZ_NORM(float, float);
+  else if (w_dtype == FZ_F32 && h_dtype == FZ_BF16) FZ_NORM(float, __nv_bfloat16);
+  else if (w_dtype == FZ_BF16 && h_dtype == FZ_BF16) FZ_NORM(__nv_bfloat16, __nv_bfloat16);
+  else if (w_dtype == FZ_BF16 && h_dtype == FZ_F32) FZ_NORM(__nv_bfloat16, float);
+  else return FZ_BAD_DTYPE;
+#undef FZ_NORM
+  FZ_LAUNCH_CHECK();
+  return FZ_OK;
+}
+
+// ------------------------------------------------------------------------------------------------ rotation + cache write
+// qkv: (N, (Hq + 2 Hkv) * hd) float32. One block per row. Pair (j, j + hd/2) of every q and k head is rotated by the
+// angle of the row's position; q goes to q_out, k and v to the row's slot of the paged pool.
+template <typename T>
+__global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const float* __restrict__ cos_t,
+                                     const float* __restrict__ sin_t, const int* __restrict__ pos,
+                                     const int* __restrict__ seq_row, const int* __restrict__ table, int mb,
+                                     T* __restrict__ k_pool, T* __restrict__ v_pool, long long page_stride,
+                                     int page_size, int write, T* __restrict__ q_out, int Hq, int Hkv, int hd,
+                                     int max_len, int* err) {
+  const int n = blockIdx.x;
+  const int half = hd >> 1;
+  const int row = seq_row[n];
+  T* qo = q_out + (size_t)n * Hq * hd;
+  if (row < 0) {
+    for (int i = threadIdx.x; i < Hq * hd; i += blockDim.x) qo[i] = Cvt<T>::from_f(0.f);
+    return;
+  }
+  const int p = pos[n];
+  if (p < 0 || p >= max_len) {
+    if (threadIdx.x == 0) atomicOr(err, FZ_ERR_POS_RANGE);
+    for (int i = threadIdx.x; i < Hq * hd; i += blockDim.x) qo[i] = Cvt<T>::from_f(0.f);
+    return;
+  }
+  const float* in = qkv + (size_t)n * (Hq + 2 * Hkv) * hd;
+  const float* cr = cos_t + (size_t)p * half;
+  const float* sr = sin_t + (size_t)p * half;
+  long long slot_base = -1;
+  if (write) {
+    const int page = table[(size_t)row * mb + p / page_size];
+    if (page < 0) {
+      if (threadIdx.x == 0) atomicOr(err, FZ_ERR_NO_PAGE);
+    } else {
+      slot_base = (long long)page * page_stride + (long long)(p % page_size) * hd;
+    }
+  }
+  const long long head_stride = (long long)page_size * hd;
+  // rotated pairs of the q and k heads
+  for (int i = threadIdx.x; i < (Hq + Hkv) * half; i += blockDim.x) {
+    const int head = i / half, j = i - head * half;
+    const float x1 = in[head * hd + j], x2 = in[head * hd + j + half];
+    const float c = cr[j], s = sr[j];
+    const float o1 = x1 * c - x2 * s;
+    const float o2 = x2 * c + x1 * s;
+    if (head < Hq) {
+      qo[head * hd + j] = Cvt<T>::from_f(o1);
+      qo[head * hd + j + half] = Cvt<T>::from_f(o2);
+    } else if (slot_base >= 0) {
+      T* kd = k_pool + slot_base + (long long)(head - Hq) * head_stride;
+      kd[j] = Cvt<T>::from_f(o1);
+      kd[j + half] = Cvt<T>::from_f(o2);
+    }
+  }
+  if (slot_base >= 0) {
+    const float* vin = in + (Hq + Hkv) * hd;
+    for (int i = threadIdx.x; i < Hkv * hd; i += blockDim.x) {
+      const int head = i / hd, j = i - head * hd;
+      v_pool[slot_base + (long long)head * head_stride + j] = Cvt<T>::from_f(vin[i]);
+    }
+  }
+}
+
+FZ_API int fz_rope_kv_write(const float* qkv, const float* cos_t, const float* sin_t, const int* pos,
+                            const int* seq_row, const int* table, int mb, void* k_pool, void* v_pool,
+                            long long page_stride, int page_size, int write, void* q_out, int dtype, int N, int Hq,
+                            int Hkv, int hd, int max_len, int* err, cudaStream_t stream) {
+  if (N <= 0) return FZ_OK;
+  if (hd % 2 || hd <= 0) return FZ_BAD_SHAPE;
+  if (dtype == FZ_F32)
+    rope_kv_write_kernel<float><<<N, 256, 0, stream>>>(qkv, cos_t, sin_t, pos, seq_row, table, mb, (float*)k_pool,
+                                                       (float*)v_pool, page_stride, page_size, write, (float*)q_out,
+                                                       Hq, Hkv, hd, max_len, err);
+  else if (dtype == FZ_BF16)
+    rope_kv_write_kernel<__nv_bfloat16><<<N, 256, 0, stream>>>(
+        qkv, cos_t, sin_t, pos, seq_row, table, mb, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, page_stride,
+        page_size, write, (__nv_bfloat16*)q_out, Hq, Hkv, hd, max_len, err);
+  else
+    return FZ_BAD_DTYPE;
+  FZ_LAUNCH_CHECK();
+  return FZ_OK;
+}
+
+// ------------------------------------------------------------------------------------------------ SwiGLU
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, long long total, int I) {
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const long long n = idx / I;
+    const int i = (int)(idx - n * I);
+    const float g = Cvt<T>::to_f(gu[n * 2 * I + i]);
+    const float u = Cvt<T>::to_f(gu[n * 2 * I + I + i]);
+    out[idx] = Cvt<T>::from_f(g / (1.0f + expf(-g)) * u);
+  }
+}
+
+FZ_API int fz_swiglu(const void* gu, void* out, int dtype, int N, int I, cudaStream_t stream) {
+  const long long total = (long long)N * I;
+  if (total <= 0) return FZ_OK;
+  const int block = 256;
+  long long blocks = (total + block - 1) / block;
+  if (blocks > 148LL * 32) blocks = 148LL * 32;
+  if (dtype == FZ_F32)
+    swiglu_kernel<float><<<(int)blocks, block, 0, stream>>>((const float*)gu, (float*)out, total, I);
+  else if (dtype == FZ_BF16)
+    swiglu_kernel<__nv_bfloat16><<<(int)blocks, block, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, total, I);
+  else
+    return FZ_BAD_DTYPE;
+  FZ_LAUNCH_CHECK();
+  return FZ_OK;
+}
+
+// ------------------------------------------------------------------------------------------------ argmax / sampling
+// (value, index) order of numpy.argmax: a NaN is the maximum, among equals the lower index wins.
+__device__ __forceinline__ bool better(float v, int i, float bv, int bi) {
+  const bool vn = isnan(v), bn = isnan(bv);
+  if (vn != bn) return vn;
+  if (vn) return i < bi;
+  if (v != bv) return v > bv;
+  return i < bi;
+}
+
+__device__ int block_argmax(const float* __restrict__ row, int V, float* s_val, int* s_idx) {
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float v = row[i];
+    if (bi == 0x7fffffff || better(v, i, bv, bi)) { bv = v; bi = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (oi != 0x7fffffff && (bi == 0x7fffffff || better(ov, oi, bv, bi))) { bv = ov; bi = oi; }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (lane == 0) { s_val[warp] = bv; s_idx[warp] = bi; }
+  __syncthreads();
+  if (warp == 0) {
+    bv = lane < nwarp ? s_val[lane] : -INFINITY;
+    bi = lane < nwarp ? s_idx[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (oi != 0x7fffffff && (bi == 0x7fffffff || better(ov, oi, bv, bi))) { bv = ov; bi = oi; }
+    }
+    if (lane == 0) s_idx[0] = bi;
+  }
+  __syncthreads();
+  const int res = s_idx[0];
+  __syncthreads();
+  return res;
+}
+
+__global__ void argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V) {
+  __shared__ float s_val[32];
+  __shared__ int s_idx[32];
+  const int r = blockIdx.x;
+  const int res = block_argmax(logits + (size_t)r * V, V, s_val, s_idx);
+  if (threadIdx.x == 0) out[r] = res;
+}
+
+FZ_API int fz_argmax(const float* logits, int* out, int R, int V, cudaStream_t stream) {
+  if (R <= 0) return FZ_OK;
+  if (V <= 0) return FZ_BAD_SHAPE;
+  argmax_kernel<<<R, 1024, 0, stream>>>(logits, out, V);
+  FZ_LAUNCH_CHECK();
+  return FZ_OK;
+}
+
+// out[r]: first index whose running sum of exp((l - max) / T) in float64, taken in index order, exceeds u * total.
+// Thread t owns the contiguous range [t * chunk, (t + 1) * chunk), so partial sums are in index order.
+__global__ void sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
+                              const double* __restrict__ uniform, int* __restrict__ out, int V) {
+  __shared__ float s_val[32];
+  __shared__ int s_idx[32];
+  __shared__ double s_sum[1024];
+  __shared__ double s_target;
+  __shared__ int s_res;
+  const int r = blockIdx.x;
+  const float* row = logits + (size_t)r * V;
+  const float T = temperature[r];
+  const int amax = block_argmax(row, V, s_val, s_idx);
+  if (!(T > 0.f)) {
+    if (threadIdx.x == 0) out[r] = amax;
+    return;
+  }
+  const double mx = (double)row[amax] / (double)T;
+  const int chunk = (V + blockDim.x - 1) / blockDim.x;
+  const int lo = min(V, (int)threadIdx.x * chunk), hi = min(V, lo + chunk);
+  double local = 0.0;
+  for (int i = lo; i < hi; ++i) local += exp((double)row[i] / (double)T - mx);
+  s_sum[threadIdx.x] = local;
+  __syncthreads();
+  if (threadIdx.x == 0) {   // exclusive prefix over the threads' ranges, in index order
+    double run = 0.0;
+    for (int t = 0; t < (int)blockDim.x; ++t) {
+      const double v = s_sum[t];
+      s_sum[t] = run;
+      run += v;
+    }
+    s_target = uniform[r] * run;
+    s_res = V - 1;
+  }
+  __syncthreads();
+  const double target = s_target;
+  const double excl = s_sum[threadIdx.x];
+  if (lo < hi && excl <= target && excl + local > target) {
+    double run = excl;
+    int res = hi - 1;
+    for (int i = lo; i < hi; ++i) {
+      run += exp((double)row[i] / (double)T - mx);
+      if (run > target) { res = i; break; }
+    }
+    s_res = res;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) out[r] = s_res;
+}
+
+FZ_API int fz_sample(const float* logits, const float* temperature, const double* uniform, int* out, int R, int V,
+                     cudaStream_t stream) {
+  if (R <= 0) return FZ_OK;
+  if (V <= 0) return FZ_BAD_SHAPE;
+  sample_kernel<<<R, 1024, 0, stream>>>(logits, temperature, uniform, out, V);
+  FZ_LAUNCH_CHECK();
+  return FZ_OK;
+}
+
+// ------------------------------------------------------------------------------------------------ error word
+// The error word is a device int the caller owns; this clears it on a stream.
+FZ_API int fz_clear_error(int* err, cudaStream_t stream) {
+  return (int)cudaMemsetAsync(err, 0, sizeof(int), stream);
+}

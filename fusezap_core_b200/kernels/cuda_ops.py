@@ -1,0 +1,201 @@
+"""`CudaOps`: the kernel table of the product, hand-written sm_100a kernels called through their C entry points.
+
+Every method checks devices, dtypes and layouts on the host and passes raw pointers and the current CUDA stream to the
+library; nothing here computes. A tensor that is not on a CUDA device, a dtype mix the kernels do not take, or a missing
+library raises; there is no CPU or library fallback. Kernels that meet bad data (a token outside the table, a position
+without a page) set a bit in a device error word instead of faulting; `check_errors()` reads and clears it.
+"""
+from __future__ import annotations
+import ctypes
+from ctypes import c_int, c_void_p, c_float, c_longlong
+
+import torch
+
+from .build import load
+from .interface import Ops
+
+F32, BF16 = 0, 1
+_CODE = {torch.float32: F32, torch.bfloat16: BF16}
+_STATUS = {1001: "dtype combination not supported", 1002: "shape not supported", 1003: "misaligned operand",
+           1004: "size too large for the kernel", 1005: "driver entry point not found", 1006: "tensor map encode failed"}
+_DEVICE_ERRORS = {1: "a token id lies outside the embedding table", 2: "a position has no page in its block table",
+                  4: "a position lies outside the position tables", 8: "a bounded wait in a kernel gave up",
+                  16: "a selected row lies outside the step"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _p(t: torch.Tensor | None) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+class CudaOps(Ops):
+    def __init__(self, dtype: str | torch.dtype, device: str | torch.device = "cuda:0"):
+        self.dtype = {"float32": torch.float32, "bfloat16": torch.bfloat16}.get(dtype, dtype)
+        if self.dtype not in _CODE:
+            raise ValueError(f"dtype {dtype!r} is not float32 or bfloat16")
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise KernelError(f"the kernels run on a CUDA device only, not on {self.device}")
+        if not torch.cuda.is_available():
+            raise KernelError("no CUDA device is available; this engine has no CPU path")
+        self.core = load("fzb200_core")
+        self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.launches = 0
+
+    # ---- plumbing
+    def _stream(self) -> c_void_p:
+        return c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def _check(self, status: int, what: str) -> None:
+        self.launches += 1
+        if status != 0:
+            why = _STATUS.get(status, f"CUDA error {status}")
+            raise KernelError(f"{what}: {why}")
+
+    def _want(self, t: torch.Tensor, name: str, dtypes: tuple, dims: int | None = None) -> None:
+        if not t.is_cuda:
+            raise KernelError(f"{name} is on {t.device}; the kernels take CUDA tensors only")
+        if t.dtype not in dtypes:
+            raise KernelError(f"{name} has dtype {t.dtype}, expected one of {dtypes}")
+        if not t.is_contiguous():
+            raise KernelError(f"{name} is not contiguous")
+        if dims is not None and t.dim() != dims:
+            raise KernelError(f"{name} has {t.dim()} dimensions, expected {dims}")
+
+    def check_errors(self) -> None:
+        """Waits for the device, then raises if any kernel since the last check flagged bad data."""
+        word = int(self.err.item())
+        if word:
+            self.err.zero_()
+            raise KernelError("a kernel reported: " + "; ".join(m for b, m in _DEVICE_ERRORS.items() if word & b))
+
+    def check_attention(self, num_heads: int, num_kv_heads: int, head_dim: int) -> None:
+        if head_dim % 16:
+            raise ValueError(f"head_dim {head_dim} is not a multiple of 16; the attention kernels refuse it")
+        if self.core.fz_attn_simt_check(c_int(num_heads), c_int(num_kv_heads), c_int(head_dim)) != 0:
+            raise ValueError(f"attention sizes not supported: {num_heads} heads, {num_kv_heads} kv heads, head_dim "
+                             f"{head_dim} (need heads % kv_heads == 0, heads / kv_heads <= 32, head_dim <= 256)")
+
+    # ---- kernels
+    def embed(self, table, tokens, x) -> None:
+        self._want(table, "embedding table", (torch.float32, torch.bfloat16), 2)
+        self._want(tokens, "tokens", (torch.int32,), 1)
+        self._want(x, "x", (torch.float32,), 2)
+        n, d = x.shape
+        if tokens.shape[0] != n or table.shape[1] != d:
+            raise KernelError(f"embed: tokens {tuple(tokens.shape)}, table {tuple(table.shape)}, x {tuple(x.shape)}")
+        self._check(self.core.fz_embed(_p(table), c_int(_CODE[table.dtype]), _p(tokens), _p(x), c_int(n), c_int(d),
+                                       c_int(table.shape[0]), _p(self.err), self._stream()), "embed")
+
+    def add_rmsnorm(self, x, delta, weight, eps, h, rows=None) -> None:
+        self._want(x, "x", (torch.float32,), 2)
+        self._want(weight, "norm weight", (torch.float32, torch.bfloat16), 1)
+        self._want(h, "h", (torch.float32, torch.bfloat16), 2)
+        if delta is not None:
+            self._want(delta, "delta", (torch.float32,), 2)
+            if delta.shape != x.shape:
+                raise KernelError(f"add_rmsnorm: delta {tuple(delta.shape)} vs x {tuple(x.shape)}")
+        n_src, d = x.shape
+        n_out = n_src
+        if rows is not None:
+            self._want(rows, "rows", (torch.int32,), 1)
+            n_out = rows.shape[0]
+        if h.shape != (n_out, d) or weight.shape[0] != d:
+            raise KernelError(f"add_rmsnorm: h {tuple(h.shape)}, expected {(n_out, d)}; weight {tuple(weight.shape)}")
+        self._check(self.core.fz_add_rmsnorm(_p(x), _p(delta), _p(weight), c_int(_CODE[weight.dtype]), _p(h),
+                                             c_int(_CODE[h.dtype]), _p(rows), c_int(n_out), c_int(n_src), c_int(d),
+                                             c_float(eps), _p(self.err), self._stream()), "add_rmsnorm")
+
+    def linear(self, a, w, bias, out) -> None:
+        self._want(a, "linear input", (self.dtype,), 2)
+        self._want(w, "linear weight", (self.dtype,), 2)
+        self._want(out, "linear output", (torch.float32, self.dtype), 2)
+        if bias is not None:
+            self._want(bias, "linear bias", (torch.float32,), 1)
+        m, k = a.shape
+        n = w.shape[0]
+        if w.shape[1] != k or out.shape != (m, n) or (bias is not None and bias.shape[0] != n):
+            raise KernelError(f"linear: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+        self._gemm(a, w, bias, out, m, n, k)
+
+    def _gemm(self, a, w, bias, out, m, n, k) -> None:
+        self._check(self.core.fz_gemm_simt(_p(a), _p(w), _p(bias), _p(out), c_int(_CODE[a.dtype]),
+                                           c_int(_CODE[out.dtype]), c_int(m), c_int(n), c_int(k), self._stream()),
+                    "linear")
+
+    def _pool(self, cache, hkv: int, hd: int):
+        k, v = cache.keys, cache.values
+        for t, name in ((k, "key pool"), (v, "value pool")):
+            if not t.is_cuda or t.dtype != self.dtype:
+                raise KernelError(f"{name}: device {t.device}, dtype {t.dtype}; expected CUDA {self.dtype}")
+            if t.dim() != 4 or t.shape[1] != hkv or t.shape[3] != hd or t.shape[2] != cache.page_size:
+                raise KernelError(f"{name} has shape {tuple(t.shape)}, expected (pages, {hkv}, {cache.page_size}, {hd})")
+            if t.stride(3) != 1 or t.stride(2) != hd or t.stride(1) != cache.page_size * hd:
+                raise KernelError(f"{name} has strides {t.stride()}: a page's heads must be contiguous")
+        if k.stride(0) != v.stride(0):
+            raise KernelError("key and value pools have different page strides")
+        return k, v, k.stride(0)
+
+    def rope_kv_write(self, qkv, cos, sin, meta, cache, q_out, num_heads, num_kv_heads, head_dim) -> None:
+        self._want(qkv, "qkv", (torch.float32,), 2)
+        self._want(cos, "cos table", (torch.float32,), 2)
+        self._want(sin, "sin table", (torch.float32,), 2)
+        self._want(q_out, "q", (self.dtype,), 2)
+        n = qkv.shape[0]
+        if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim or q_out.shape != (n, num_heads * head_dim) \
+                or cos.shape[1] != head_dim // 2 or sin.shape != cos.shape:
+            raise KernelError(f"rope_kv_write: qkv {tuple(qkv.shape)}, q {tuple(q_out.shape)}, cos {tuple(cos.shape)}")
+        k, v, page_stride = self._pool(cache, num_kv_heads, head_dim)
+        table = meta.table(cache.group)
+        self._check(self.core.fz_rope_kv_write(
+            _p(qkv), _p(cos), _p(sin), _p(meta.pos), _p(meta.seq_row), _p(table), c_int(table.shape[1]), _p(k), _p(v),
+            c_longlong(page_stride), c_int(cache.page_size), c_int(1 if cache.write else 0), _p(q_out),
+            c_int(_CODE[self.dtype]), c_int(n), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
+            c_int(cos.shape[0]), _p(self.err), self._stream()), "rope_kv_write")
+
+    def paged_attention(self, q, cache, meta, out, num_heads, num_kv_heads, head_dim, scale, window) -> None:
+        self._want(q, "q", (self.dtype,), 2)
+        self._want(out, "attention output", (self.dtype,), 2)
+        n = q.shape[0]
+        if q.shape[1] != num_heads * head_dim or out.shape != q.shape:
+            raise KernelError(f"paged_attention: q {tuple(q.shape)}, out {tuple(out.shape)}")
+        k, v, page_stride = self._pool(cache, num_kv_heads, head_dim)
+        table = meta.table(cache.group)
+        self._attention(q, k, v, page_stride, cache, meta, table, out, n, num_heads, num_kv_heads, head_dim, scale, window)
+
+    def _attention(self, q, k, v, page_stride, cache, meta, table, out, n, hq, hkv, hd, scale, window) -> None:
+        self._check(self.core.fz_attn_simt(
+            _p(q), _p(k), _p(v), _p(meta.pos), _p(meta.seq_row), _p(table), c_int(table.shape[1]),
+            c_longlong(page_stride), c_int(cache.page_size), _p(out), c_int(_CODE[self.dtype]), c_int(n), c_int(hq),
+            c_int(hkv), c_int(hd), c_float(scale), c_int(window), _p(self.err), self._stream()), "paged_attention")
+
+    def swiglu(self, gate_up, out) -> None:
+        self._want(gate_up, "gate_up", (self.dtype,), 2)
+        self._want(out, "swiglu output", (self.dtype,), 2)
+        n, i = out.shape
+        if gate_up.shape != (n, 2 * i):
+            raise KernelError(f"swiglu: gate_up {tuple(gate_up.shape)}, out {tuple(out.shape)}")
+        self._check(self.core.fz_swiglu(_p(gate_up), _p(out), c_int(_CODE[self.dtype]), c_int(n), c_int(i),
+                                        self._stream()), "swiglu")
+
+    def argmax(self, logits, out) -> None:
+        self._want(logits, "logits", (torch.float32,), 2)
+        self._want(out, "argmax output", (torch.int32,), 1)
+        r, v = logits.shape
+        if out.shape[0] != r:
+            raise KernelError(f"argmax: logits {tuple(logits.shape)}, out {tuple(out.shape)}")
+        self._check(self.core.fz_argmax(_p(logits), _p(out), c_int(r), c_int(v), self._stream()), "argmax")
+
+    def sample(self, logits, temperature, uniform, out) -> None:
+        self._want(logits, "logits", (torch.float32,), 2)
+        self._want(temperature, "temperature", (torch.float32,), 1)
+        self._want(uniform, "uniform", (torch.float64,), 1)
+        self._want(out, "sample output", (torch.int32,), 1)
+        r, v = logits.shape
+        if out.shape[0] != r or temperature.shape[0] != r or uniform.shape[0] != r:
+            raise KernelError("sample: row counts differ")
+        self._check(self.core.fz_sample(_p(logits), _p(temperature), _p(uniform), _p(out), c_int(r), c_int(v),
+                                        self._stream()), "sample")
