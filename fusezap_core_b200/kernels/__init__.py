@@ -8,7 +8,7 @@ _tables: dict = {}
 def cuda_ops(dtype: str, device="cuda:0"):
     """The kernel table for `dtype` on `device` (built once per pair). Raises if there is no GPU or no compiler."""
     import torch
-    from .cuda_ops import CudaOps
+    from .table import CudaOps
     key = (str(dtype), str(torch.device(device)))
     if key not in _tables:
         _tables[key] = CudaOps(dtype, device)

@@ -112,3 +112,6 @@ class PlainOps:
             c = np.cumsum(e)
             res[r] = int(np.searchsorted(c, float(uniform[r]) * c[-1], side="right").clip(0, len(c) - 1))
         out.copy_(torch.from_numpy(res))
+
+    def check_errors(self) -> None:
+        pass
