@@ -1,0 +1,154 @@
+"""Command line: `python -m fusezap_core_b200 <command>`.
+
+  generate MODEL          run prompts (token ids) through the engine and print each request's new tokens as JSON
+  random-weights          write a model folder (config.json, model.safetensors) from a configuration and a seed
+  build                   compile the CUDA kernels now
+
+Engine options carry the names, meanings and defaults of the reference's `fusezap serve`
+(fusezap/serve/cli.py:8-41): --dtype auto|float32|bfloat16 (auto: bfloat16), --max-model-len 2048, --max-num-seqs 32,
+--max-prefill-tokens, --num-blocks 1024, --block-size 16, --device; sampling options those of its `SamplingParams`
+(fusezap/serve/engine.py:39-50). The reference's text side (tokenizer, HTTP) is not part of this engine: prompts are
+token ids.
+"""
+from __future__ import annotations
+import argparse
+import json
+import os
+import sys
+import time
+
+PRESET_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "config", "presets")
+
+
+def presets() -> list[str]:
+    return sorted(f[:-5] for f in os.listdir(PRESET_DIR) if f.endswith(".json"))
+
+
+def load_preset(name: str) -> dict:
+    path = os.path.join(PRESET_DIR, name + ".json")
+    if not os.path.isfile(path):
+        raise SystemExit(f"unknown preset {name!r} (have {presets()})")
+    with open(path) as f:
+        return json.load(f)
+
+
+def add_engine_options(s: argparse.ArgumentParser) -> None:
+    s.add_argument("--device", default="cuda:0")
+    s.add_argument("--dtype", default="auto", choices=["auto", "float32", "bfloat16"], help="auto (default): bfloat16")
+    s.add_argument("--max-model-len", type=int, default=2048)
+    s.add_argument("--max-num-seqs", type=int, default=32, help="max concurrent requests (decode rows per step)")
+    s.add_argument("--max-prefill-tokens", type=int, default=None, help="prompt tokens per step (default 2048, at most max-model-len)")
+    s.add_argument("--num-blocks", type=int, default=1024, help="cache pages (shared by all requests)")
+    s.add_argument("--block-size", type=int, default=16, help="tokens per page")
+    s.add_argument("--no-cuda-graphs", action="store_true", help="launch decode steps kernel by kernel")
+
+
+def build_parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(prog="fusezap_core_b200", description="B200-native engine for the dense Llama / Qwen2.5 decoder")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    g = sub.add_parser("generate", help="generate tokens for prompts given as token ids")
+    g.add_argument("model", help="model folder (config.json + safetensors)")
+    add_engine_options(g)
+    g.add_argument("--prompt-ids", action="append", default=[], help="comma-separated token ids; repeat for more prompts")
+    g.add_argument("--prompt-file", default=None, help="JSON lines, each a list of token ids")
+    g.add_argument("--prompt-lens", default=None, help="comma-separated lengths of random prompts (with --prompt-seed)")
+    g.add_argument("--prompt-seed", type=int, default=0)
+    g.add_argument("--max-tokens", type=int, default=16)
+    g.add_argument("--temperature", type=float, default=0.0)
+    g.add_argument("--top-k", type=int, default=0)
+    g.add_argument("--top-p", type=float, default=1.0)
+    g.add_argument("--repetition-penalty", type=float, default=1.0)
+    g.add_argument("--seed", type=int, default=None, help="sampling seed; request i uses seed + i")
+    g.add_argument("--stop-token-ids", default="", help="comma-separated")
+    g.add_argument("--ignore-eos", action="store_true")
+    r = sub.add_parser("random-weights", help="write a model folder with seeded random weights")
+    r.add_argument("--preset", default=None, help=f"one of {presets()}")
+    r.add_argument("--config", default=None, help="a config.json to take the sizes from")
+    r.add_argument("--out", required=True)
+    r.add_argument("--seed", type=int, default=0)
+    r.add_argument("--dtype", default="bfloat16", choices=["float32", "bfloat16"])
+    r.add_argument("--norm-noise", action="store_true", help="norm weights 1 + N(0, 0.02) instead of 1")
+    r.add_argument("--num-layers", type=int, default=None, help="override the layer count")
+    sub.add_parser("build", help="compile the CUDA kernels")
+    return ap
+
+
+def resolve_dtype(name: str) -> str:
+    return "bfloat16" if name == "auto" else name
+
+
+def build_engine(a: argparse.Namespace):
+    from .engine.llm_engine import LLMEngine
+    from .engine.model import load_model
+    model = load_model(a.model, resolve_dtype(a.dtype), a.device, max_len=a.max_model_len)
+    return LLMEngine(model, num_blocks=a.num_blocks, block_size=a.block_size, max_num_seqs=a.max_num_seqs,
+                     max_prefill_tokens=a.max_prefill_tokens, max_model_len=a.max_model_len,
+                     cuda_graphs=not a.no_cuda_graphs)
+
+
+def cmd_generate(a: argparse.Namespace) -> int:
+    import numpy as np
+    from .sampling import SamplingParams
+    t0 = time.perf_counter()
+    eng = build_engine(a)
+    print(f"fusezap_core_b200: loaded {a.model} on {a.device} ({resolve_dtype(a.dtype)}) in {time.perf_counter() - t0:.1f}s",
+          file=sys.stderr, flush=True)
+    prompts = [[int(t) for t in p.split(",") if t.strip()] for p in a.prompt_ids]
+    if a.prompt_file:
+        with open(a.prompt_file) as f:
+            prompts += [json.loads(line) for line in f if line.strip()]
+    if a.prompt_lens:
+        rng = np.random.default_rng(a.prompt_seed)
+        V = eng.model.spec.vocab_size
+        prompts += [rng.integers(0, V, int(n)).tolist() for n in a.prompt_lens.split(",")]
+    if not prompts:
+        raise SystemExit("no prompts: give --prompt-ids, --prompt-file or --prompt-lens")
+    stop = [int(t) for t in a.stop_token_ids.split(",") if t.strip()]
+    params = [SamplingParams(max_tokens=a.max_tokens, temperature=a.temperature, top_k=a.top_k, top_p=a.top_p,
+                             repetition_penalty=a.repetition_penalty, seed=None if a.seed is None else a.seed + i,
+                             stop_token_ids=stop, ignore_eos=a.ignore_eos) for i in range(len(prompts))]
+    t0 = time.perf_counter()
+    rids = [eng.add_request(p, q) for p, q in zip(prompts, params)]
+    done = {}
+    while eng.has_unfinished():
+        for out in eng.step():
+            if out.finished:
+                done[out.request_id] = out
+    dt = time.perf_counter() - t0
+    for rid in rids:
+        o = done[rid]
+        print(json.dumps({"request_id": rid, "num_prompt_tokens": o.num_prompt_tokens, "token_ids": o.token_ids,
+                          "finish_reason": o.finish_reason}))
+    n = sum(len(done[r].token_ids) for r in rids)
+    print(f"fusezap_core_b200: {n} tokens in {dt:.2f}s ({n / dt:.1f} tok/s), {eng.stats}", file=sys.stderr, flush=True)
+    return 0
+
+
+def cmd_random_weights(a: argparse.Namespace) -> int:
+    from .weights import write_random_model
+    if bool(a.preset) == bool(a.config):
+        raise SystemExit("give exactly one of --preset and --config")
+    if a.preset:
+        cfg = load_preset(a.preset)
+    else:
+        with open(a.config) as f:
+            cfg = json.load(f)
+    if a.num_layers:
+        cfg["num_hidden_layers"] = a.num_layers
+    write_random_model(cfg, a.out, a.seed, a.dtype, a.norm_noise)
+    print(f"fusezap_core_b200: wrote {a.out} (seed {a.seed}, {a.dtype})", file=sys.stderr)
+    return 0
+
+
+def main(argv: list[str] | None = None) -> int:
+    a = build_parser().parse_args(argv)
+    if a.cmd == "generate":
+        return cmd_generate(a)
+    if a.cmd == "random-weights":
+        return cmd_random_weights(a)
+    if a.cmd == "build":
+        from .kernels.build import build_all
+        for so in build_all():
+            print(so)
+        return 0
+    return 2

@@ -122,10 +122,12 @@ int launch(const void* q, const void* k_pool, const void* v_pool, const int* pos
   const int W = G < MAX_WARPS ? G : MAX_WARPS;
   const size_t smem = sizeof(float) * ((size_t)CHUNK * (hd + 1) + (size_t)CHUNK * hd + (size_t)G * hd);
   auto kern = attn_simt_kernel<T, DPL>;
-  if (smem > 48 * 1024) {
+  static size_t allowed = 48 * 1024;   // per instantiation: the attribute is raised once, outside any capture
+  if (smem > allowed) {
     if (smem > 227 * 1024) return FZ_TOO_LARGE;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
+    allowed = smem;
   }
   dim3 grid(N, Hkv);
   kern<<<grid, 32 * W, smem, stream>>>((const T*)q, (const T*)k_pool, (const T*)v_pool, pos, seq_row, table, mb,

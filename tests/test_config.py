@@ -1,0 +1,107 @@
+"""Configuration: config.json keys -> typed config -> model description; the registry; refusals."""
+import copy
+
+import pytest
+
+from fusezap_core_b200.config import (ARCHITECTURES, DenseDecoderConfig, EngineConfig, ModelSpec, PartSpec, ScheduleEntry,
+                                      describe, register_architecture)
+from tiny_configs import TINY_LLAMA, TINY_QWEN2, TINY_WINDOW
+
+
+def test_keys_and_defaults():
+    c = DenseDecoderConfig.from_hf({"hidden_size": 64, "intermediate_size": 128, "num_hidden_layers": 2,
+                                    "num_attention_heads": 4, "vocab_size": 100})
+    assert (c.model_type, c.num_key_value_heads, c.head_dim, c.rms_norm_eps, c.max_position_embeddings, c.rope_theta) == \
+        ("llama", 4, 16, 1e-6, 4096, 10000.0)
+    assert c.rope_scaling.kind == "default" and not c.tie_word_embeddings and c.layer_windows == ()
+    c = DenseDecoderConfig.from_hf(TINY_LLAMA)
+    assert c.rope_scaling.kind == "llama3" and c.rope_scaling.original_max_position_embeddings == 32
+    assert c.rope_scaling.factor == 8.0 and c.rms_norm_eps == 1e-5
+    c = DenseDecoderConfig.from_hf({**TINY_QWEN2, "eos_token_id": [5, 9], "bos_token_id": 1})
+    assert c.eos_token_ids == (5, 9) and c.bos_token_id == 1 and c.tie_word_embeddings and c.writes_qkv_bias
+    assert DenseDecoderConfig.from_hf({**TINY_QWEN2, "eos_token_id": 7}).eos_token_ids == (7,)
+
+
+def test_rope_parameters_form():
+    c = copy.deepcopy(TINY_LLAMA)
+    rs = c.pop("rope_scaling"); theta = c.pop("rope_theta")
+    c["rope_parameters"] = {"rope_theta": theta, **rs}
+    assert DenseDecoderConfig.from_hf(c) == DenseDecoderConfig.from_hf(TINY_LLAMA)
+    c["rope_parameters"] = {"rope_theta": 5.0, "rope_type": "default"}
+    assert DenseDecoderConfig.from_hf(c).rope_theta == 5.0 and DenseDecoderConfig.from_hf(c).rope_scaling.kind == "default"
+
+
+def test_windows():
+    c = DenseDecoderConfig.from_hf(TINY_WINDOW)
+    assert c.layer_windows == (12, 0, 12)
+    w = copy.deepcopy(TINY_WINDOW); del w["layer_types"]
+    assert DenseDecoderConfig.from_hf(w).layer_windows == (12, 12, 12)
+    w["use_sliding_window"] = False
+    assert DenseDecoderConfig.from_hf(w).layer_windows == ()
+    assert DenseDecoderConfig.from_hf({**TINY_QWEN2, "sliding_window": 4096}).layer_windows == ()   # key alone does nothing
+    spec = c.spec()
+    assert [l.mixer.params["window"] for l in spec.layers] == [12, 0, 12]
+
+
+def test_round_trip_through_config_json():
+    for cfg in (TINY_LLAMA, TINY_QWEN2, TINY_WINDOW):
+        c = DenseDecoderConfig.from_hf(cfg)
+        assert DenseDecoderConfig.from_hf(c.to_hf()) == c
+
+
+@pytest.mark.parametrize("patch,err,match", [
+    ({"num_key_value_heads": 3}, ValueError, "multiple"),
+    ({"head_dim": 15}, ValueError, "even"),
+    ({"hidden_act": "gelu"}, NotImplementedError, "hidden_act"),
+    ({"rope_scaling": {"rope_type": "yarn", "factor": 2}}, NotImplementedError, "yarn"),
+    ({"rope_scaling": {"rope_type": "llama3"}}, ValueError, "factor"),
+    ({"rope_scaling": {"rope_type": "llama3", "factor": 2.0}}, ValueError, "original_max_position"),
+    ({"vocab_size": 0}, ValueError, "vocab_size"),
+    ({"rms_norm_eps": 0.0}, ValueError, "rms_norm_eps"),
+    ({"use_sliding_window": True, "sliding_window": 8, "layer_types": ["full_attention"]}, ValueError, "layer_types"),
+])
+def test_bad_configs(patch, err, match):
+    with pytest.raises(err, match=match):
+        DenseDecoderConfig.from_hf({**TINY_LLAMA, **patch})
+
+
+def test_missing_key_is_named():
+    c = copy.deepcopy(TINY_LLAMA); del c["intermediate_size"]
+    with pytest.raises(ValueError, match="intermediate_size"):
+        DenseDecoderConfig.from_hf(c)
+
+
+def test_registry():
+    typed, spec = describe(TINY_QWEN2)
+    assert isinstance(typed, DenseDecoderConfig) and isinstance(spec, ModelSpec) and spec.tie_embeddings
+    assert len(spec.layers) == 3 and [e.layer for e in spec.schedule] == [0, 1, 2]
+    assert spec.layers[0].mixer.kind == "gqa_attention" and spec.layers[0].ffn.kind == "swiglu"
+    assert spec.layers[1].prefix == "model.layers.1."
+    with pytest.raises(NotImplementedError, match="mamba.*llama.*qwen2"):
+        describe({**TINY_QWEN2, "model_type": "mamba"})
+    assert {"llama", "qwen2"} <= set(ARCHITECTURES)
+    register_architecture("unit_test_arch", lambda c: describe({**c, "model_type": "llama"}))
+    try:
+        assert describe({**TINY_LLAMA, "model_type": "unit_test_arch"})[1].architecture == "llama"
+    finally:
+        del ARCHITECTURES["unit_test_arch"]
+
+
+def test_schedule_validation():
+    _, spec = describe(TINY_LLAMA)
+    import dataclasses
+    ok = dataclasses.replace(spec, schedule=(ScheduleEntry(0, 0), ScheduleEntry(1, 1), ScheduleEntry(0, 2), ScheduleEntry(1, 1, write_cache=False)))
+    ok.validate()
+    for bad, match in (((ScheduleEntry(0, 0), ScheduleEntry(1, 0)), "both write"),
+                       ((ScheduleEntry(0, 0, write_cache=False),), "before any entry wrote"),
+                       ((ScheduleEntry(5, 0),), "names layer 5"), ((), "empty")):
+        with pytest.raises(ValueError, match=match):
+            dataclasses.replace(spec, schedule=bad).validate()
+
+
+def test_engine_config():
+    e = EngineConfig(max_num_seqs=8, max_prefill_tokens=64)
+    assert e.token_budget == 72 and EngineConfig(max_num_batched_tokens=100).token_budget == 100
+    for bad in (dict(dtype="float16"), dict(block_size=0), dict(num_blocks=-1), dict(prefill_first=-1)):
+        with pytest.raises(ValueError):
+            EngineConfig(**bad)
