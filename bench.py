@@ -1,0 +1,266 @@
+"""Benchmark: decode tokens per second of the Llama-3.1-8B-sized model (random bf16 weights) on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 4096] [--layers L] [--impl ours|reference]
+
+A "step" is one decode step of `--batch` requests whose contexts end at `--context` tokens. Prints ONE JSON line:
+  value      decoded tokens per second, timed on the device (CUDA events around K steps: metadata copy + graph replay)
+  e2e        the same through the Python entry point (`LLMEngine.step()`): host token ids in (pinned, copied to the device
+             every step), chosen token ids out (copied back every step)
+  prefill    one 2,048-token prompt in one step: tokens per second, and the step's FLOPs / time / the measured bf16 peak
+  roofline   the decode step's bytes (every weight once + the cache of the live requests) / time, against the measured
+             copy bandwidth
+  points     decode tokens per second at batch 1 and 64
+Peaks come from MEASURED_PEAKS.json beside this file when the driver wrote it, else the fallback figures.
+Weights are N(0, 0.02) drawn on the device, prompts are seeded uniform token ids ("data": "synthetic"); the weights
+(16 GB) are far larger than the L2, so nothing has to be flushed between steps.
+"""
+from __future__ import annotations
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+def peaks() -> dict:
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(p):
+        with open(p) as f:
+            d = json.load(f)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown," \
+        "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self):
+        self.path = os.path.join(tempfile.mkdtemp(), "clocks.csv")
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-f", self.path], stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            with open(self.path) as f:
+                for line in f:
+                    c = [x.strip() for x in line.split(",")]
+                    if len(c) < 8 or not c[0].isdigit():
+                        continue
+                    sm.append(int(c[0])); mx.append(int(c[1]))
+                    for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), c[4:8]):
+                        if v == "Active":
+                            reasons.add(name)
+        except OSError:
+            pass
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def reference_arm(a) -> int:
+    """The unmodified reference through its own public API, if it is installed under baseline/_ref."""
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    why = None
+    if not os.path.isdir(os.path.join(ref, "fusezap")):
+        why = "the reference is not installed under baseline/_ref"
+    else:
+        why = ("the reference has no sm_100 path (its CUDA GEMMs are sm_90a wgmma, which does not build for sm_100a, and its "
+               "decode kernels are NVRTC-compiled at run time for architectures up to sm_90); not run on this pool")
+    print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
+    ap.add_argument("--preset", default="llama-3.1-8b")
+    ap.add_argument("--prefill-tokens", type=int, default=2048)
+    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
+    ap.add_argument("--no-e2e", action="store_true")
+    a = ap.parse_args()
+    if a.impl == "reference":
+        return reference_arm(a)
+    if a.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {a.gpus} is not supported")
+        return 2
+    a.warmup = max(a.warmup, 3)
+
+    import numpy as np
+    import torch
+    from fusezap_core_b200 import LLMEngine, SamplingParams
+    from fusezap_core_b200.cli import load_preset
+    from fusezap_core_b200.engine import Portion
+    from fusezap_core_b200.engine.model import random_model
+
+    cfg = load_preset(a.preset)
+    full_layers = cfg["num_hidden_layers"]
+    if a.layers:
+        cfg["num_hidden_layers"] = a.layers
+    L = cfg["num_hidden_layers"]
+    pk = peaks()
+    dev = torch.device("cuda:0")
+    page = 16
+    t0 = time.time()
+    model = random_model(cfg, "bfloat16", dev, seed=0, max_len=a.context)
+    torch.cuda.synchronize()
+    print(f"bench: model built in {time.time() - t0:.1f}s, {model.weight_bytes() / 1e9:.2f} GB of weights read per step",
+          file=sys.stderr, flush=True)
+    Hkv, hd = cfg["num_key_value_heads"], cfg["head_dim"]
+    kv_bytes_per_token = 2 * Hkv * hd * 2 * L
+    rng = np.random.default_rng(3)
+    V = cfg["vocab_size"]
+
+    def make_engine(batch: int) -> LLMEngine:
+        pages = batch * (-(-a.context // page)) + 8
+        # prefill_first: while prompts are pending the requests that already decode wait, so all of them start
+        # decoding together, at equal contexts
+        return LLMEngine(model, num_blocks=pages, block_size=page, max_num_seqs=batch, max_prefill_tokens=a.prefill_tokens,
+                         max_model_len=a.context, prefill_first=1 << 30)
+
+    def prefill_to(eng: LLMEngine, batch: int, n_prompt: int, max_tokens: int) -> list[int]:
+        """Admits `batch` requests of n_prompt seeded tokens and steps until every one decodes."""
+        rids = [eng.add_request(rng.integers(0, V, n_prompt).tolist(), SamplingParams(max_tokens=max_tokens, ignore_eos=True))
+                for _ in range(batch)]
+        while any(not eng.seqs[r].decoding for r in rids):
+            eng.step()
+        return rids
+
+    def decode_run(batch: int, steps: int, warmup: int, e2e: bool) -> dict:
+        """Times `steps` decode steps of `batch` requests whose contexts end at a.context."""
+        eng = make_engine(batch)
+        total = steps + warmup
+        runs = 2 if e2e else 1
+        n_prompt = a.context - runs * total - 2
+        rids = prefill_to(eng, batch, n_prompt, max_tokens=runs * total + 2)
+        out = {}
+        # device-timed: metadata copy + graph replay per step, tokens fixed beforehand, no read-back inside
+        runner, meta = eng.runner, eng.runner.meta
+        seqs = [eng.seqs[r] for r in rids]
+        bucket = next(b for b in eng._buckets if b >= batch)
+        def one_step(i: int):
+            portions = [Portion(s.seq_id, [s.tokens[s.num_computed]], [0]) for s in seqs]
+            starts = runner.prepare(portions, pad_rows=bucket, pad_wanted=bucket)
+            eng._graphs[bucket].replay()
+            runner.commit(portions, starts)
+            for s, st in zip(seqs, starts):   # the next token is fixed beforehand: nothing is read back in this loop
+                s.num_computed = st + 1
+                s.output.append(int((s.seq_id * 7919 + i) % V))
+        eng.step()                      # builds the graph of this bucket
+        for i in range(warmup - 1):
+            one_step(i)
+        torch.cuda.synchronize()
+        launches0 = model.ops.launches
+        ctx0 = seqs[0].num_computed
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for i in range(steps):
+            one_step(i)
+        end.record()
+        torch.cuda.synchronize()
+        ms = start.elapsed_time(end) / steps
+        ctx_mean = ctx0 + steps / 2
+        out.update(ms=ms, tok_s=batch * 1000.0 / ms, context=ctx_mean,
+                   launches=steps * eng.launches_per_graph.get(bucket, 0) + (model.ops.launches - launches0),
+                   bytes=model.weight_bytes() + batch * ctx_mean * kv_bytes_per_token)
+        if e2e:
+            for _ in range(warmup):
+                eng.step()
+            torch.cuda.synchronize()
+            h0, d0 = eng.stats["h2d_bytes"], eng.stats["d2h_bytes"]
+            t = time.perf_counter()
+            n_tok = 0
+            for _ in range(steps):
+                n_tok += len(eng.step())
+            torch.cuda.synchronize()
+            dt = time.perf_counter() - t
+            out.update(e2e_tok_s=n_tok / dt, e2e_ms=dt * 1000 / steps, h2d=(eng.stats["h2d_bytes"] - h0) // steps,
+                       d2h=(eng.stats["d2h_bytes"] - d0) // steps)
+        for r in rids:
+            eng.abort(r)
+        del eng
+        torch.cuda.empty_cache()
+        return out
+
+    def prefill_run(tokens: int) -> dict:
+        eng = make_engine(1)
+        ids = rng.integers(0, V, tokens).tolist()
+        times = []
+        for i in range(4):
+            rid = eng.add_request(ids, SamplingParams(max_tokens=1, ignore_eos=True))
+            torch.cuda.synchronize()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            eng.step()
+            end.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(end))
+            eng.release(rid)
+        ms = min(times[1:])
+        D, I, Hq = cfg["hidden_size"], cfg["intermediate_size"], cfg["num_attention_heads"]
+        lin = 2 * tokens * L * (D * (Hq + 2 * Hkv) * hd + Hq * hd * D + 3 * D * I) + 2 * D * V
+        attn = 2 * tokens * tokens * hd * Hq * L     # causal: half of 4 T^2 hd Hq
+        flops = lin + attn
+        return {"value": round(tokens * 1000.0 / ms, 1), "tokens": tokens, "ms": round(ms, 3),
+                "frac": round(flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4), "flops": flops}
+
+    clocks = ClockSampler()
+    clocks.start()
+    main_run = decode_run(a.batch, a.steps, a.warmup, e2e=not a.no_e2e)
+    clk = clocks.stop()
+    pre = prefill_run(a.prefill_tokens)
+    points = {}
+    if not a.no_points:
+        for b in (1, 64):
+            points[f"decode_b{b}"] = round(decode_run(b, max(8, a.steps // 2), a.warmup, e2e=False)["tok_s"], 1)
+    achieved = main_run["bytes"] / (main_run["ms"] * 1e-3) / 1e9
+    line = {
+        "metric": "decode_tokens_per_s", "value": round(main_run["tok_s"], 1), "unit": "tok/s", "n_gpus": 1,
+        "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(main_run["ms"], 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+        "config": {"model": a.preset, "layers": L, "layers_full": full_layers, "hidden": cfg["hidden_size"],
+                   "heads": cfg["num_attention_heads"], "kv_heads": Hkv, "head_dim": hd, "intermediate": cfg["intermediate_size"],
+                   "vocab": V, "global_batch": a.batch, "seq_len": a.context, "context_mean": round(main_run["context"], 1),
+                   "page_size": page, "parallelism": "single", "weights": "random N(0,0.02)", "l2": "inputs larger than L2",
+                   "peaks": pk["source"]},
+        "clocks": clk,
+        "e2e": ({"value": round(main_run["e2e_tok_s"], 1), "unit": "tok/s", "ms_per_step": round(main_run["e2e_ms"], 4),
+                 "h2d_bytes_per_step": int(main_run["h2d"]), "d2h_bytes_per_step": int(main_run["d2h"])} if not a.no_e2e else None),
+        "gpu_launches": int(main_run["launches"]),
+        "prefill": {k: pre[k] for k in ("value", "tokens", "ms", "frac")},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

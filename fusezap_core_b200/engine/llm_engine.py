@@ -70,6 +70,7 @@ class LLMEngine:
         self._ids_d = torch.zeros(R, dtype=torch.int32, device=dev)
         self.cuda_graphs = bool(cuda_graphs) and pin
         self._graphs: dict[int, torch.cuda.CUDAGraph] = {}
+        self.launches_per_graph: dict[int, int] = {}     # kernels of this package in one replay of a bucket's graph
         self._buckets = sorted({min(1 << i, R) for i in range(R.bit_length() + 1)})
         self.stats = {"steps": 0, "decode_steps": 0, "prefill_steps": 0, "mixed_steps": 0, "tokens": 0,
                       "preemptions": 0, "graph_replays": 0, "h2d_bytes": 0, "d2h_bytes": 0}
@@ -172,10 +173,13 @@ class LLMEngine:
                 logits = self._eager(n_w)              # warm-up: builds, sets kernel attributes, sizes the buffers
                 torch.cuda.synchronize()
                 g = torch.cuda.CUDAGraph()
+                before = ops.launches
                 with torch.cuda.graph(g):
                     self._eager(n_w)
+                self.launches_per_graph[bucket] = ops.launches - before
                 self._graphs[bucket] = g
             g.replay()
+            ops.launches += self.launches_per_graph[bucket]
             self.stats["graph_replays"] += 1
             logits = runner.ws.get("logits", (n_w, self.model.spec.vocab_size), torch.float32)
         else:

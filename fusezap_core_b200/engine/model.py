@@ -137,3 +137,41 @@ def load_model(path: str, dtype: str = "bfloat16", device: str | torch.device = 
     tensors = load_weights(path, model.expected_tensors(), device, dtype)
     model.ops = ops
     return model.bind(tensors, ops, dtype, torch.device(device), max_len or spec.max_position)
+
+
+def random_model(config: dict, dtype: str = "bfloat16", device: str | torch.device = "cuda:0", seed: int = 0,
+                 max_len: int | None = None, ops: Any = None, norm_noise: bool = False) -> DecoderModel:
+    """A bound model with seeded random weights drawn on the device (no files): matrices and biases N(0, 0.02), norm
+    weights 1 (or 1 + N(0, 0.02)). The same rule as the random-weights writer, from the device's own generator, for
+    models too large to write and read back quickly."""
+    if dtype not in TORCH_DTYPE:
+        raise ValueError(f"dtype {dtype!r} is not one of {sorted(TORCH_DTYPE)}")
+    typed, spec = describe(config)
+    model = DecoderModel(spec, typed)
+    device = torch.device(device)
+    if ops is None:
+        from ..kernels import cuda_ops
+        ops = cuda_ops(dtype, device)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed)
+    compute = TORCH_DTYPE[dtype]
+    groups = optional_groups_to_write(typed, spec)
+    tensors: dict[str, torch.Tensor] = {}
+    for name, p in model.expected_tensors().items():
+        if p.ignore or (p.group is not None and p.group not in groups):
+            continue
+        if p.role == "int_table":
+            tensors[name] = torch.zeros(p.shape, dtype=torch.int32, device=device)
+            continue
+        if p.init == "ones":
+            t = torch.ones(p.shape, dtype=torch.float32, device=device)
+            if norm_noise:
+                t += torch.randn(p.shape, generator=gen, dtype=torch.float32, device=device) * 0.02
+        elif p.init == "zeros":
+            t = torch.zeros(p.shape, dtype=torch.float32, device=device)
+        else:
+            t = torch.empty(p.shape, dtype=compute, device=device)
+            t.normal_(0.0, 0.02, generator=gen)
+        tensors[name] = t.to(torch.float32 if (p.role == "vector" and compute != torch.float32) else compute)
+    model.ops = ops
+    return model.bind(tensors, ops, dtype, device, max_len or spec.max_position)

@@ -1,0 +1,124 @@
+"""The engine on the GPU through the Python entry point and the command line: greedy generation, long decoding, the
+first tokens of a sequence, sampling, CUDA graphs on and off, few pages."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_model
+from util import ROOT, make_model_dir, plain_logits, prompts, read_weights
+
+pytestmark = pytest.mark.gpu
+
+
+def follows_plain_model(cfg, w, dtype, prompt, toks, margin):
+    """Every generated token is the plain model's argmax, or within `margin` of it (a near tie)."""
+    wr = w if dtype == "float32" else {k: v.to(torch.bfloat16) for k, v in w.items()}
+    act = torch.float32 if dtype == "float32" else torch.bfloat16
+    lg = plain_model.forward(cfg, wr, list(prompt) + list(toks), act).numpy()
+    for i, t in enumerate(toks):
+        row = lg[len(prompt) - 1 + i]
+        assert row.max() - row[t] <= margin, f"{dtype}: token {i} = {t} has logit {row[t]:.4f}, the maximum is {row.max():.4f}"
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    return {n: make_model_dir(n, tmp_path_factory.mktemp(n)) for n in ("tiny_llama", "tiny_qwen2", "tiny_window")}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,lens,new,chunk", [("tiny_llama", (5, 11, 17), 8, 64), ("tiny_qwen2", (1, 7, 23, 40), 12, 8),
+                                                 ("tiny_window", (3, 30, 14), 20, 8)])
+def test_greedy_generation(folders, name, lens, new, chunk, dtype):
+    from fusezap_core_b200 import LLMEngine, SamplingParams, load_model
+    d, cfg, opts = folders[name]
+    w = read_weights(d)
+    P = prompts(cfg, lens, seed=1 if name == "tiny_llama" else 2)
+    model = load_model(d, dtype, "cuda:0", max_len=128)
+    margin = 1e-3 if dtype == "float32" else 0.15
+    outs = {}
+    for graphs in (True, False):
+        eng = LLMEngine(model, num_blocks=64, block_size=opts["page_size"], max_num_seqs=4, max_prefill_tokens=chunk,
+                        max_model_len=128, cuda_graphs=graphs)
+        outs[graphs] = eng.generate(P, SamplingParams(max_tokens=new, ignore_eos=True))
+        assert (eng.stats["graph_replays"] > 0) == graphs
+        assert eng.cache.num_free_pages == 64
+    assert outs[True] == outs[False], "replaying captured steps changes no token"
+    for p, t in zip(P, outs[True]):
+        assert len(t) == new
+        follows_plain_model(cfg, w, dtype, p, t, margin)
+    # so few pages that requests lose theirs and are recomputed
+    few = LLMEngine(model, num_blocks=-(-(max(lens) + new) // opts["page_size"]), block_size=opts["page_size"],
+                    max_num_seqs=4, max_prefill_tokens=chunk, max_model_len=128)
+    again = few.generate(P, SamplingParams(max_tokens=new, ignore_eos=True))
+    assert few.stats["preemptions"] > 0
+    if dtype == "float32":
+        assert again == outs[True], "float32: a row's bits do not depend on the batch or the cut, so neither do the tokens"
+    for p, t in zip(P, again):
+        follows_plain_model(cfg, w, dtype, p, t, margin)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_and_first_tokens(folders, dtype):
+    """200 tokens decoded one by one from a one-token prompt: the first tokens of a sequence (positions 0, 1, 2, ...),
+    every page boundary, and a context of hundreds of keys."""
+    from fusezap_core_b200 import LLMEngine, SamplingParams, load_model
+    d, cfg, opts = folders["tiny_qwen2"]
+    w = read_weights(d)
+    model = load_model(d, dtype, "cuda:0", max_len=256)
+    eng = LLMEngine(model, num_blocks=40, block_size=8, max_num_seqs=2, max_model_len=256)
+    toks = eng.generate([[17]], SamplingParams(max_tokens=200, ignore_eos=True))[0]
+    assert len(toks) == 200
+    follows_plain_model(cfg, w, dtype, [17], toks, 1e-3 if dtype == "float32" else 0.15)
+
+
+def test_seeded_sampling_on_the_device(folders):
+    from fusezap_core_b200 import LLMEngine, SamplingParams, load_model
+    d, cfg, opts = folders["tiny_qwen2"]
+    w = read_weights(d)
+    P = prompts(cfg, (1, 7, 23, 40), seed=2)
+    model = load_model(d, "float32", "cuda:0", max_len=128)
+    ps = [SamplingParams(max_tokens=12, temperature=0.8, seed=10 + i, ignore_eos=True) for i in range(4)]
+    ps[2] = SamplingParams(max_tokens=12, temperature=0.8, top_k=20, top_p=0.9, repetition_penalty=1.2, seed=5, ignore_eos=True)
+    mk = lambda: LLMEngine(model, num_blocks=64, block_size=8, max_num_seqs=4, max_prefill_tokens=8, max_model_len=128)
+    together = mk().generate(P, ps)
+    alone = [mk().generate([p], [q])[0] for p, q in zip(P, ps)]
+    assert together == alone, "a request's draws do not depend on the batch"
+    # request 0 (temperature only, picked on the device) against the plain sampler on the plain model's logits
+    rng, ids = np.random.default_rng(10), list(P[0])
+    for t in together[0]:
+        lg = plain_model.forward(cfg, w, ids)[-1].numpy().astype(np.float64) / 0.8
+        e = np.exp(lg - lg.max()); c = np.cumsum(e); u = rng.random() * c[-1]
+        want = int(np.searchsorted(c, u, side="right"))
+        near = abs(c[want] - u) < 1e-4 * c[-1] or (want > 0 and abs(c[want - 1] - u) < 1e-4 * c[-1])
+        assert t == want or near
+        ids.append(t)
+
+
+def test_command_line(folders, tmp_path):
+    d, cfg, opts = folders["tiny_llama"]
+    cmd = [sys.executable, "-m", "fusezap_core_b200", "generate", d, "--dtype", "float32", "--prompt-ids", "5,17,3,200",
+           "--prompt-lens", "9", "--prompt-seed", "4", "--max-tokens", "5", "--ignore-eos", "--max-model-len", "64",
+           "--num-blocks", "32", "--block-size", "4", "--max-num-seqs", "2"]
+    p = subprocess.run(cmd, capture_output=True, text=True, cwd=ROOT, timeout=300)
+    assert p.returncode == 0, p.stderr[-2000:]
+    lines = [json.loads(l) for l in p.stdout.splitlines() if l.startswith("{")]
+    assert len(lines) == 2 and all(len(l["token_ids"]) == 5 and l["finish_reason"] == "length" for l in lines)
+    assert lines[0]["num_prompt_tokens"] == 4 and lines[1]["num_prompt_tokens"] == 9
+    w = read_weights(d)
+    follows_plain_model(cfg, w, "float32", [5, 17, 3, 200], lines[0]["token_ids"], 1e-3)
+    out = str(tmp_path / "rw")
+    p = subprocess.run([sys.executable, "-m", "fusezap_core_b200", "random-weights", "--preset", "tiny-qwen2", "--out", out,
+                        "--seed", "3", "--dtype", "bfloat16"], capture_output=True, text=True, cwd=ROOT, timeout=120)
+    assert p.returncode == 0 and os.path.isfile(os.path.join(out, "model.safetensors")) and os.path.isfile(os.path.join(out, "config.json"))
+
+
+def test_no_gpu_tensor_no_run(folders):
+    from fusezap_core_b200.kernels import cuda_ops
+    from fusezap_core_b200.kernels.table import KernelError
+    with pytest.raises(KernelError, match="CUDA device only"):
+        cuda_ops("float32", "cpu")
