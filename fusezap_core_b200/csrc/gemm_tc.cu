@@ -1,0 +1,464 @@
+// bf16 matrix product on the 5th-generation tensor cores: C[M, N] = X[M, K] . W[N, K]^T (+ bias), float32 accumulation.
+//
+// One kernel serves prompt portions and decoded tokens. Both operands are K-major in global memory, so either can be
+// the 128-row operand of `tcgen05.mma`:
+//   rows mode  (many tokens): the 128 TMEM lanes are token rows, the instruction's N (BN = 64..256) are output features;
+//   swap mode  (few tokens):  the 128 TMEM lanes are output features (rows of W, the operand that has to be streamed
+//                             from HBM once), the instruction's N (BN = 16..128) are the token rows; the tile is stored
+//                             transposed. Nothing is padded to 128 tokens. (The reference's decode GEMM swaps operands the
+//                             same way on sm_90a wgmma: fusezap/device/cuda_kernels/wgmma.py:182-317.)
+// A CTA computes one 128 x BN tile over one range of K:
+//   warp 0  one lane issues the TMA loads (cp.async.bulk.tensor.2d, 128-byte swizzle, 64 k per stage) into a ring of
+//           shared-memory stages guarded by full/empty mbarriers; no multicast;
+//   warp 1  allocates the TMEM accumulator; one lane issues tcgen05.mma (128 x BN x 16, 4 per stage) and commits each
+//           stage's completion to its empty barrier, the last one to the accumulator-ready barrier;
+//   warps 2-5  read the accumulator with tcgen05.ld (each warp its own 32 lanes), add the bias and store.
+// Split K (chosen from N and K only, never from M): every split writes its float32 partial tile to a workspace, the
+// split that arrives last at the tile's counter adds all partials in split order 0, 1, 2, ... and stores the result, so
+// the sum has one fixed order whatever the arrival order (as the reference's split-K does: wgmma.py:209-239). No
+// device-side spin on other CTAs exists; waits on this CTA's own mbarriers are bounded by a time limit after which the
+// kernel sets an error bit and leaves.
+#include "common.cuh"
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+
+namespace {
+
+constexpr int BM = 128;           // TMEM lanes = rows of the 128-row operand
+constexpr int BK = 64;            // k per stage: 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int NUM_THREADS = 192;  // warp 0 TMA, warp 1 MMA, warps 2..5 epilogue
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+
+// ---------------------------------------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Waits for the phase with the given parity; gives up after WAIT_LIMIT_NS and returns false.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  const uint32_t addr = smem_u32(bar);
+  unsigned long long t0 = 0;
+  for (uint32_t spins = 0;; ++spins) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+    if (done) return true;
+    if ((spins & 1023u) == 1023u) {
+      const unsigned long long now = global_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > WAIT_LIMIT_NS) return false;
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// 16 consecutive float32 columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory operand descriptor: K-major tile of rows x 64 bf16 with the 128-byte swizzle; rows are 128 bytes apart,
+// groups of 8 rows 1024 bytes apart. Bits: [0,14) address >> 4, [16,30) leading offset >> 4 (1: unused with a swizzle),
+// [32,46) stride offset >> 4 (1024 >> 4), [46,48) version 1, [61,64) layout 2 = 128-byte swizzle.
+__device__ __forceinline__ uint64_t make_smem_desc(const void* tile) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_u32(tile) & 0x3FFFF) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// Instruction descriptor: D float32 (bits [4,6) = 1), A and B bf16 ([7,10) = 1, [10,13) = 1), both K-major ([15], [16]
+// = 0), N >> 3 at [17,23), M >> 4 at [24,29).
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+struct Params {
+  float* c_f32;            // exactly one of c_f32 / c_bf16 is set
+  __nv_bfloat16* c_bf16;
+  const float* bias;       // over output features, may be null
+  float* partials;         // [tiles][splits][128][BN] float32, used when splits > 1
+  int* counters;           // [tiles], zero before the launch, zero again after it
+  int* err;
+  int rows;                // token rows (M of the product)
+  int feats;               // output features (N of the product)
+  int K;
+  int swap;                // 1: lanes are features, columns are token rows
+  int splits;
+  int stages;
+  int vec_ok;              // rows mode: C rows are 16-byte aligned, so full groups of 16 columns go out as vectors
+};
+
+template <int BN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  // stages of [A: 128 x 64 bf16][B: BN x 64 bf16], 1024-byte aligned for the swizzle
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+  uint64_t* full = (uint64_t*)(smem + (size_t)p.stages * STAGE_BYTES);
+  uint64_t* empty = full + p.stages;
+  uint64_t* acc_ready = empty + p.stages;
+  uint32_t* tmem_slot = (uint32_t*)(acc_ready + 1);
+  int* flag = (int*)(tmem_slot + 1);     // [0]: this CTA arrived last at its tile  [1]: a wait gave up
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile_a = blockIdx.x, tile_b = blockIdx.y, split = blockIdx.z;
+  const int kblocks = (p.K + BK - 1) / BK;
+  const int kb0 = (int)((long long)kblocks * split / p.splits), kb1 = (int)((long long)kblocks * (split + 1) / p.splits);
+  const int nkb = kb1 - kb0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    mbar_init(acc_ready, 1);
+    flag[0] = 0; flag[1] = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_d = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % p.stages, round = i / p.stages;
+        if (round > 0 && !mbar_wait(&empty[s], (round - 1) & 1)) { flag[1] = 1; break; }
+        uint8_t* sa = smem + (size_t)s * STAGE_BYTES;
+        mbar_expect_tx(&full[s], STAGE_BYTES);
+        tma_load_2d(sa, &map_a, &full[s], (kb0 + i) * BK, tile_a * BM);
+        tma_load_2d(sa + A_BYTES, &map_b, &full[s], (kb0 + i) * BK, tile_b * BN);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(BM, BN);
+      bool ok = true;
+      for (int i = 0; i < nkb && ok; ++i) {
+        const int s = i % p.stages, round = i / p.stages;
+        if (!mbar_wait(&full[s], round & 1)) { flag[1] = 1; ok = false; break; }
+        tc_fence_after();
+        const uint8_t* sa = smem + (size_t)s * STAGE_BYTES;
+        const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + A_BYTES);
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k)   // 32 bytes further along the swizzled row per 16 k
+          umma_bf16(tmem_d, da + (uint64_t)(k * UMMA_K * 2 / 16), db + (uint64_t)(k * UMMA_K * 2 / 16), idesc,
+                    (i > 0 || k > 0) ? 1u : 0u);
+        umma_commit(&empty[s]);
+      }
+      umma_commit(acc_ready);   // arrives when every MMA issued so far has finished (at once if none was issued)
+    }
+  } else {
+    // ---- epilogue: 4 warps, warp w reads TMEM lanes 32 * (w % 4) ..
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;          // TMEM lane = row of the 128-row operand
+    const bool ok = __all_sync(0xffffffffu, mbar_wait(acc_ready, 0));   // warp-uniform: tcgen05.ld is warp-wide
+    if (!ok) flag[1] = 1;
+    tc_fence_after();
+    const int a_row = tile_a * BM + r;       // rows mode: token row; swap mode: output feature
+    const int a_limit = p.swap ? p.feats : p.rows;
+    const int b_limit = p.swap ? p.rows : p.feats;
+    const int b0 = tile_b * BN;
+    const uint32_t taddr = tmem_d + ((uint32_t)(quad * 32) << 16);
+    const int tile_id = tile_b * gridDim.x + tile_a;
+    const bool direct = p.splits == 1;
+    float* part = p.partials ? p.partials + ((size_t)tile_id * p.splits + split) * BM * BN + (size_t)r * BN : nullptr;
+    float v[16];
+    auto store16 = [&](const float* x, int c) {   // columns c..c+15 of this thread's row, final values
+      if (a_row >= a_limit) return;
+      if (p.swap) {
+        const float bv = p.bias ? p.bias[a_row] : 0.f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int m = b0 + c + j;
+          if (m < b_limit) {
+            const float y = x[j] + bv;
+            if (p.c_f32) p.c_f32[(size_t)m * p.feats + a_row] = y;
+            else p.c_bf16[(size_t)m * p.feats + a_row] = __float2bfloat16_rn(y);
+          }
+        }
+      } else if (p.vec_ok && b0 + c + 16 <= b_limit) {
+        const int n = b0 + c;
+        float y[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) y[j] = x[j] + (p.bias ? p.bias[n + j] : 0.f);
+        if (p.c_f32) {
+          float4* dst = (float4*)(p.c_f32 + (size_t)a_row * p.feats + n);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) dst[j] = make_float4(y[4 * j], y[4 * j + 1], y[4 * j + 2], y[4 * j + 3]);
+        } else {
+          uint32_t w[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const __nv_bfloat162 h = __floats2bfloat162_rn(y[2 * j], y[2 * j + 1]);
+            w[j] = *(const uint32_t*)&h;
+          }
+          uint4* dst = (uint4*)(p.c_bf16 + (size_t)a_row * p.feats + n);
+          dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+          dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int n = b0 + c + j;
+          if (n < b_limit) {
+            const float y = x[j] + (p.bias ? p.bias[n] : 0.f);
+            if (p.c_f32) p.c_f32[(size_t)a_row * p.feats + n] = y;
+            else p.c_bf16[(size_t)a_row * p.feats + n] = __float2bfloat16_rn(y);
+          }
+        }
+      }
+    };
+    if (ok) {
+      for (int c = 0; c < BN; c += 16) {
+        if (nkb > 0) tmem_ld16(taddr + (uint32_t)c, v);
+        else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = 0.f;
+        }
+        if (direct) store16(v, c);
+        else {
+#pragma unroll
+          for (int j = 0; j < 16; j += 4) *(float4*)(part + c + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        }
+      }
+    }
+    if (!direct) {
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (r == 0) {
+        const int old = atomicAdd(&p.counters[tile_id], 1);
+        flag[0] = (old == p.splits - 1) ? 1 : 0;
+        if (old == p.splits - 1) p.counters[tile_id] = 0;   // ready for the next launch
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (flag[0]) {
+        __threadfence();
+        const float* base = p.partials + (size_t)tile_id * p.splits * BM * BN + (size_t)r * BN;
+        for (int c = 0; c < BN; c += 16) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = 0.f;
+          for (int s = 0; s < p.splits; ++s) {      // fixed order: split 0, 1, 2, ...
+            const float* ps = base + (size_t)s * BM * BN + c;
+#pragma unroll
+            for (int j = 0; j < 16; j += 4) {
+              const float4 t = __ldcg((const float4*)(ps + j));
+              v[j] += t.x; v[j + 1] += t.y; v[j + 2] += t.z; v[j + 3] += t.w;
+            }
+          }
+          store16(v, c);
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_d, TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && flag[1]) atomicOr(p.err, FZ_ERR_WAIT_TIMEOUT);
+}
+
+// ---------------------------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_fn() {
+  static EncodeTiled fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiled)p;
+  });
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr; int rows, K, box_rows;
+  bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && K == o.K && box_rows == o.box_rows; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    return std::hash<const void*>()(k.ptr) ^ ((size_t)k.rows * 1000003u) ^ ((size_t)k.K * 10007u) ^ ((size_t)k.box_rows << 20);
+  }
+};
+
+// A 2-D map over a row-major [rows, K] bf16 matrix with boxes of box_rows x 64 elements and the 128-byte swizzle.
+// Out-of-range rows and k read as zero. Maps are cached by (pointer, shape, box): weights are encoded once.
+int get_map(const void* ptr, int rows, int K, int box_rows, CUtensorMap* out) {
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
+  const MapKey key{ptr, rows, K, box_rows};
+  auto it = cache.find(key);
+  if (it != cache.end()) { *out = it->second; return FZ_OK; }
+  EncodeTiled enc = encode_fn();
+  if (!enc) return FZ_NO_DRIVER_ENTRY;
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  CUtensorMap m;
+  const CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return FZ_TMAP_ENCODE;
+  if (cache.size() > 4096) cache.clear();
+  cache[key] = m;
+  *out = m;
+  return FZ_OK;
+}
+
+template <int BN>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, dim3 grid, cudaStream_t stream) {
+  constexpr int STAGE_BYTES = (BM + BN) * BK * 2;
+  const size_t smem = (size_t)p.stages * STAGE_BYTES + 1024 + 8 * (2 * p.stages + 1) + 16;
+  static size_t allowed = 48 * 1024;
+  if (smem > allowed) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    allowed = smem;
+  }
+  gemm_tc_kernel<BN><<<grid, NUM_THREADS, smem, stream>>>(ma, mb, p);
+  FZ_LAUNCH_CHECK();
+  return FZ_OK;
+}
+
+int pick_stages(int bn) {
+  const int stage = (BM + bn) * BK * 2;
+  int s = (200 * 1024) / stage;
+  if (bn <= 64) s = (100 * 1024) / stage;   // leaves room for two CTAs per SM when the tile is small
+  return s < 2 ? 2 : (s > 8 ? 8 : s);
+}
+}  // namespace
+
+// Can this kernel take the product? K a multiple of 8 (16-byte rows for TMA), operands 16-byte aligned.
+FZ_API int fz_gemm_tc_check(const void* x, const void* w, int M, int N, int K) {
+  if (M <= 0 || N <= 0 || K <= 0) return FZ_BAD_SHAPE;
+  if (K % 8) return FZ_BAD_SHAPE;
+  if (((uintptr_t)x | (uintptr_t)w) & 15) return FZ_BAD_ALIGNMENT;
+  return FZ_OK;
+}
+
+// The number of K splits for a product with these N and K in swap mode: from N and K only, so that a token row's sum
+// order never depends on how many rows share the step.
+FZ_API int fz_gemm_tc_splits(int N, int K) {
+  const int tiles = (N + BM - 1) / BM, kblocks = (K + BK - 1) / BK;
+  int s = 296 / tiles;               // two CTAs on each of the 148 SMs
+  if (s > kblocks / 4) s = kblocks / 4;
+  if (s > 16) s = 16;
+  return s < 1 ? 1 : s;
+}
+
+// Workspace needs of fz_gemm_tc for a product: bytes of float32 partials and number of int32 counters.
+FZ_API long long fz_gemm_tc_workspace(int M, int N, int K, long long* counters) {
+  const int tiles = (N + BM - 1) / BM;
+  const int splits = fz_gemm_tc_splits(N, K);
+  *counters = tiles;
+  return splits > 1 ? (long long)tiles * splits * BM * 128 * 4 : 0;
+}
+
+// x: [M, K] bf16, w: [N, K] bf16, bias: [N] float32 or null, c: [M, N] float32 (out_dtype 0) or bf16 (1).
+// partials / counters: workspace for split K (counters zeroed once at allocation); may be null, then K is not split.
+FZ_API int fz_gemm_tc(const void* x, const void* w, const float* bias, void* c, int out_dtype, int M, int N, int K,
+                      float* partials, long long partial_bytes, int* counters, int n_counters, int* err,
+                      cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return FZ_OK;
+  int st = fz_gemm_tc_check(x, w, M, N, K);
+  if (st != FZ_OK) return st;
+  if (out_dtype != FZ_F32 && out_dtype != FZ_BF16) return FZ_BAD_DTYPE;
+  Params p{};
+  p.c_f32 = out_dtype == FZ_F32 ? (float*)c : nullptr;
+  p.c_bf16 = out_dtype == FZ_BF16 ? (__nv_bfloat16*)c : nullptr;
+  p.bias = bias; p.err = err; p.rows = M; p.feats = N; p.K = K;
+  p.partials = nullptr; p.counters = nullptr; p.splits = 1;
+  p.vec_ok = (N % 8 == 0 && ((uintptr_t)c & 15) == 0) ? 1 : 0;
+  CUtensorMap ma, mb;
+  if (M <= 128) {
+    // swap mode: W rows are the 128 lanes, the token rows are the instruction's N
+    const int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
+    p.swap = 1;
+    p.stages = pick_stages(bn);
+    const int tiles = (N + BM - 1) / BM;
+    int splits = fz_gemm_tc_splits(N, K);
+    if (splits > 1 && partials && counters && n_counters >= tiles &&
+        partial_bytes >= (long long)tiles * splits * BM * bn * 4) {
+      p.splits = splits; p.partials = partials; p.counters = counters;
+    }
+    if ((st = get_map(w, N, K, BM, &ma)) != FZ_OK) return st;
+    if ((st = get_map(x, M, K, bn, &mb)) != FZ_OK) return st;
+    dim3 grid(tiles, 1, p.splits);
+    switch (bn) {
+      case 16: return launch<16>(ma, mb, p, grid, stream);
+      case 32: return launch<32>(ma, mb, p, grid, stream);
+      case 64: return launch<64>(ma, mb, p, grid, stream);
+      default: return launch<128>(ma, mb, p, grid, stream);
+    }
+  }
+  // rows mode: token rows are the 128 lanes
+  p.swap = 0;
+  const int bn = N >= 256 ? 256 : N >= 128 ? 128 : 64;
+  p.stages = pick_stages(bn);
+  if ((st = get_map(x, M, K, BM, &ma)) != FZ_OK) return st;
+  if ((st = get_map(w, N, K, bn, &mb)) != FZ_OK) return st;
+  dim3 grid((M + BM - 1) / BM, (N + bn - 1) / bn, 1);
+  if (grid.y > 65535) return FZ_TOO_LARGE;
+  switch (bn) {
+    case 256: return launch<256>(ma, mb, p, grid, stream);
+    case 128: return launch<128>(ma, mb, p, grid, stream);
+    default: return launch<64>(ma, mb, p, grid, stream);
+  }
+}

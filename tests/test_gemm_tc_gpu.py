@@ -1,0 +1,83 @@
+"""The tcgen05 / TMA matrix product alone, against a plain float32 product of the same bfloat16 operands: few rows
+(swapped operands, with and without split K), many rows, ragged edges in every dimension, bias, both output dtypes."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def run(M, N, K, out_dtype, bias, seed=0):
+    from fusezap_core_b200.kernels import cuda_ops
+    ops = cuda_ops("bfloat16")
+    assert ops.use_tensor_cores
+    g = torch.Generator().manual_seed(seed + M + 3 * N + 7 * K)
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    w = torch.randn(N, K, generator=g).to(torch.bfloat16).cuda()
+    b = torch.randn(N, generator=g).cuda() if bias else None
+    out = torch.full((M, N), float("nan"), dtype=out_dtype, device="cuda")
+    before = ops.launches
+    ops.linear(a, w, b, out)
+    ops.check_errors()
+    assert ops.launches == before + 1
+    ref = a.double() @ w.double().T
+    if b is not None:
+        ref = ref + b.double()
+    return out, ref
+
+
+def check(out, ref, K):
+    out, ref = out.double().cpu(), ref.cpu()
+    assert torch.isfinite(out).all(), "unwritten or non-finite outputs"
+    scale = float(ref.abs().max())
+    tol = 2e-5 * scale if out.dtype == torch.float64 and False else None
+    err = float((out - ref).abs().max())
+    return err, scale
+
+
+@pytest.mark.parametrize("M", [1, 8, 16, 17, 33, 64, 100, 128])
+@pytest.mark.parametrize("N,K", [(1000, 4096), (512, 4096), (128, 64), (48, 80), (6144, 512), (384, 96)])
+def test_few_rows(M, N, K):
+    for out_dtype, bias in ((torch.float32, False), (torch.bfloat16, True)):
+        out, ref = run(M, N, K, out_dtype, bias)
+        err, scale = check(out, ref, K)
+        lim = 1e-4 * scale if out_dtype == torch.float32 else 2.0 ** -8 * scale
+        assert err <= lim, f"M={M} N={N} K={K} {out_dtype}: max |diff| {err:.3e} > {lim:.3e}"
+
+
+@pytest.mark.parametrize("M,N,K", [(129, 256, 128), (300, 777, 200), (2048, 1024, 512), (257, 64, 4096), (1000, 136, 72),
+                                   (384, 96, 96)])
+def test_many_rows(M, N, K):
+    for out_dtype, bias in ((torch.float32, True), (torch.bfloat16, False)):
+        out, ref = run(M, N, K, out_dtype, bias)
+        err, scale = check(out, ref, K)
+        lim = 1e-4 * scale if out_dtype == torch.float32 else 2.0 ** -8 * scale
+        assert err <= lim, f"M={M} N={N} K={K} {out_dtype}: max |diff| {err:.3e} > {lim:.3e}"
+
+
+def test_a_row_does_not_depend_on_the_other_rows():
+    """Few rows: the same row gives the same bits alone and among 8, 16 or 64 rows (the split of K depends on N and K
+    only, and the sum over the splits has one order)."""
+    from fusezap_core_b200.kernels import cuda_ops
+    ops = cuda_ops("bfloat16")
+    g = torch.Generator().manual_seed(5)
+    a = torch.randn(64, 2048, generator=g).to(torch.bfloat16).cuda()
+    w = torch.randn(640, 2048, generator=g).to(torch.bfloat16).cuda()
+    full = torch.empty(64, 640, device="cuda"); ops.linear(a, w, None, full)
+    for rows in (1, 8, 16, 40):
+        part = torch.empty(rows, 640, device="cuda")
+        ops.linear(a[:rows].contiguous(), w, None, part)
+        assert torch.equal(part, full[:rows]), f"{rows} rows"
+    again = torch.empty(64, 640, device="cuda"); ops.linear(a, w, None, again)
+    assert torch.equal(again, full), "split-K sums are deterministic"
+    ops.check_errors()
+
+
+def test_refused_shapes_fall_back_to_the_plain_kernel():
+    from fusezap_core_b200.kernels import cuda_ops
+    ops = cuda_ops("bfloat16")
+    g = torch.Generator().manual_seed(6)
+    a = torch.randn(5, 36, generator=g).to(torch.bfloat16).cuda()      # K = 36 is no multiple of 8
+    w = torch.randn(20, 36, generator=g).to(torch.bfloat16).cuda()
+    out = torch.empty(5, 20, device="cuda")
+    ops.linear(a, w, None, out)
+    assert float((out.double() - a.double() @ w.double().T).abs().max()) < 1e-3
