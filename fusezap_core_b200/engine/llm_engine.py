@@ -160,6 +160,9 @@ class LLMEngine:
         bucket = next((b for b in self._buckets if b >= len(portions)), None) if decode_only and self.cuda_graphs else None
         pad = bucket or 0
         starts = runner.prepare(portions, pad_rows=pad, pad_wanted=pad)
+        if bucket is not None:
+            # a captured step must cover every context it may be replayed with (its launch sizes are fixed)
+            runner.meta.max_context = self.max_model_len
         n_w = runner.meta.n_wanted
         if n_w:
             self._temp_h[R:n_w] = 0.0

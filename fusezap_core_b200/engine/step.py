@@ -23,6 +23,10 @@ from ..parts import LayerCache
 from .model import DecoderModel
 
 
+LONG_PORTION = 8    # portions of at least this many tokens go to the tile (prefill) attention kernel
+TILE_ROWS = 64      # token rows per tile of that kernel
+
+
 @dataclass
 class Portion:
     """One request's next tokens in a step; `want`: places among these tokens whose logits are asked for."""
@@ -74,6 +78,8 @@ class StepMeta:
         self.o_sel, o = o, o + max_wanted
         self.o_seg, o = o, o + 4 * max_segments
         self.o_tab, o = o, o + num_groups * max_segments * pages_per_request
+        self.max_tiles = max_rows // TILE_ROWS + max_segments
+        self.o_tiles, o = o, o + 2 * self.max_tiles
         self.size = o
         # a ring of pinned host blocks: a block is rewritten only after the copy that read it has finished
         pin = device.type == "cuda"
@@ -89,6 +95,8 @@ class StepMeta:
         self.segments: list[Segment] = []
         self.max_context = 0      # the longest context (position + 1) among the step's rows
         self.max_portion = 0      # the longest portion
+        self.n_tiles = 0          # 64-row tiles of the long portions (tile kernels); the other rows are "short"
+        self.n_short_rows = 0     # rows of short portions, padding rows included
 
     # device views (static addresses; sliced to the step's sizes)
     @property
@@ -101,6 +109,8 @@ class StepMeta:
     def sel(self) -> torch.Tensor: return self.dev[self.o_sel: self.o_sel + self.n_wanted]
     @property
     def seg(self) -> torch.Tensor: return self.dev[self.o_seg: self.o_seg + 4 * self.max_segments].view(self.max_segments, 4)
+    @property
+    def tiles(self) -> torch.Tensor: return self.dev[self.o_tiles: self.o_tiles + 2 * self.max_tiles].view(self.max_tiles, 2)
     def table(self, group: int) -> torch.Tensor:
         n = self.max_segments * self.mb
         return self.dev[self.o_tab + group * n: self.o_tab + (group + 1) * n].view(self.max_segments, self.mb)
@@ -151,6 +161,16 @@ class StepMeta:
             for s, p in enumerate(portions):
                 pages = cache.table(g, p.req)
                 t[s, :len(pages)] = pages
+        # 64-row tiles of the portions with at least LONG_PORTION tokens, the ones that see the most keys first
+        tl = [(sg.pos0 + min(r + TILE_ROWS, sg.n), sg.seq_row, r) for sg in self.segments if sg.n >= LONG_PORTION
+              for r in range(0, sg.n, TILE_ROWS)]
+        tl.sort(key=lambda x: -x[0])
+        tiles = a[self.o_tiles: self.o_tiles + 2 * self.max_tiles].reshape(self.max_tiles, 2)
+        tiles[len(tl):] = -1
+        for i, (_, s, r) in enumerate(tl):
+            tiles[i] = (s, r)
+        self.n_tiles = len(tl)
+        self.n_short_rows = n_rows - sum(sg.n for sg in self.segments if sg.n >= LONG_PORTION)
         self.n_rows, self.n_wanted, self.n_segments = n_rows, n_wanted, len(portions)
         self.dev.copy_(self.host, non_blocking=True)
         if self._events[self._turn] is not None:

@@ -53,6 +53,7 @@ class CudaOps(Ops):
             self._partials = torch.empty(296 * 128 * 128, dtype=torch.float32, device=self.device)
             self._counters = torch.zeros(4096, dtype=torch.int32, device=self.device)
         self.use_tensor_cores = self.tc is not None
+        self._attn_scratch: torch.Tensor | None = None      # float32 partial outputs of the split decode attention
 
     # ---- plumbing
     def _stream(self) -> c_void_p:
@@ -182,6 +183,28 @@ class CudaOps(Ops):
         self._attention(q, k, v, page_stride, cache, meta, table, out, n, num_heads, num_kv_heads, head_dim, scale, window)
 
     def _attention(self, q, k, v, page_stride, cache, meta, table, out, n, hq, hkv, hd, scale, window) -> None:
+        if self.use_tensor_cores and self.tc.fz_attn_decode_check(c_int(hq), c_int(hkv), c_int(hd)) == 0:
+            from ..engine.step import LONG_PORTION
+            if meta.n_short_rows > 0:
+                # rows of short portions and decoded tokens: split over key partitions, partials in float32 scratch
+                parts = self.tc.fz_attn_partitions(c_int(meta.max_context))
+                need = n * hq * parts * (hd + 2)
+                if self._attn_scratch is None or self._attn_scratch.numel() < need:
+                    self._attn_scratch = torch.empty(need, dtype=torch.float32, device=self.device)
+                part_o = self._attn_scratch
+                part_ml = self._attn_scratch[n * hq * parts * hd:]
+                self._check(self.tc.fz_attn_decode(
+                    _p(q), _p(k), _p(v), _p(meta.pos), _p(meta.seq_row), _p(meta.seg), _p(table), c_int(table.shape[1]),
+                    c_longlong(page_stride), c_int(cache.page_size), _p(out), _p(part_o), _p(part_ml), c_int(n),
+                    c_int(hq), c_int(hkv), c_int(hd), c_float(scale), c_int(window), c_int(meta.max_context),
+                    c_int(LONG_PORTION), self._stream()), "paged_attention (decode)")
+                self.launches += 1    # the combine kernel
+            if meta.n_tiles > 0:
+                self._check(self.tc.fz_attn_prefill(
+                    _p(q), _p(k), _p(v), _p(meta.seg), _p(meta.tiles), c_int(meta.n_tiles), _p(table),
+                    c_int(table.shape[1]), c_longlong(page_stride), c_int(cache.page_size), _p(out), c_int(hq),
+                    c_int(hkv), c_int(hd), c_float(scale), c_int(window), self._stream()), "paged_attention (prefill)")
+            return
         self._check(self.core.fz_attn_simt(
             _p(q), _p(k), _p(v), _p(meta.pos), _p(meta.seq_row), _p(table), c_int(table.shape[1]),
             c_longlong(page_stride), c_int(cache.page_size), _p(out), c_int(_CODE[self.dtype]), c_int(n), c_int(hq),

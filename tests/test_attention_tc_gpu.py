@@ -1,0 +1,93 @@
+"""The tensor-core attention kernels alone (bf16 cache): the split decode kernel with its combine, and the tile
+prefill kernel, against the plain reference, at head sizes 64 and 128, groups of 1 to 16 query heads per kv head, long
+contexts across several key partitions, portions that span several 64-row tiles, windows, odd page sizes."""
+import pytest
+import torch
+
+from plain_ops import PlainOps
+from test_kernels_gpu import Meta, fill_cache, make_cache
+
+pytestmark = pytest.mark.gpu
+BF = torch.bfloat16
+
+
+def run_both(Hq, Hkv, hd, bs, window, lengths, rows, seed=0):
+    """rows: list of (request, first position, count). Returns (cuda out, plain out, ops)."""
+    from fusezap_core_b200.kernels import cuda_ops
+    cu, pl = cuda_ops("bfloat16"), PlainOps(BF)
+    assert cu.use_tensor_cores and cu.tc.fz_attn_decode_check(Hq, Hkv, hd) == 0
+    g = torch.Generator().manual_seed(seed + Hq + hd + window)
+    mb = -(-max(lengths) // bs)
+    pages = mb * len(lengths) + 3
+    perm = torch.randperm(pages, generator=g).tolist()
+    table = [perm[r * mb:(r + 1) * mb] for r in range(len(lengths))]
+    cp = make_cache(pages, Hkv, bs, hd, BF, "cpu")
+    fill_cache(cp, table, lengths, g)
+    cc = make_cache(pages, Hkv, bs, hd, BF, "cuda")
+    cc.pool.copy_(cp.pool)
+    pos, seq_row = [], []
+    for req, p0, cnt in rows:
+        pos += list(range(p0, p0 + cnt)); seq_row += [req] * cnt
+    n = len(pos)
+    q = torch.randn(n, Hq * hd, generator=g).to(BF)
+    o, op = torch.full((n, Hq * hd), float("nan"), dtype=BF, device="cuda"), torch.empty(n, Hq * hd, dtype=BF)
+    scale = hd ** -0.5
+    cu.paged_attention(q.cuda(), cc, Meta(pos, seq_row, table, "cuda"), o, Hq, Hkv, hd, scale, window)
+    pl.paged_attention(q, cp, Meta(pos, seq_row, table, "cpu"), op, Hq, Hkv, hd, scale, window)
+    cu.check_errors()
+    return o.float().cpu(), op.float(), seq_row
+
+
+def close(o, op, what):
+    assert torch.isfinite(o).all(), f"{what}: unwritten or non-finite rows {torch.where(~torch.isfinite(o).all(-1))[0][:8].tolist()}"
+    err = (o - op).abs().max(-1).values
+    tol = 2.0 ** -7 * max(float(op.abs().max()), 1e-3)      # two bf16 steps: P is rounded to bf16 before P.V
+    bad = torch.where(err > tol)[0]
+    assert len(bad) == 0, f"{what}: rows {bad[:8].tolist()} differ by {float(err.max()):.3e} > {tol:.3e}"
+
+
+@pytest.mark.parametrize("Hq,Hkv,hd", [(4, 1, 128), (14, 2, 64), (8, 8, 64), (16, 1, 128), (10, 2, 128), (3, 3, 64)])
+@pytest.mark.parametrize("bs,window", [(16, 0), (8, 300), (5, 0)])
+def test_decode_rows_at_long_contexts(Hq, Hkv, hd, bs, window):
+    lengths = [1100, 257, 1, 640]
+    # single tokens at the ends of partitions and tiles, the first token, and short portions (below 8 rows)
+    rows = [(0, 1099, 1), (1, 255, 2), (2, 0, 1), (3, 511, 1), (3, 512, 1), (0, 62, 3), (3, 633, 7)]
+    o, op, _ = run_both(Hq, Hkv, hd, bs, window, lengths, rows)
+    close(o, op, "decode")
+
+
+@pytest.mark.parametrize("Hq,Hkv,hd", [(4, 1, 128), (14, 2, 64), (8, 8, 64), (2, 1, 128)])
+@pytest.mark.parametrize("bs,window", [(16, 0), (8, 100), (3, 0)])
+def test_prefill_portions(Hq, Hkv, hd, bs, window):
+    lengths = [400, 70, 200]
+    # a first portion from position 0 (three tiles), a later portion that continues a request (ragged last tile),
+    # a portion of exactly 8 rows, and single tokens beside them (mixed step)
+    rows = [(0, 0, 150), (2, 61, 139), (1, 62, 8), (0, 399, 1), (1, 30, 1)]
+    o, op, _ = run_both(Hq, Hkv, hd, bs, window, lengths, rows)
+    close(o, op, "prefill")
+
+
+def test_padding_rows_and_row_independence():
+    """A padding row gives zeros; a row's bits do not change with the rows around it."""
+    Hq, Hkv, hd = 8, 2, 128
+    lengths = [700, 300]
+    from fusezap_core_b200.kernels import cuda_ops
+    cu = cuda_ops("bfloat16")
+    g = torch.Generator().manual_seed(3)
+    cc = make_cache(80, Hkv, 16, hd, BF, "cuda")
+    table = [list(range(0, 44)), list(range(44, 63)) + [-1] * 25]
+    cp = make_cache(80, Hkv, 16, hd, BF, "cpu")
+    fill_cache(cp, table, lengths, g)
+    cc.pool.copy_(cp.pool)
+    q = torch.randn(43, Hq * hd, generator=g).to(BF).cuda()
+    pos = [699] + list(range(100, 140)) + [299] + [0]
+    seq = [0] + [1] * 40 + [1] + [-1]
+    full = torch.empty(43, Hq * hd, dtype=BF, device="cuda")
+    cu.paged_attention(q, cc, Meta(pos, seq, table, "cuda"), full, Hq, Hkv, hd, hd ** -0.5, 0)
+    assert float(full[42].float().abs().max()) == 0.0
+    one = torch.empty(1, Hq * hd, dtype=BF, device="cuda")
+    cu.paged_attention(q[:1].contiguous(), cc, Meta([699], [0], table, "cuda"), one, Hq, Hkv, hd, hd ** -0.5, 0)
+    assert torch.equal(one[0], full[0])
+    part = torch.empty(40, Hq * hd, dtype=BF, device="cuda")
+    cu.paged_attention(q[1:41].contiguous(), cc, Meta(list(range(100, 140)), [1] * 40, table, "cuda"), part, Hq, Hkv, hd, hd ** -0.5, 0)
+    assert torch.equal(part, full[1:41])

@@ -67,7 +67,7 @@ def build_trace(P: list[list[int]]) -> TraceBuilder:
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["tiny_llama", "tiny_qwen2", "tiny_window"])
+@pytest.mark.parametrize("name", ["tiny_llama", "tiny_qwen2", "tiny_window", "tiny_hd64", "tiny_hd128"])
 def test_replay_all_cuttings(name, dtype, tmp_path):
     model_dir, cfg, opts = make_model_dir(name, tmp_path, "float32")
     weights = read_weights(model_dir)
