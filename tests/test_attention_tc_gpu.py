@@ -79,12 +79,12 @@ def test_padding_rows_and_row_independence():
     cp = make_cache(80, Hkv, 16, hd, BF, "cpu")
     fill_cache(cp, table, lengths, g)
     cc.pool.copy_(cp.pool)
-    q = torch.randn(43, Hq * hd, generator=g).to(BF).cuda()
-    pos = [699] + list(range(100, 140)) + [299] + [0]
-    seq = [0] + [1] * 40 + [1] + [-1]
-    full = torch.empty(43, Hq * hd, dtype=BF, device="cuda")
+    q = torch.randn(42, Hq * hd, generator=g).to(BF).cuda()
+    pos = [699] + list(range(100, 140)) + [0]
+    seq = [0] + [1] * 40 + [-1]
+    full = torch.empty(42, Hq * hd, dtype=BF, device="cuda")
     cu.paged_attention(q, cc, Meta(pos, seq, table, "cuda"), full, Hq, Hkv, hd, hd ** -0.5, 0)
-    assert float(full[42].float().abs().max()) == 0.0
+    assert float(full[41].float().abs().max()) == 0.0
     one = torch.empty(1, Hq * hd, dtype=BF, device="cuda")
     cu.paged_attention(q[:1].contiguous(), cc, Meta([699], [0], table, "cuda"), one, Hq, Hkv, hd, hd ** -0.5, 0)
     assert torch.equal(one[0], full[0])
