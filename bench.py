@@ -167,7 +167,7 @@ def main() -> int:
         def one_step(i: int):
             portions = [Portion(s.seq_id, [s.tokens[s.num_computed]], [0]) for s in seqs]
             starts = runner.prepare(portions, pad_rows=bucket, pad_wanted=bucket)
-            eng._graphs[bucket].replay()
+            eng._graphs[(bucket, True)].replay()
             runner.commit(portions, starts)
             for s, st in zip(seqs, starts):   # the next token is fixed beforehand: nothing is read back in this loop
                 s.num_computed = st + 1
@@ -187,7 +187,7 @@ def main() -> int:
         ms = start.elapsed_time(end) / steps
         ctx_mean = ctx0 + steps / 2
         out.update(ms=ms, tok_s=batch * 1000.0 / ms, context=ctx_mean,
-                   launches=steps * eng.launches_per_graph.get(bucket, 0) + (model.ops.launches - launches0),
+                   launches=steps * eng.launches_per_graph.get((bucket, True), 0) + (model.ops.launches - launches0),
                    bytes=model.weight_bytes() + batch * ctx_mean * kv_bytes_per_token)
         if e2e:
             for _ in range(warmup):

@@ -5,7 +5,7 @@
 // have one order that depends only on its own position). All G = Hq / Hkv query heads of the kv head are the rows of
 // the 16-row MMA tile, so the keys and values of the partition are read once for the whole group (the reference's
 // default decode kernel lays the group out the same way: fusezap/device/cuda_kernels/attention.py:860-1043).
-// Keys and values come in tiles of 64 through a two-stage cp.async ring; warp w owns keys 16 w .. 16 w + 15 of each
+// Keys and values come in tiles of 64 through a three-stage cp.async ring; warp w owns keys 16 w .. 16 w + 15 of each
 // tile: S = Q K^T and O += P V with mma.sync m16n8k16, softmax online in the exp2 domain with float32 max and sum, P
 // rounded to bf16 for the second product. The four warps' (max, sum, O) are merged in warp order, and the partition's
 // unnormalised O with its (max, sum) goes to a float32 scratch; `attn_combine_kernel` merges a row's partitions in
@@ -19,6 +19,7 @@ using namespace fzattn;
 constexpr int PART = 256;      // keys per partition
 constexpr int TILE = 64;       // keys per shared-memory tile
 constexpr int THREADS = 128;
+constexpr int STAGES = 3;      // key / value tiles in flight
 
 template <int HD>
 __global__ void __launch_bounds__(THREADS)
@@ -30,10 +31,10 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   constexpr int KSTEPS = HD / 16;      // k-steps of Q K^T
   constexpr int NB = HD / 8;           // 8-wide output blocks of P V
   extern __shared__ __align__(128) uint8_t smem[];
-  // [2 stages][K tile | V tile] then the Q tile; the merge buffers reuse the stages
+  // [STAGES][K tile | V tile] then the Q tile; the merge buffers reuse the stages
   constexpr int TILE_BYTES = TILE * HD * 2;
   const uint32_t s_base = smem_u32(smem);
-  const uint32_t s_q = s_base + 4 * TILE_BYTES;
+  const uint32_t s_q = s_base + 2 * STAGES * TILE_BYTES;
 
   const int part = blockIdx.x, kvh = blockIdx.y, n = blockIdx.z, NP = gridDim.x;
   const int G = Hq / Hkv;
@@ -61,13 +62,16 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     }
   }
   const int ntiles = (k_end - k_begin + TILE - 1) / TILE;
-  auto issue = [&](int t) {
-    const uint32_t st = s_base + (t & 1) * 2 * TILE_BYTES;
-    load_kv_tile<HD, TILE, THREADS>(st, k_pool, trow, page_stride, head_off, page_size, k_begin + t * TILE, lo, p, tid);
-    load_kv_tile<HD, TILE, THREADS>(st + TILE_BYTES, v_pool, trow, page_stride, head_off, page_size, k_begin + t * TILE, lo, p, tid);
+  auto issue = [&](int t) {      // one commit group per call, empty past the last tile
+    if (t < ntiles) {
+      const uint32_t st = s_base + (t % STAGES) * 2 * TILE_BYTES;
+      load_kv_tile<HD, TILE, THREADS>(st, st + TILE_BYTES, k_pool, v_pool, trow, page_stride, head_off, page_size,
+                                      k_begin + t * TILE, lo, p, tid);
+    }
     cp_async_commit();
   };
-  issue(0);
+#pragma unroll
+  for (int t = 0; t < STAGES - 1; ++t) issue(t);
 
   uint32_t qf[KSTEPS][4];
   float o[NB][4];
@@ -76,14 +80,15 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};   // rows lane/4 and lane/4 + 8
 
   for (int t = 0; t < ntiles; ++t) {
-    if (t + 1 < ntiles) { issue(t + 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+    issue(t + STAGES - 1);
+    cp_async_wait<STAGES - 1>();      // all but the newest STAGES - 1 groups have landed: tile t is in
     __syncthreads();
     if (t == 0) {
 #pragma unroll
       for (int ks = 0; ks < KSTEPS; ++ks)
         ldmatrix_x4(qf[ks], s_q + swz<HD>(lane & 15, ks * 2 + (lane >> 4)));
     }
-    const uint32_t sk = s_base + (t & 1) * 2 * TILE_BYTES, sv = sk + TILE_BYTES;
+    const uint32_t sk = s_base + (t % STAGES) * 2 * TILE_BYTES, sv = sk + TILE_BYTES;
     // S (16 x 16): this warp's keys 16 warp .. + 15 of the tile
     float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
@@ -210,7 +215,7 @@ int launch(const void* q, const void* k_pool, const void* v_pool, const int* pos
            const int* table, int mb, long long page_stride, int page_size, void* out, float* part_o, float* part_ml,
            int N, int Hq, int Hkv, float scale, int window, int NP, int long_from, cudaStream_t stream) {
   constexpr int TILE_BYTES = TILE * HD * 2;
-  constexpr size_t smem_pipe = 4 * TILE_BYTES + 16 * HD * 2;
+  constexpr size_t smem_pipe = 2 * STAGES * TILE_BYTES + 16 * HD * 2;
   constexpr size_t smem_merge = (size_t)4 * 16 * HD * 4 + 4 * 16 * 2 * 4;
   constexpr size_t smem = smem_pipe > smem_merge ? smem_pipe : smem_merge;
   static bool raised = false;

@@ -43,24 +43,35 @@ __device__ __forceinline__ uint32_t swz(int row, int chunk) {
   return (uint32_t)(row * (HD * 2) + ((chunk ^ (row & 7)) << 4));
 }
 
-// Gathers keys [key0, key0 + ROWS) of one kv head from the paged pool into a swizzled [ROWS][HD] tile. Keys outside
-// [lo, hi] are zero-filled. `trow` is the request's block table.
+// Gathers keys [key0, key0 + ROWS) of one kv head, keys and values at once, from the paged pools into two swizzled
+// [ROWS][HD] tiles. THREADS / ROWS threads share a row: each looks its page up once and copies its part of the key row
+// and of the value row (they sit at the same offset of the two pools). Keys outside [lo, hi], or whose page is missing,
+// are zero-filled. `trow` is the request's block table.
 template <int HD, int ROWS, int THREADS>
-__device__ __forceinline__ void load_kv_tile(uint32_t smem_tile, const __nv_bfloat16* __restrict__ pool,
-                                             const int* __restrict__ trow, long long page_stride, long long head_off,
-                                             int page_size, int key0, int lo, int hi, int tid) {
+__device__ __forceinline__ void load_kv_tile(uint32_t smem_k, uint32_t smem_v, const __nv_bfloat16* __restrict__ k_pool,
+                                             const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ trow,
+                                             long long page_stride, long long head_off, int page_size, int key0, int lo,
+                                             int hi, int tid) {
+  constexpr int TPR = THREADS / ROWS;        // threads per row
   constexpr int CHUNKS = HD / 8;             // 16-byte chunks per row
-  for (int e = tid; e < ROWS * CHUNKS; e += THREADS) {
-    const int r = e / CHUNKS, c = e - r * CHUNKS;
-    const int key = key0 + r;
-    bool valid = key >= lo && key <= hi;
-    const __nv_bfloat16* src = pool;
-    if (valid) {
-      const int page = trow[key / page_size];
-      valid = page >= 0;
-      if (valid) src = pool + (long long)page * page_stride + head_off + (long long)(key % page_size) * HD + c * 8;
-    }
-    cp_async16(smem_tile + swz<HD>(r, c), src, valid);
+  constexpr int CPT = CHUNKS / TPR;          // chunks per thread
+  static_assert(THREADS % ROWS == 0 && CHUNKS % TPR == 0, "tile shape");
+  const int r = tid / TPR, c0 = (tid % TPR) * CPT;
+  const int key = key0 + r;
+  bool valid = key >= lo && key <= hi;
+  long long off = 0;
+  if (valid) {
+    const int pi = key / page_size;
+    const int page = trow[pi];
+    valid = page >= 0;
+    off = (long long)page * page_stride + head_off + (long long)(key - pi * page_size) * HD;
+  }
+  if (!valid) off = 0;
+#pragma unroll
+  for (int i = 0; i < CPT; ++i) {
+    const int c = c0 + i;
+    cp_async16(smem_k + swz<HD>(r, c), k_pool + off + c * 8, valid);
+    cp_async16(smem_v + swz<HD>(r, c), v_pool + off + c * 8, valid);
   }
 }
 

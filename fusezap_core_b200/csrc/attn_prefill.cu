@@ -50,8 +50,8 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   }
   auto issue = [&](int t) {
     const uint32_t st = s_base + (t & 1) * 2 * TILE_BYTES;
-    load_kv_tile<HD, BN, THREADS>(st, k_pool, trow, page_stride, head_off, page_size, k_begin + t * BN, lo_tile, last_pos, tid);
-    load_kv_tile<HD, BN, THREADS>(st + TILE_BYTES, v_pool, trow, page_stride, head_off, page_size, k_begin + t * BN, lo_tile, last_pos, tid);
+    load_kv_tile<HD, BN, THREADS>(st, st + TILE_BYTES, k_pool, v_pool, trow, page_stride, head_off, page_size,
+                                  k_begin + t * BN, lo_tile, last_pos, tid);
     cp_async_commit();
   };
   issue(0);

@@ -75,18 +75,97 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restric
   }
 }
 
+// The same for D % 4 == 0 and D <= 4 * 512 * VPT: 512 threads, a thread keeps its VPT float4 groups of the row in
+// registers (all loads are issued before anything depends on them), so the row is read once.
+template <typename TW, typename TH, int VPT>
+__global__ void __launch_bounds__(512)
+add_rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ delta, const TW* __restrict__ w,
+                       TH* __restrict__ h, const int* __restrict__ rows, int n_src, int D, float eps, int* err) {
+  __shared__ float scratch[32];
+  const int r = blockIdx.x;
+  const int D4 = D >> 2;
+  int src = r;
+  TH* hr = h + (size_t)r * D;
+  if (rows != nullptr) {
+    src = rows[r];
+    if (src < 0 || src >= n_src) {
+      if (src >= n_src && threadIdx.x == 0) atomicOr(err, FZ_ERR_ROW_RANGE);
+      for (int d = threadIdx.x; d < D; d += blockDim.x) hr[d] = Cvt<TH>::from_f(0.f);
+      return;
+    }
+  }
+  float4* xr = (float4*)(x + (size_t)src * D);
+  const float4* dr = delta ? (const float4*)(delta + (size_t)src * D) : nullptr;
+  const bool write_x = rows == nullptr && dr != nullptr;
+  float4 v[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int c = threadIdx.x + i * 512;
+    v[i] = c < D4 ? xr[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  if (dr) {
+    float4 dv[VPT];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int c = threadIdx.x + i * 512;
+      dv[i] = c < D4 ? dr[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) { v[i].x += dv[i].x; v[i].y += dv[i].y; v[i].z += dv[i].z; v[i].w += dv[i].w; }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    ss = fmaf(v[i].x, v[i].x, ss); ss = fmaf(v[i].y, v[i].y, ss); ss = fmaf(v[i].z, v[i].z, ss); ss = fmaf(v[i].w, v[i].w, ss);
+  }
+  if (write_x) {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int c = threadIdx.x + i * 512;
+      if (c < D4) xr[c] = v[i];
+    }
+  }
+  ss = block_sum(ss, scratch);
+  const float scale = 1.0f / sqrtf(ss * (1.0f / (float)D) + eps);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int c = threadIdx.x + i * 512;
+    if (c < D4) {
+      const int d = c * 4;
+      hr[d] = Cvt<TH>::from_f(Cvt<TW>::to_f(w[d]) * (v[i].x * scale));
+      hr[d + 1] = Cvt<TH>::from_f(Cvt<TW>::to_f(w[d + 1]) * (v[i].y * scale));
+      hr[d + 2] = Cvt<TH>::from_f(Cvt<TW>::to_f(w[d + 2]) * (v[i].z * scale));
+      hr[d + 3] = Cvt<TH>::from_f(Cvt<TW>::to_f(w[d + 3]) * (v[i].w * scale));
+    }
+  }
+}
+
+template <typename TW, typename TH>
+static int launch_norm(float* x, const float* delta, const void* w, void* h, const int* rows, int n_out, int n_src, int D,
+                       float eps, int* err, cudaStream_t stream) {
+  const bool vec = D % 4 == 0 && D <= 4 * 512 * 8 && (((uintptr_t)x | (uintptr_t)delta) & 15) == 0;
+  if (vec) {
+    const int groups = (D / 4 + 511) / 512;
+#define FZ_V(V) add_rmsnorm_vec_kernel<TW, TH, V><<<n_out, 512, 0, stream>>>(x, delta, (const TW*)w, (TH*)h, rows, n_src, D, eps, err)
+    if (groups <= 1) FZ_V(1); else if (groups <= 2) FZ_V(2); else if (groups <= 4) FZ_V(4); else FZ_V(8);
+#undef FZ_V
+  } else {
+    add_rmsnorm_kernel<TW, TH><<<n_out, 256, 0, stream>>>(x, delta, (const TW*)w, (TH*)h, rows, n_src, D, eps, err);
+  }
+  FZ_LAUNCH_CHECK();
+  return FZ_OK;
+}
+
 FZ_API int fz_add_rmsnorm(float* x, const float* delta, const void* w, int w_dtype, void* h, int h_dtype,
                           const int* rows, int n_out, int n_src, int D, float eps, int* err, cudaStream_t stream) {
   if (n_out <= 0) return FZ_OK;
-#define FZ_NORM(TW, TH) add_rmsnorm_kernel<TW, TH><<<n_out, 256, 0, stream>>>(x, delta, (const TW*)w, (TH*)h, rows, n_src, D, eps, err)
+#define FZ_NORM(TW, TH) return launch_norm<TW, TH>(x, delta, w, h, rows, n_out, n_src, D, eps, err, stream)
   if (w_dtype == FZ_F32 && h_dtype == FZ_F32) FZ_NORM(float, float);
-  else if (w_dtype == FZ_F32 && h_dtype == FZ_BF16) FZ_NORM(float, __nv_bfloat16);
-  else if (w_dtype == FZ_BF16 && h_dtype == FZ_BF16) FZ_NORM(__nv_bfloat16, __nv_bfloat16);
-  else if (w_dtype == FZ_BF16 && h_dtype == FZ_F32) FZ_NORM(__nv_bfloat16, float);
-  else return FZ_BAD_DTYPE;
+  if (w_dtype == FZ_F32 && h_dtype == FZ_BF16) FZ_NORM(float, __nv_bfloat16);
+  if (w_dtype == FZ_BF16 && h_dtype == FZ_BF16) FZ_NORM(__nv_bfloat16, __nv_bfloat16);
+  if (w_dtype == FZ_BF16 && h_dtype == FZ_F32) FZ_NORM(__nv_bfloat16, float);
 #undef FZ_NORM
-  FZ_LAUNCH_CHECK();
-  return FZ_OK;
+  return FZ_BAD_DTYPE;
 }
 
 // ------------------------------------------------------------------------------------------------ rotation + cache write
@@ -244,18 +323,50 @@ __device__ int block_argmax(const float* __restrict__ row, int V, float* s_val, 
   return res;
 }
 
-__global__ void argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V) {
+// Argmax of a row split over `gridDim.y` CTAs: each takes a contiguous slice and leaves its (value, index) in
+// `partial`; the CTA that arrives last at the row's counter reduces the slices in index order and resets the counter.
+__global__ void argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, float* partial_val,
+                              int* partial_idx, int* counters) {
   __shared__ float s_val[32];
   __shared__ int s_idx[32];
-  const int r = blockIdx.x;
-  const int res = block_argmax(logits + (size_t)r * V, V, s_val, s_idx);
-  if (threadIdx.x == 0) out[r] = res;
+  __shared__ int s_last;
+  const int r = blockIdx.x, S = gridDim.y, c = blockIdx.y;
+  const int chunk = (V + S - 1) / S;
+  const int lo = min(V, c * chunk), hi = min(V, lo + chunk);
+  const float* row = logits + (size_t)r * V;
+  int res = block_argmax(row + lo, hi - lo, s_val, s_idx);
+  if (threadIdx.x == 0) {
+    const bool empty = hi <= lo;
+    partial_val[r * S + c] = empty ? -INFINITY : row[lo + res];
+    partial_idx[r * S + c] = empty ? 0x7fffffff : lo + res;
+    __threadfence();
+    const int old = atomicAdd(&counters[r], 1);
+    s_last = old == S - 1;
+    if (s_last) counters[r] = 0;
+  }
+  __syncthreads();
+  if (!s_last || threadIdx.x != 0) return;
+  __threadfence();
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = 0; i < S; ++i) {
+    const float v = __ldcg(&partial_val[r * S + i]);
+    const int ix = __ldcg(&partial_idx[r * S + i]);
+    if (ix != 0x7fffffff && (bi == 0x7fffffff || better(v, ix, bv, bi))) { bv = v; bi = ix; }
+  }
+  out[r] = bi == 0x7fffffff ? 0 : bi;
 }
 
-FZ_API int fz_argmax(const float* logits, int* out, int R, int V, cudaStream_t stream) {
+// scratch: float partial_val[R * S], int partial_idx[R * S], int counters[R] (zero before the first call; the kernel
+// leaves them zero). S = fz_argmax_slices(V).
+FZ_API int fz_argmax_slices(int V) { const int s = (V + 8191) / 8192; return s < 1 ? 1 : (s > 64 ? 64 : s); }
+
+FZ_API int fz_argmax(const float* logits, int* out, int R, int V, float* partial_val, int* partial_idx, int* counters,
+                     cudaStream_t stream) {
   if (R <= 0) return FZ_OK;
   if (V <= 0) return FZ_BAD_SHAPE;
-  argmax_kernel<<<R, 1024, 0, stream>>>(logits, out, V);
+  dim3 grid(R, fz_argmax_slices(V));
+  argmax_kernel<<<grid, 512, 0, stream>>>(logits, out, V, partial_val, partial_idx, counters);
   FZ_LAUNCH_CHECK();
   return FZ_OK;
 }

@@ -69,8 +69,9 @@ class LLMEngine:
         self._unif_d = torch.zeros(R, dtype=torch.float64, device=dev)
         self._ids_d = torch.zeros(R, dtype=torch.int32, device=dev)
         self.cuda_graphs = bool(cuda_graphs) and pin
-        self._graphs: dict[int, torch.cuda.CUDAGraph] = {}
-        self.launches_per_graph: dict[int, int] = {}     # kernels of this package in one replay of a bucket's graph
+        self._graphs: dict[tuple, torch.cuda.CUDAGraph] = {}     # (bucket, all rows greedy) -> captured step
+        self.launches_per_graph: dict[tuple, int] = {}           # kernels of this package in one replay of it
+        self._greedy_step = True
         self._buckets = sorted({min(1 << i, R) for i in range(R.bit_length() + 1)})
         self.stats = {"steps": 0, "decode_steps": 0, "prefill_steps": 0, "mixed_steps": 0, "tokens": 0,
                       "preemptions": 0, "graph_replays": 0, "h2d_bytes": 0, "d2h_bytes": 0}
@@ -157,6 +158,8 @@ class LLMEngine:
             device_row = p.on_device and not p.greedy
             self._temp_h[i] = p.temperature if device_row else 0.0
             self._unif_h[i] = seq.sampler.next_uniform() if device_row else 0.0
+        # all rows greedy: the row-split argmax kernel picks the tokens; else the sampling kernel (argmax for its greedy rows)
+        self._greedy_step = all(s.params.greedy or not s.params.on_device for s in producing)
         bucket = next((b for b in self._buckets if b >= len(portions)), None) if decode_only and self.cuda_graphs else None
         pad = bucket or 0
         starts = runner.prepare(portions, pad_rows=pad, pad_wanted=pad)
@@ -171,7 +174,8 @@ class LLMEngine:
         self.stats["h2d_bytes"] += runner.meta.size * 4 + n_w * 12
         logits = None
         if bucket is not None:
-            g = self._graphs.get(bucket)
+            key = (bucket, self._greedy_step)
+            g = self._graphs.get(key)
             if g is None:
                 logits = self._eager(n_w)              # warm-up: builds, sets kernel attributes, sizes the buffers
                 torch.cuda.synchronize()
@@ -179,10 +183,10 @@ class LLMEngine:
                 before = ops.launches
                 with torch.cuda.graph(g):
                     self._eager(n_w)
-                self.launches_per_graph[bucket] = ops.launches - before
-                self._graphs[bucket] = g
+                self.launches_per_graph[key] = ops.launches - before
+                self._graphs[key] = g
             g.replay()
-            ops.launches += self.launches_per_graph[bucket]
+            ops.launches += self.launches_per_graph[key]
             self.stats["graph_replays"] += 1
             logits = runner.ws.get("logits", (n_w, self.model.spec.vocab_size), torch.float32)
         else:
@@ -202,7 +206,9 @@ class LLMEngine:
 
     def _eager(self, n_wanted: int) -> torch.Tensor:
         logits = self.runner.forward()
-        if n_wanted:
+        if n_wanted and self._greedy_step:
+            self.ops.argmax(logits, self._ids_d[:n_wanted])
+        elif n_wanted:
             self.ops.sample(logits, self._temp_d[:n_wanted], self._unif_d[:n_wanted], self._ids_d[:n_wanted])
         return logits
 

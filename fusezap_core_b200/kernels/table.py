@@ -44,6 +44,7 @@ class CudaOps(Ops):
         self.core = load("fzb200_core")
         self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.launches = 0
+        self._argmax_scratch = None
         self.tc = None
         if self.dtype == torch.bfloat16:
             # tensor-core kernels and their split-K workspace: float32 partial tiles (at most 296 tiles x splits of
@@ -225,7 +226,15 @@ class CudaOps(Ops):
         r, v = logits.shape
         if out.shape[0] != r:
             raise KernelError(f"argmax: logits {tuple(logits.shape)}, out {tuple(out.shape)}")
-        self._check(self.core.fz_argmax(_p(logits), _p(out), c_int(r), c_int(v), self._stream()), "argmax")
+        # scratch of the row-split argmax: per row up to 64 partial (value, index) pairs and one counter (kept zero)
+        if self._argmax_scratch is None or self._argmax_scratch[2].numel() < r:
+            cap = max(r, 64)
+            self._argmax_scratch = (torch.empty(cap * 64, dtype=torch.float32, device=self.device),
+                                    torch.empty(cap * 64, dtype=torch.int32, device=self.device),
+                                    torch.zeros(cap, dtype=torch.int32, device=self.device))
+        pv, pi, cnt = self._argmax_scratch
+        self._check(self.core.fz_argmax(_p(logits), _p(out), c_int(r), c_int(v), _p(pv), _p(pi), _p(cnt), self._stream()),
+                    "argmax")
 
     def sample(self, logits, temperature, uniform, out) -> None:
         self._want(logits, "logits", (torch.float32,), 2)
