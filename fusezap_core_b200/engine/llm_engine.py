@@ -68,7 +68,7 @@ class LLMEngine:
         self._temp_d = torch.zeros(R, dtype=torch.float32, device=dev)
         self._unif_d = torch.zeros(R, dtype=torch.float64, device=dev)
         self._ids_d = torch.zeros(R, dtype=torch.int32, device=dev)
-        self.cuda_graphs = bool(cuda_graphs) and pin
+        self.cuda_graphs = bool(cuda_graphs) and pin and model.graph_safe()
         self._graphs: dict[tuple, torch.cuda.CUDAGraph] = {}     # (bucket, all rows greedy) -> captured step
         self.launches_per_graph: dict[tuple, int] = {}           # kernels of this package in one replay of it
         self._greedy_step = True

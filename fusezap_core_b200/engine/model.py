@@ -84,6 +84,13 @@ class DecoderModel:
         return {(n, name): tuple(shape) for n, e in enumerate(self.spec.schedule)
                 for name, shape in self.layers[e.layer].mixer.state_need().items()}
 
+    def graph_safe(self) -> bool:
+        """True if every part's forward is a fixed sequence of kernels over device data (see `Part.graph_safe`)."""
+        parts = [self.final_norm, *self.positions.values()]
+        for block in self.layers:
+            parts += [block, block.mixer, block.ffn]
+        return all(getattr(p, "graph_safe", True) for p in parts)
+
     def expected_tensors(self) -> dict[str, ParamSpec]:
         return declared_tensors(self.spec, self.layers)
 

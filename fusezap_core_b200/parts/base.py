@@ -70,6 +70,11 @@ class LayerCache:
 
 
 class Part:
+    # False for a part whose forward depends on the step's host-side metadata (for instance a Python loop over
+    # `ctx.meta.segments`): such a step cannot be replayed from a captured CUDA graph, and the engine then runs every
+    # step kernel by kernel.
+    graph_safe = True
+
     def tensors(self) -> dict[str, ParamSpec]:
         return {}
 
