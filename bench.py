@@ -79,14 +79,16 @@ class ClockSampler:
 
 
 def reference_arm(a) -> int:
-    """The unmodified reference through its own public API, if it is installed under baseline/_ref."""
+    """The unmodified reference through its own public API, if it is installed under baseline/_ref. The offline
+    install (`pip install --no-index --no-build-isolation --find-links /opt/wheelhouse --target baseline/_ref`) fails
+    here: the reference's build backend, hatchling, is not among the offline wheels, so no wheel can be built."""
     ref = os.path.join(ROOT, "baseline", "_ref")
-    why = None
     if not os.path.isdir(os.path.join(ref, "fusezap")):
-        why = "the reference is not installed under baseline/_ref"
+        why = ("the reference cannot be installed offline: its build backend (hatchling) is not in /opt/wheelhouse, "
+               "pip stops with ModuleNotFoundError: No module named 'hatchling'")
     else:
-        why = ("the reference has no sm_100 path (its CUDA GEMMs are sm_90a wgmma, which does not build for sm_100a, and its "
-               "decode kernels are NVRTC-compiled at run time for architectures up to sm_90); not run on this pool")
+        why = ("the reference has no sm_100 path: its CUDA GEMMs are sm_90a wgmma strings compiled at run time, which do "
+               "not build for sm_100a")
     print(json.dumps({"impl": "reference", "unavailable": why}))
     return 0
 
