@@ -28,6 +28,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                    const int* __restrict__ seq_row, const int* __restrict__ seg, const int* __restrict__ table, int mb,
                    long long page_stride, int page_size, float* __restrict__ part_o, float* __restrict__ part_ml,
                    int Hq, int Hkv, float scale_log2, int window, int long_from) {
+  fz_grid_wait();
+  fz_grid_launch_dependents();
   constexpr int KSTEPS = HD / 16;      // k-steps of Q K^T
   constexpr int NB = HD / 8;           // 8-wide output blocks of P V
   extern __shared__ __align__(128) uint8_t smem[];
@@ -185,6 +187,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 __global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     const int* __restrict__ seq_row, const int* __restrict__ seg,
                                     __nv_bfloat16* __restrict__ out, int Hq, int HD, int NP, int long_from) {
+  fz_grid_wait();
+  fz_grid_launch_dependents();
   const int n = blockIdx.y, h = blockIdx.x;
   __nv_bfloat16* orow = out + ((size_t)n * Hq + h) * HD;
   const int row = seq_row[n];
@@ -225,12 +229,13 @@ int launch(const void* q, const void* k_pool, const void* v_pool, const int* pos
     raised = true;
   }
   dim3 grid(NP, Hkv, N);
-  attn_decode_kernel<HD><<<grid, THREADS, smem, stream>>>(
-      (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, pos, seq_row, seg, table, mb,
-      page_stride, page_size, part_o, part_ml, Hq, Hkv, scale * 1.4426950408889634f, window, long_from);
+  fz_launch(attn_decode_kernel<HD>, grid, dim3(THREADS), smem, stream, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
+            (const __nv_bfloat16*)v_pool, pos, seq_row, seg, table, mb, page_stride, page_size, part_o, part_ml, Hq, Hkv,
+            scale * 1.4426950408889634f, window, long_from);
   FZ_LAUNCH_CHECK();
   dim3 cgrid(Hq, N);
-  attn_combine_kernel<<<cgrid, HD < 128 ? 64 : 128, 0, stream>>>(part_o, part_ml, seq_row, seg, (__nv_bfloat16*)out, Hq, HD, NP, long_from);
+  fz_launch(attn_combine_kernel, cgrid, dim3(HD < 128 ? 64 : 128), 0, stream, (const float*)part_o, (const float*)part_ml,
+            seq_row, seg, (__nv_bfloat16*)out, Hq, HD, NP, long_from);
   FZ_LAUNCH_CHECK();
   return FZ_OK;
 }

@@ -22,6 +22,8 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
                     const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ seg,
                     const int* __restrict__ tiles, const int* __restrict__ table, int mb, long long page_stride,
                     int page_size, __nv_bfloat16* __restrict__ out, int Hq, int Hkv, float scale_log2, int window) {
+  fz_grid_wait();
+  fz_grid_launch_dependents();
   constexpr int KSTEPS = HD / 16, NB = HD / 8, TILE_BYTES = BN * HD * 2;
   extern __shared__ __align__(128) uint8_t smem[];
   const uint32_t s_base = smem_u32(smem);          // [2 stages][K | V], then Q
@@ -179,9 +181,9 @@ int launch(const void* q, const void* k_pool, const void* v_pool, const int* seg
     raised = true;
   }
   dim3 grid(n_tiles, Hq);
-  attn_prefill_kernel<HD><<<grid, THREADS, smem, stream>>>(
-      (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, seg, tiles, table, mb,
-      page_stride, page_size, (__nv_bfloat16*)out, Hq, Hkv, scale * 1.4426950408889634f, window);
+  fz_launch(attn_prefill_kernel<HD>, grid, dim3(THREADS), smem, stream, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
+            (const __nv_bfloat16*)v_pool, seg, tiles, table, mb, page_stride, page_size, (__nv_bfloat16*)out, Hq, Hkv,
+            scale * 1.4426950408889634f, window);
   FZ_LAUNCH_CHECK();
   return FZ_OK;
 }

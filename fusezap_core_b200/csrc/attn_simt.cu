@@ -23,6 +23,8 @@ __global__ void attn_simt_kernel(const T* __restrict__ q, const T* __restrict__ 
                                  const int* __restrict__ pos, const int* __restrict__ seq_row,
                                  const int* __restrict__ table, int mb, long long page_stride, int page_size,
                                  T* __restrict__ out, int Hq, int Hkv, int hd, float scale, int window, int* err) {
+  fz_grid_wait();
+  fz_grid_launch_dependents();
   extern __shared__ float smem[];
   const int n = blockIdx.x, kvh = blockIdx.y;
   const int G = Hq / Hkv;
@@ -130,8 +132,8 @@ int launch(const void* q, const void* k_pool, const void* v_pool, const int* pos
     allowed = smem;
   }
   dim3 grid(N, Hkv);
-  kern<<<grid, 32 * W, smem, stream>>>((const T*)q, (const T*)k_pool, (const T*)v_pool, pos, seq_row, table, mb,
-                                       page_stride, page_size, (T*)out, Hq, Hkv, hd, scale, window, err);
+  fz_launch(kern, grid, dim3(32 * W), smem, stream, (const T*)q, (const T*)k_pool, (const T*)v_pool, pos, seq_row, table, mb,
+            page_stride, page_size, (T*)out, Hq, Hkv, hd, scale, window, err);
   FZ_LAUNCH_CHECK();
   return FZ_OK;
 }

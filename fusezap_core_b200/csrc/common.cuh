@@ -3,6 +3,7 @@
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define FZ_API extern "C" __attribute__((visibility("default")))
 
@@ -34,6 +35,39 @@ enum FzDeviceError : int {
     cudaError_t e__ = cudaGetLastError();          \
     if (e__ != cudaSuccess) return (int)e__;       \
   } while (0)
+
+// Programmatic dependent launch. A kernel launched with `fz_launch(..., pdl = true)` may start while the kernel before
+// it in the stream is still running: its blocks become resident and run their prologue early. Every kernel of this
+// package therefore calls `fz_grid_wait()` before it reads or writes anything another kernel of the step touches (on
+// every path, also the early-exit ones: a grid that finished without waiting would let its successor's wait return
+// while an older grid still runs), and `fz_grid_launch_dependents()` to let its own successor come in early.
+__device__ __forceinline__ void fz_grid_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void fz_grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// FZB200_PDL=0 in the environment turns programmatic dependent launch off (plain stream order).
+inline bool fz_pdl_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("FZB200_PDL");
+    return !(v && v[0] == '0');
+  }();
+  return on;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t fz_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = fz_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 template <typename T> struct Cvt;
 template <> struct Cvt<float> {

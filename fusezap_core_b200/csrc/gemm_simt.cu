@@ -17,6 +17,8 @@ template <typename TA, typename TC>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TA* __restrict__ A, const TA* __restrict__ W, const float* __restrict__ bias,
                  TC* __restrict__ C, int M, int N, int K) {
+  fz_grid_wait();
+  fz_grid_launch_dependents();
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -79,6 +81,8 @@ template <typename TA, typename TC>
 __global__ void __launch_bounds__(256)
 gemm_simt_small_kernel(const TA* __restrict__ A, const TA* __restrict__ W, const float* __restrict__ bias,
                        TC* __restrict__ C, int M, int N, int K) {
+  fz_grid_wait();
+  fz_grid_launch_dependents();
   __shared__ float As[SK][SM_ROWS + 1];
   __shared__ float Ws[SK][SN + 1];
   const int tid = threadIdx.x;
@@ -122,10 +126,10 @@ template <typename TA, typename TC>
 int launch(const void* A, const void* W, const float* bias, void* C, int M, int N, int K, cudaStream_t stream) {
   if (M <= SM_ROWS) {
     dim3 grid((N + SN - 1) / SN, (M + SM_ROWS - 1) / SM_ROWS);
-    gemm_simt_small_kernel<TA, TC><<<grid, 256, 0, stream>>>((const TA*)A, (const TA*)W, bias, (TC*)C, M, N, K);
+    fz_launch(gemm_simt_small_kernel<TA, TC>, grid, dim3(256), 0, stream, (const TA*)A, (const TA*)W, bias, (TC*)C, M, N, K);
   } else {
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-    gemm_simt_kernel<TA, TC><<<grid, 256, 0, stream>>>((const TA*)A, (const TA*)W, bias, (TC*)C, M, N, K);
+    fz_launch(gemm_simt_kernel<TA, TC>, grid, dim3(256), 0, stream, (const TA*)A, (const TA*)W, bias, (TC*)C, M, N, K);
   }
   FZ_LAUNCH_CHECK();
   return FZ_OK;

@@ -166,16 +166,37 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_d = *tmem_slot;
+  fz_grid_launch_dependents();
+  if (warp != 0) fz_grid_wait();    // warp 0 waits after it has requested the first weight stages
 
   if (warp == 0) {
     if (lane == 0) {
+      // The weight operand does not depend on the kernel before this one: its first stages are requested before the
+      // wait on that kernel, so the weights stream in while it finishes. (swap mode: A holds the weights; rows mode: B.)
+      auto load_weights = [&](int i, int s) {
+        uint8_t* sa = smem + (size_t)s * STAGE_BYTES;
+        if (p.swap) tma_load_2d(sa, &map_a, &full[s], (kb0 + i) * BK, tile_a * BM);
+        else tma_load_2d(sa + A_BYTES, &map_b, &full[s], (kb0 + i) * BK, tile_b * BN);
+      };
+      auto load_activations = [&](int i, int s) {
+        uint8_t* sa = smem + (size_t)s * STAGE_BYTES;
+        if (p.swap) tma_load_2d(sa + A_BYTES, &map_b, &full[s], (kb0 + i) * BK, tile_b * BN);
+        else tma_load_2d(sa, &map_a, &full[s], (kb0 + i) * BK, tile_a * BM);
+      };
+      const int early = nkb < p.stages ? nkb : p.stages;
+      for (int i = 0; i < early; ++i) {
+        mbar_expect_tx(&full[i], STAGE_BYTES);
+        load_weights(i, i);
+      }
+      fz_grid_wait();
       for (int i = 0; i < nkb; ++i) {
         const int s = i % p.stages, round = i / p.stages;
-        if (round > 0 && !mbar_wait(&empty[s], (round - 1) & 1)) { flag[1] = 1; break; }
-        uint8_t* sa = smem + (size_t)s * STAGE_BYTES;
-        mbar_expect_tx(&full[s], STAGE_BYTES);
-        tma_load_2d(sa, &map_a, &full[s], (kb0 + i) * BK, tile_a * BM);
-        tma_load_2d(sa + A_BYTES, &map_b, &full[s], (kb0 + i) * BK, tile_b * BN);
+        if (round > 0) {
+          if (!mbar_wait(&empty[s], (round - 1) & 1)) { flag[1] = 1; break; }
+          mbar_expect_tx(&full[s], STAGE_BYTES);
+          load_weights(i, s);
+        }
+        load_activations(i, s);
       }
     }
   } else if (warp == 1) {
@@ -372,7 +393,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, dim3 g
     if (e != cudaSuccess) return (int)e;
     allowed = smem;
   }
-  gemm_tc_kernel<BN><<<grid, NUM_THREADS, smem, stream>>>(ma, mb, p);
+  fz_launch(gemm_tc_kernel<BN>, grid, dim3(NUM_THREADS), smem, stream, ma, mb, p);
   FZ_LAUNCH_CHECK();
   return FZ_OK;
 }

@@ -12,6 +12,8 @@
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tokens, float* __restrict__ x,
                              int D, int V, int* err) {
+  fz_grid_wait();
+  fz_grid_launch_dependents();
   const int n = blockIdx.x;
   const int tok = tokens[n];
   float* xr = x + (size_t)n * D;
@@ -28,9 +30,9 @@ FZ_API int fz_embed(const void* table, int table_dtype, const int* tokens, float
                     cudaStream_t stream) {
   if (N <= 0) return FZ_OK;
   if (table_dtype == FZ_F32)
-    embed_kernel<float><<<N, 256, 0, stream>>>((const float*)table, tokens, x, D, V, err);
+    fz_launch(embed_kernel<float>, dim3(N), dim3(256), 0, stream, (const float*)table, tokens, x, D, V, err);
   else if (table_dtype == FZ_BF16)
-    embed_kernel<__nv_bfloat16><<<N, 256, 0, stream>>>((const __nv_bfloat16*)table, tokens, x, D, V, err);
+    fz_launch(embed_kernel<__nv_bfloat16>, dim3(N), dim3(256), 0, stream, (const __nv_bfloat16*)table, tokens, x, D, V, err);
   else
     return FZ_BAD_DTYPE;
   FZ_LAUNCH_CHECK();
@@ -44,6 +46,8 @@ template <typename TW, typename TH>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, const TW* __restrict__ w,
                                    TH* __restrict__ h, const int* __restrict__ rows, int n_src, int D, float eps,
                                    int* err) {
+  fz_grid_wait();
+  fz_grid_launch_dependents();
   __shared__ float scratch[32];
   const int r = blockIdx.x;
   int src = r;
@@ -81,6 +85,8 @@ template <typename TW, typename TH, int VPT>
 __global__ void __launch_bounds__(512)
 add_rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ delta, const TW* __restrict__ w,
                        TH* __restrict__ h, const int* __restrict__ rows, int n_src, int D, float eps, int* err) {
+  fz_grid_wait();
+  fz_grid_launch_dependents();
   __shared__ float scratch[32];
   const int r = blockIdx.x;
   const int D4 = D >> 2;
@@ -146,11 +152,11 @@ static int launch_norm(float* x, const float* delta, const void* w, void* h, con
   const bool vec = D % 4 == 0 && D <= 4 * 512 * 8 && (((uintptr_t)x | (uintptr_t)delta) & 15) == 0;
   if (vec) {
     const int groups = (D / 4 + 511) / 512;
-#define FZ_V(V) add_rmsnorm_vec_kernel<TW, TH, V><<<n_out, 512, 0, stream>>>(x, delta, (const TW*)w, (TH*)h, rows, n_src, D, eps, err)
+#define FZ_V(V) fz_launch(add_rmsnorm_vec_kernel<TW, TH, V>, dim3(n_out), dim3(512), 0, stream, x, delta, (const TW*)w, (TH*)h, rows, n_src, D, eps, err)
     if (groups <= 1) FZ_V(1); else if (groups <= 2) FZ_V(2); else if (groups <= 4) FZ_V(4); else FZ_V(8);
 #undef FZ_V
   } else {
-    add_rmsnorm_kernel<TW, TH><<<n_out, 256, 0, stream>>>(x, delta, (const TW*)w, (TH*)h, rows, n_src, D, eps, err);
+    fz_launch(add_rmsnorm_kernel<TW, TH>, dim3(n_out), dim3(256), 0, stream, x, delta, (const TW*)w, (TH*)h, rows, n_src, D, eps, err);
   }
   FZ_LAUNCH_CHECK();
   return FZ_OK;
@@ -178,6 +184,8 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const float*
                                      T* __restrict__ k_pool, T* __restrict__ v_pool, long long page_stride,
                                      int page_size, int write, T* __restrict__ q_out, int Hq, int Hkv, int hd,
                                      int max_len, int* err) {
+  fz_grid_wait();
+  fz_grid_launch_dependents();
   const int n = blockIdx.x;
   const int half = hd >> 1;
   const int row = seq_row[n];
@@ -237,13 +245,12 @@ FZ_API int fz_rope_kv_write(const float* qkv, const float* cos_t, const float* s
   if (N <= 0) return FZ_OK;
   if (hd % 2 || hd <= 0) return FZ_BAD_SHAPE;
   if (dtype == FZ_F32)
-    rope_kv_write_kernel<float><<<N, 256, 0, stream>>>(qkv, cos_t, sin_t, pos, seq_row, table, mb, (float*)k_pool,
-                                                       (float*)v_pool, page_stride, page_size, write, (float*)q_out,
-                                                       Hq, Hkv, hd, max_len, err);
+    fz_launch(rope_kv_write_kernel<float>, dim3(N), dim3(256), 0, stream, qkv, cos_t, sin_t, pos, seq_row, table, mb,
+              (float*)k_pool, (float*)v_pool, page_stride, page_size, write, (float*)q_out, Hq, Hkv, hd, max_len, err);
   else if (dtype == FZ_BF16)
-    rope_kv_write_kernel<__nv_bfloat16><<<N, 256, 0, stream>>>(
-        qkv, cos_t, sin_t, pos, seq_row, table, mb, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, page_stride,
-        page_size, write, (__nv_bfloat16*)q_out, Hq, Hkv, hd, max_len, err);
+    fz_launch(rope_kv_write_kernel<__nv_bfloat16>, dim3(N), dim3(256), 0, stream, qkv, cos_t, sin_t, pos, seq_row, table,
+              mb, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, page_stride, page_size, write, (__nv_bfloat16*)q_out,
+              Hq, Hkv, hd, max_len, err);
   else
     return FZ_BAD_DTYPE;
   FZ_LAUNCH_CHECK();
@@ -253,6 +260,8 @@ FZ_API int fz_rope_kv_write(const float* qkv, const float* cos_t, const float* s
 // ------------------------------------------------------------------------------------------------ SwiGLU
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, long long total, int I) {
+  fz_grid_wait();
+  fz_grid_launch_dependents();
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (long long)gridDim.x * blockDim.x) {
     const long long n = idx / I;
@@ -270,9 +279,9 @@ FZ_API int fz_swiglu(const void* gu, void* out, int dtype, int N, int I, cudaStr
   long long blocks = (total + block - 1) / block;
   if (blocks > 148LL * 32) blocks = 148LL * 32;
   if (dtype == FZ_F32)
-    swiglu_kernel<float><<<(int)blocks, block, 0, stream>>>((const float*)gu, (float*)out, total, I);
+    fz_launch(swiglu_kernel<float>, dim3((int)blocks), dim3(block), 0, stream, (const float*)gu, (float*)out, total, I);
   else if (dtype == FZ_BF16)
-    swiglu_kernel<__nv_bfloat16><<<(int)blocks, block, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, total, I);
+    fz_launch(swiglu_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(block), 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, total, I);
   else
     return FZ_BAD_DTYPE;
   FZ_LAUNCH_CHECK();
@@ -327,6 +336,8 @@ __device__ int block_argmax(const float* __restrict__ row, int V, float* s_val, 
 // `partial`; the CTA that arrives last at the row's counter reduces the slices in index order and resets the counter.
 __global__ void argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, float* partial_val,
                               int* partial_idx, int* counters) {
+  fz_grid_wait();
+  fz_grid_launch_dependents();
   __shared__ float s_val[32];
   __shared__ int s_idx[32];
   __shared__ int s_last;
@@ -366,7 +377,7 @@ FZ_API int fz_argmax(const float* logits, int* out, int R, int V, float* partial
   if (R <= 0) return FZ_OK;
   if (V <= 0) return FZ_BAD_SHAPE;
   dim3 grid(R, fz_argmax_slices(V));
-  argmax_kernel<<<grid, 512, 0, stream>>>(logits, out, V, partial_val, partial_idx, counters);
+  fz_launch(argmax_kernel, grid, dim3(512), 0, stream, logits, out, V, partial_val, partial_idx, counters);
   FZ_LAUNCH_CHECK();
   return FZ_OK;
 }
@@ -375,6 +386,8 @@ FZ_API int fz_argmax(const float* logits, int* out, int R, int V, float* partial
 // Thread t owns the contiguous range [t * chunk, (t + 1) * chunk), so partial sums are in index order.
 __global__ void sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
                               const double* __restrict__ uniform, int* __restrict__ out, int V) {
+  fz_grid_wait();
+  fz_grid_launch_dependents();
   __shared__ float s_val[32];
   __shared__ int s_idx[32];
   __shared__ double s_sum[1024];
@@ -425,7 +438,7 @@ FZ_API int fz_sample(const float* logits, const float* temperature, const double
                      cudaStream_t stream) {
   if (R <= 0) return FZ_OK;
   if (V <= 0) return FZ_BAD_SHAPE;
-  sample_kernel<<<R, 1024, 0, stream>>>(logits, temperature, uniform, out, V);
+  fz_launch(sample_kernel, dim3(R), dim3(1024), 0, stream, logits, temperature, uniform, out, V);
   FZ_LAUNCH_CHECK();
   return FZ_OK;
 }
