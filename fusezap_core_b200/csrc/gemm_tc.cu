@@ -18,57 +18,17 @@
 // the sum has one fixed order whatever the arrival order (as the reference's split-K does: wgmma.py:209-239). No
 // device-side spin on other CTAs exists; waits on this CTA's own mbarriers are bounded by a time limit after which the
 // kernel sets an error bit and leaves.
-#include "common.cuh"
-#include <cuda.h>
-#include <mutex>
-#include <unordered_map>
+#include "tma.cuh"
 
 namespace {
+using namespace fztma;
 
 constexpr int BM = 128;           // TMEM lanes = rows of the 128-row operand
 constexpr int BK = 64;            // k per stage: 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int NUM_THREADS = 192;  // warp 0 TMA, warp 1 MMA, warps 2..5 epilogue
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 
 // ---------------------------------------------------------------------------------------------- PTX wrappers
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ unsigned long long global_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-// Waits for the phase with the given parity; gives up after WAIT_LIMIT_NS and returns false.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  const uint32_t addr = smem_u32(bar);
-  unsigned long long t0 = 0;
-  for (uint32_t spins = 0;; ++spins) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.b32 %0, 1, 0, p;\n\t}"
-        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-    if (done) return true;
-    if ((spins & 1023u) == 1023u) {
-      const unsigned long long now = global_ns();
-      if (t0 == 0) t0 = now;
-      else if (now - t0 > WAIT_LIMIT_NS) return false;
-    }
-  }
-}
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
-}
 __device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(cols) : "memory");
   asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -159,7 +119,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     for (int s = 0; s < p.stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     mbar_init(acc_ready, 1);
     flag[0] = 0; flag[1] = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_init_fence();
   }
   if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
   tc_fence_before();
@@ -330,59 +290,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 }
 
 // ---------------------------------------------------------------------------------------------- host side
-typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiled encode_fn() {
-  static EncodeTiled fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiled)p;
-  });
-  return fn;
-}
-
-struct MapKey {
-  const void* ptr; int rows, K, box_rows;
-  bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && K == o.K && box_rows == o.box_rows; }
-};
-struct MapKeyHash {
-  size_t operator()(const MapKey& k) const {
-    return std::hash<const void*>()(k.ptr) ^ ((size_t)k.rows * 1000003u) ^ ((size_t)k.K * 10007u) ^ ((size_t)k.box_rows << 20);
-  }
-};
-
-// A 2-D map over a row-major [rows, K] bf16 matrix with boxes of box_rows x 64 elements and the 128-byte swizzle.
-// Out-of-range rows and k read as zero. Maps are cached by (pointer, shape, box): weights are encoded once.
-int get_map(const void* ptr, int rows, int K, int box_rows, CUtensorMap* out) {
-  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
-  static std::mutex mu;
-  std::lock_guard<std::mutex> lock(mu);
-  const MapKey key{ptr, rows, K, box_rows};
-  auto it = cache.find(key);
-  if (it != cache.end()) { *out = it->second; return FZ_OK; }
-  EncodeTiled enc = encode_fn();
-  if (!enc) return FZ_NO_DRIVER_ENTRY;
-  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-  const cuuint32_t estr[2] = {1, 1};
-  CUtensorMap m;
-  const CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return FZ_TMAP_ENCODE;
-  if (cache.size() > 4096) cache.clear();
-  cache[key] = m;
-  *out = m;
-  return FZ_OK;
-}
-
 template <int BN>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, dim3 grid, cudaStream_t stream) {
   constexpr int STAGE_BYTES = (BM + BN) * BK * 2;
@@ -459,8 +366,8 @@ FZ_API int fz_gemm_tc(const void* x, const void* w, const float* bias, void* c, 
         partial_bytes >= (long long)tiles * splits * BM * bn * 4) {
       p.splits = splits; p.partials = partials; p.counters = counters;
     }
-    if ((st = get_map(w, N, K, BM, &ma)) != FZ_OK) return st;
-    if ((st = get_map(x, M, K, bn, &mb)) != FZ_OK) return st;
+    if ((st = get_map_bf16(w, N, K, BM, &ma)) != FZ_OK) return st;
+    if ((st = get_map_bf16(x, M, K, bn, &mb)) != FZ_OK) return st;
     dim3 grid(tiles, 1, p.splits);
     switch (bn) {
       case 16: return launch<16>(ma, mb, p, grid, stream);
@@ -473,8 +380,8 @@ FZ_API int fz_gemm_tc(const void* x, const void* w, const float* bias, void* c, 
   p.swap = 0;
   const int bn = N >= 256 ? 256 : N >= 128 ? 128 : 64;
   p.stages = pick_stages(bn);
-  if ((st = get_map(x, M, K, BM, &ma)) != FZ_OK) return st;
-  if ((st = get_map(w, N, K, bn, &mb)) != FZ_OK) return st;
+  if ((st = get_map_bf16(x, M, K, BM, &ma)) != FZ_OK) return st;
+  if ((st = get_map_bf16(w, N, K, bn, &mb)) != FZ_OK) return st;
   dim3 grid((M + BM - 1) / BM, (N + bn - 1) / bn, 1);
   if (grid.y > 65535) return FZ_TOO_LARGE;
   switch (bn) {

@@ -198,7 +198,7 @@ class CudaOps(Ops):
                     _p(q), _p(k), _p(v), _p(meta.pos), _p(meta.seq_row), _p(meta.seg), _p(table), c_int(table.shape[1]),
                     c_longlong(page_stride), c_int(cache.page_size), _p(out), _p(part_o), _p(part_ml), c_int(n),
                     c_int(hq), c_int(hkv), c_int(hd), c_float(scale), c_int(window), c_int(meta.max_context),
-                    c_int(LONG_PORTION), self._stream()), "paged_attention (decode)")
+                    c_int(LONG_PORTION), c_int(k.shape[0]), _p(self.err), self._stream()), "paged_attention (decode)")
                 self.launches += 1    # the combine kernel
             if meta.n_tiles > 0:
                 self._check(self.tc.fz_attn_prefill(
