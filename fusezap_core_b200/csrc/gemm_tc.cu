@@ -13,11 +13,12 @@
 //   warp 1  allocates the TMEM accumulator; one lane issues tcgen05.mma (128 x BN x 16, 4 per stage) and commits each
 //           stage's completion to its empty barrier, the last one to the accumulator-ready barrier;
 //   warps 2-5  read the accumulator with tcgen05.ld (each warp its own 32 lanes), add the bias and store.
-// Split K (chosen from N and K only, never from M): every split writes its float32 partial tile to a workspace, the
-// split that arrives last at the tile's counter adds all partials in split order 0, 1, 2, ... and stores the result, so
-// the sum has one fixed order whatever the arrival order (as the reference's split-K does: wgmma.py:209-239). No
-// device-side spin on other CTAs exists; waits on this CTA's own mbarriers are bounded by a time limit after which the
-// kernel sets an error bit and leaves.
+// Split K (swap mode; the count is chosen from N and K only, never from M): the splits of a tile form one thread-block
+// cluster. Each CTA leaves its float32 partial tile in its own shared memory; after a cluster barrier CTA r adds, for
+// the columns r, r + S, ..., the partials of all splits in split order 0, 1, 2, ... through distributed shared memory and
+// stores the result. The sum has one fixed order (as the reference's split-K has: wgmma.py:209-239) and no partial ever
+// goes to global memory. Waits on this CTA's own mbarriers are bounded by a time limit after which the kernel sets an
+// error bit and leaves; the cluster barriers are hardware barriers, not spins.
 #include "tma.cuh"
 
 namespace {
@@ -47,6 +48,23 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// The float at shared-memory address `addr` of the cluster's CTA `rank`
+__device__ __forceinline__ float ld_dsmem(uint32_t addr, uint32_t rank) {
+  uint32_t remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
 }
 // 16 consecutive float32 columns of this thread's TMEM lane
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
@@ -83,8 +101,6 @@ struct Params {
   float* c_f32;            // exactly one of c_f32 / c_bf16 is set
   __nv_bfloat16* c_bf16;
   const float* bias;       // over output features, may be null
-  float* partials;         // [tiles][splits][128][BN] float32, used when splits > 1
-  int* counters;           // [tiles], zero before the launch, zero again after it
   int* err;
   int rows;                // token rows (M of the product)
   int feats;               // output features (N of the product)
@@ -189,9 +205,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int b_limit = p.swap ? p.rows : p.feats;
     const int b0 = tile_b * BN;
     const uint32_t taddr = tmem_d + ((uint32_t)(quad * 32) << 16);
-    const int tile_id = tile_b * gridDim.x + tile_a;
     const bool direct = p.splits == 1;
-    float* part = p.partials ? p.partials + ((size_t)tile_id * p.splits + split) * BM * BN + (size_t)r * BN : nullptr;
+    float* part = (float*)smem + r;          // split K: partial tile as [column][row] in the (now idle) stage buffers
     float v[16];
     auto store16 = [&](const float* x, int c) {   // columns c..c+15 of this thread's row, final values
       if (a_row >= a_limit) return;
@@ -248,37 +263,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (direct) store16(v, c);
         else {
 #pragma unroll
-          for (int j = 0; j < 16; j += 4) *(float4*)(part + c + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+          for (int j = 0; j < 16; ++j) part[(c + j) * BM] = v[j];
         }
       }
     }
-    if (!direct) {
-      __threadfence();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (r == 0) {
-        const int old = atomicAdd(&p.counters[tile_id], 1);
-        flag[0] = (old == p.splits - 1) ? 1 : 0;
-        if (old == p.splits - 1) p.counters[tile_id] = 0;   // ready for the next launch
-      }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (flag[0]) {
-        __threadfence();
-        const float* base = p.partials + (size_t)tile_id * p.splits * BM * BN + (size_t)r * BN;
-        for (int c = 0; c < BN; c += 16) {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = 0.f;
-          for (int s = 0; s < p.splits; ++s) {      // fixed order: split 0, 1, 2, ...
-            const float* ps = base + (size_t)s * BM * BN + c;
-#pragma unroll
-            for (int j = 0; j < 16; j += 4) {
-              const float4 t = __ldcg((const float4*)(ps + j));
-              v[j] += t.x; v[j + 1] += t.y; v[j + 2] += t.z; v[j + 3] += t.w;
-            }
-          }
-          store16(v, c);
+  }
+  if (p.splits > 1) {
+    // every thread of every CTA of the cluster passes both barriers; only the epilogue warps work between them
+    cluster_sync_all();
+    if (warp >= 2) {
+      const int r = (warp & 3) * 32 + lane;
+      const int feat = tile_a * BM + r;
+      const uint32_t rank = cluster_rank();
+      const int cols = min(BN, p.rows - tile_b * BN);
+      const float bv = (p.bias && feat < p.feats) ? p.bias[feat] : 0.f;
+      const uint32_t base = smem_u32(smem) + (uint32_t)r * 4u;
+      for (int c = (int)rank; c < cols; c += p.splits) {
+        float acc = 0.f;
+        for (int sp = 0; sp < p.splits; ++sp) acc += ld_dsmem(base + (uint32_t)(c * BM) * 4u, (uint32_t)sp);   // split order
+        if (feat < p.feats) {
+          const int m = tile_b * BN + c;
+          const float y = acc + bv;
+          if (p.c_f32) p.c_f32[(size_t)m * p.feats + feat] = y;
+          else p.c_bf16[(size_t)m * p.feats + feat] = __float2bfloat16_rn(y);
         }
       }
     }
+    cluster_sync_all();    // nobody leaves while its shared memory may still be read
   }
   tc_fence_before();
   __syncthreads();
@@ -300,7 +311,29 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, dim3 g
     if (e != cudaSuccess) return (int)e;
     allowed = smem;
   }
-  fz_launch(gemm_tc_kernel<BN>, grid, dim3(NUM_THREADS), smem, stream, ma, mb, p);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (fz_pdl_enabled()) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  if (p.splits > 1) {      // the splits of one tile are one cluster (z dimension)
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = 1;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = (unsigned)p.splits;
+    ++na;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN>, ma, mb, p);
+  if (le != cudaSuccess) return (int)le;
   FZ_LAUNCH_CHECK();
   return FZ_OK;
 }
@@ -327,23 +360,13 @@ FZ_API int fz_gemm_tc_splits(int N, int K) {
   const int tiles = (N + BM - 1) / BM, kblocks = (K + BK - 1) / BK;
   int s = 296 / tiles;               // two CTAs on each of the 148 SMs
   if (s > kblocks / 4) s = kblocks / 4;
-  if (s > 16) s = 16;
+  if (s > 8) s = 8;                  // a portable cluster holds at most 8 CTAs
   return s < 1 ? 1 : s;
 }
 
-// Workspace needs of fz_gemm_tc for a product: bytes of float32 partials and number of int32 counters.
-FZ_API long long fz_gemm_tc_workspace(int M, int N, int K, long long* counters) {
-  const int tiles = (N + BM - 1) / BM;
-  const int splits = fz_gemm_tc_splits(N, K);
-  *counters = tiles;
-  return splits > 1 ? (long long)tiles * splits * BM * 128 * 4 : 0;
-}
-
 // x: [M, K] bf16, w: [N, K] bf16, bias: [N] float32 or null, c: [M, N] float32 (out_dtype 0) or bf16 (1).
-// partials / counters: workspace for split K (counters zeroed once at allocation); may be null, then K is not split.
 FZ_API int fz_gemm_tc(const void* x, const void* w, const float* bias, void* c, int out_dtype, int M, int N, int K,
-                      float* partials, long long partial_bytes, int* counters, int n_counters, int* err,
-                      cudaStream_t stream) {
+                      int* err, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return FZ_OK;
   int st = fz_gemm_tc_check(x, w, M, N, K);
   if (st != FZ_OK) return st;
@@ -352,7 +375,7 @@ FZ_API int fz_gemm_tc(const void* x, const void* w, const float* bias, void* c, 
   p.c_f32 = out_dtype == FZ_F32 ? (float*)c : nullptr;
   p.c_bf16 = out_dtype == FZ_BF16 ? (__nv_bfloat16*)c : nullptr;
   p.bias = bias; p.err = err; p.rows = M; p.feats = N; p.K = K;
-  p.partials = nullptr; p.counters = nullptr; p.splits = 1;
+  p.splits = 1;
   p.vec_ok = (N % 8 == 0 && ((uintptr_t)c & 15) == 0) ? 1 : 0;
   CUtensorMap ma, mb;
   if (M <= 128) {
@@ -361,11 +384,7 @@ FZ_API int fz_gemm_tc(const void* x, const void* w, const float* bias, void* c, 
     p.swap = 1;
     p.stages = pick_stages(bn);
     const int tiles = (N + BM - 1) / BM;
-    int splits = fz_gemm_tc_splits(N, K);
-    if (splits > 1 && partials && counters && n_counters >= tiles &&
-        partial_bytes >= (long long)tiles * splits * BM * bn * 4) {
-      p.splits = splits; p.partials = partials; p.counters = counters;
-    }
+    p.splits = fz_gemm_tc_splits(N, K);
     if ((st = get_map_bf16(w, N, K, BM, &ma)) != FZ_OK) return st;
     if ((st = get_map_bf16(x, M, K, bn, &mb)) != FZ_OK) return st;
     dim3 grid(tiles, 1, p.splits);

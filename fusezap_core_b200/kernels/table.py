@@ -47,12 +47,7 @@ class CudaOps(Ops):
         self._argmax_scratch = None
         self.tc = None
         if self.dtype == torch.bfloat16:
-            # tensor-core kernels and their split-K workspace: float32 partial tiles (at most 296 tiles x splits of
-            # 128 x 128) and one counter per tile, zeroed once (the kernel leaves them zero)
-            self.tc = load("fzb200_tc")
-            self.tc.fz_gemm_tc_workspace.restype = c_longlong
-            self._partials = torch.empty(296 * 128 * 128, dtype=torch.float32, device=self.device)
-            self._counters = torch.zeros(4096, dtype=torch.int32, device=self.device)
+            self.tc = load("fzb200_tc")      # tcgen05 / TMA kernels
         self.use_tensor_cores = self.tc is not None
         self._attn_scratch: torch.Tensor | None = None      # float32 partial outputs of the split decode attention
 
@@ -136,8 +131,7 @@ class CudaOps(Ops):
         if self.use_tensor_cores and self.tc.fz_gemm_tc_check(_p(a), _p(w), c_int(m), c_int(n), c_int(k)) == 0:
             self._check(self.tc.fz_gemm_tc(
                 _p(a), _p(w), _p(bias), _p(out), c_int(_CODE[out.dtype]), c_int(m), c_int(n), c_int(k),
-                _p(self._partials), c_longlong(self._partials.numel() * 4), _p(self._counters),
-                c_int(self._counters.numel()), _p(self.err), self._stream()), "linear (tensor cores)")
+                _p(self.err), self._stream()), "linear (tensor cores)")
             return
         self._check(self.core.fz_gemm_simt(_p(a), _p(w), _p(bias), _p(out), c_int(_CODE[a.dtype]),
                                            c_int(_CODE[out.dtype]), c_int(m), c_int(n), c_int(k), self._stream()),
