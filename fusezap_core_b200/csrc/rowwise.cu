@@ -484,3 +484,88 @@ FZ_API int fz_sample(const float* logits, const float* temperature, const double
 FZ_API int fz_clear_error(int* err, cudaStream_t stream) {
   return (int)cudaMemsetAsync(err, 0, sizeof(int), stream);
 }
+
+// ------------------------------------------------------------------------------------------------ argmax without allocation
+// See no_alloc.h. The scratch of the row-split argmax sits in this fixed device array. In host code the array's name is
+// only a stand-in for the symbol, not a device address, so the address is looked up once per device and passed to the
+// kernel as a pointer.
+#include "no_alloc.h"
+#include <mutex>
+#include <stdio.h>
+
+static __device__ __align__(256) unsigned char fz_no_alloc_scratch[FZ_NO_ALLOC_SCRATCH_BYTES];
+
+namespace {
+constexpr int NO_ALLOC_MAX_DEVICES = 64;
+void* g_no_alloc_ptr[NO_ALLOC_MAX_DEVICES] = {};
+std::mutex g_no_alloc_mu;
+thread_local char g_no_alloc_error[256] = "";
+
+// The scratch array's address on the current device (looked up at the first call on that device).
+int no_alloc_scratch(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) {
+    snprintf(g_no_alloc_error, sizeof g_no_alloc_error, "cudaGetDevice failed: %s", cudaGetErrorString(e));
+    return (int)e;
+  }
+  if (dev < 0 || dev >= NO_ALLOC_MAX_DEVICES) {
+    snprintf(g_no_alloc_error, sizeof g_no_alloc_error, "device ordinal %d is outside 0..%d", dev, NO_ALLOC_MAX_DEVICES - 1);
+    return FZ_TOO_LARGE;
+  }
+  std::lock_guard<std::mutex> lock(g_no_alloc_mu);
+  if (g_no_alloc_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, fz_no_alloc_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      snprintf(g_no_alloc_error, sizeof g_no_alloc_error, "cudaGetSymbolAddress failed on device %d: %s", dev,
+               cudaGetErrorString(e));
+      return e != cudaSuccess ? (int)e : FZ_BAD_ALIGNMENT;
+    }
+    g_no_alloc_ptr[dev] = p;
+  }
+  *out = g_no_alloc_ptr[dev];
+  return FZ_OK;
+}
+}  // namespace
+
+FZ_API const char* fz_no_alloc_last_error(void) { return g_no_alloc_error; }
+
+FZ_API int fz_argmax_no_alloc(const float* logits, int* out, int rows, int vocab, cudaStream_t stream) {
+  g_no_alloc_error[0] = 0;
+  if (rows <= 0) return FZ_OK;
+  if (vocab <= 0 || logits == nullptr || out == nullptr) {
+    snprintf(g_no_alloc_error, sizeof g_no_alloc_error, "bad arguments: rows %d, vocab %d, logits %p, out %p", rows, vocab,
+             (const void*)logits, (void*)out);
+    return FZ_BAD_SHAPE;
+  }
+  if (rows > FZ_NO_ALLOC_MAX_ROWS) {
+    snprintf(g_no_alloc_error, sizeof g_no_alloc_error,
+             "%d rows exceed the fixed scratch of this entry point (at most %d rows per call); split the call", rows,
+             FZ_NO_ALLOC_MAX_ROWS);
+    return FZ_TOO_LARGE;
+  }
+  void* base = nullptr;
+  const int st = no_alloc_scratch(&base);
+  if (st != FZ_OK) return st;
+  // [partial values: MAX_ROWS x MAX_SLICES float][partial indices: the same in int][counters: MAX_ROWS int]
+  float* partial_val = (float*)base;
+  int* partial_idx = (int*)((unsigned char*)base + (size_t)FZ_NO_ALLOC_MAX_ROWS * FZ_NO_ALLOC_MAX_SLICES * 4);
+  int* counters = (int*)((unsigned char*)base + (size_t)FZ_NO_ALLOC_MAX_ROWS * FZ_NO_ALLOC_MAX_SLICES * 8);
+  // the counters must start at zero whatever an earlier call left behind
+  cudaError_t e = cudaMemsetAsync(counters, 0, (size_t)rows * sizeof(int), stream);
+  if (e != cudaSuccess) {
+    snprintf(g_no_alloc_error, sizeof g_no_alloc_error, "clearing the counters failed: %s", cudaGetErrorString(e));
+    return (int)e;
+  }
+  const int slices = fz_argmax_slices(vocab);     // at most FZ_NO_ALLOC_MAX_SLICES
+  dim3 grid(rows, slices);
+  // launched without the dependent-launch attribute: the memset above must be complete before the kernel starts
+  argmax_kernel<<<grid, 512, 0, stream>>>(logits, out, vocab, partial_val, partial_idx, counters);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    snprintf(g_no_alloc_error, sizeof g_no_alloc_error, "the launch failed: %s", cudaGetErrorString(e));
+    return (int)e;
+  }
+  return FZ_OK;
+}
