@@ -167,7 +167,7 @@ def main() -> int:
         seqs = [eng.seqs[r] for r in rids]
         bucket = next(b for b in eng._buckets if b >= batch)
         def one_step(i: int):
-            portions = [Portion(s.seq_id, [s.tokens[s.num_computed]], [0]) for s in seqs]
+            portions = [Portion(s.seq_id, [s.token_at(s.num_computed)], [0]) for s in seqs]
             starts = runner.prepare(portions, pad_rows=bucket, pad_wanted=bucket)
             eng._graphs[(bucket, True)].replay()
             runner.commit(portions, starts)

@@ -18,6 +18,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Any, Hashable
 
+import numpy as np
 import torch
 
 from .allocator import OutOfPages, PageAllocator
@@ -37,12 +38,21 @@ class KVGroup:
     page_size: int
     num_pages: int
     slots: list[int]                              # cache slot ids that live in this group
+    max_pages_per_request: int = 0
     pool: torch.Tensor | None = None              # (len(slots), num_pages, 2, Hkv, page_size, hd)
     allocator: PageAllocator = field(init=False)
-    tables: dict[Hashable, list[int]] = field(default_factory=dict)   # request -> page id per page index (-1: given back / not yet)
+    # request -> int32 row of page ids by page index (-1: given back, or not yet there) and how many entries are in use.
+    # Entries below the first live page are -1; every entry from there to `lens[req]` holds a page.
+    rows: dict[Hashable, np.ndarray] = field(default_factory=dict)
+    lens: dict[Hashable, int] = field(default_factory=dict)
 
     def __post_init__(self) -> None:
         self.allocator = PageAllocator(self.num_pages)
+
+    @property
+    def tables(self) -> dict[Hashable, list[int]]:
+        """The block tables as plain lists (for inspection and tests)."""
+        return {r: self.rows[r][: self.lens[r]].tolist() for r in self.rows}
 
     def first_live_page(self, computed: int) -> int:
         """Index of the first page a query at position `computed` can still see."""
@@ -51,35 +61,42 @@ class KVGroup:
         return max(0, computed - self.need.window + 1) // self.page_size
 
     def pages_needed(self, req: Hashable, computed: int, n_tokens: int) -> int:
-        t = self.tables.get(req, ())
+        have = self.lens.get(req, 0)
         lo, hi = self.first_live_page(computed), -(-n_tokens // self.page_size)
-        return sum(1 for i in range(lo, hi) if i >= len(t) or t[i] < 0)
+        return max(0, hi - max(lo, have))      # everything between the first live page and `have` is already there
 
     def ensure(self, req: Hashable, computed: int, n_tokens: int) -> None:
-        t = self.tables.setdefault(req, [])
         lo, hi = self.first_live_page(computed), -(-n_tokens // self.page_size)
-        want = [i for i in range(lo, hi) if i >= len(t) or t[i] < 0]
-        pages = self.allocator.allocate(len(want))
-        while len(t) < hi:
-            t.append(-1)
-        for i, p in zip(want, pages):
-            t[i] = p
+        have = self.lens.get(req, 0)
+        first = max(lo, have)
+        if hi <= first and req in self.rows:
+            return
+        row = self.rows.get(req)
+        if row is None or hi > row.shape[0]:
+            grown = np.full(max(hi, self.max_pages_per_request, 1), -1, dtype=np.int32)
+            if row is not None:
+                grown[: row.shape[0]] = row
+            row = self.rows[req] = grown
+        if hi > first:
+            row[first:hi] = self.allocator.allocate(hi - first)
+        self.lens[req] = max(have, hi)
 
     def release_before(self, req: Hashable, computed: int) -> None:
-        t = self.tables.get(req)
-        if not t or not self.need.window:
+        if not self.need.window or req not in self.rows:
             return
-        lo = min(self.first_live_page(computed), len(t))
-        gone = [p for p in t[:lo] if p >= 0]
-        if gone:
-            self.allocator.free(gone)
-            for i in range(lo):
-                t[i] = -1
+        row, lo = self.rows[req], min(self.first_live_page(computed), self.lens[req])
+        head = row[:lo]
+        gone = head[head >= 0]
+        if gone.size:
+            self.allocator.free(gone.tolist())
+            head[:] = -1
 
     def free(self, req: Hashable) -> None:
-        t = self.tables.pop(req, None)
-        if t:
-            self.allocator.free([p for p in t if p >= 0])
+        row = self.rows.pop(req, None)
+        n = self.lens.pop(req, 0)
+        if row is not None:
+            held = row[:n]
+            self.allocator.free(held[held >= 0].tolist())
 
     def view(self, slot: int) -> tuple[torch.Tensor, torch.Tensor]:
         """(keys, values) of one cache slot, each (num_pages, Hkv, page_size, hd) strided views of the pool."""
@@ -131,7 +148,8 @@ class CacheManager:
         by_need: dict[KVNeed, list[int]] = {}
         for slot, need in sorted(needs.items()):
             by_need.setdefault(need, []).append(slot)
-        self.groups: list[KVGroup] = [KVGroup(need, page_size, num_pages, slots) for need, slots in by_need.items()]
+        self.groups: list[KVGroup] = [KVGroup(need, page_size, num_pages, slots, self.max_pages_per_request)
+                                      for need, slots in by_need.items()]
         self.slot_group: dict[int, int] = {s: g for g, grp in enumerate(self.groups) for s in grp.slots}
         self.computed: dict[Hashable, int] = {}
         self.states = StateSlots(max_requests)
@@ -204,7 +222,13 @@ class CacheManager:
 
     # ---- views for the step function
     def table(self, group: int, req: Hashable) -> list[int]:
-        return self.groups[group].tables.get(req, [])
+        g = self.groups[group]
+        return g.rows[req][: g.lens[req]].tolist() if req in g.rows else []
+
+    def table_row(self, group: int, req: Hashable) -> tuple[np.ndarray | None, int]:
+        """(int32 row of page ids, entries in use) without copying; (None, 0) for a request that holds nothing."""
+        g = self.groups[group]
+        return g.rows.get(req), g.lens.get(req, 0)
 
     def state_slot(self, req: Hashable) -> int:
         return self.states.owner.get(req, -1)
@@ -215,6 +239,7 @@ class CacheManager:
             g.allocator.check()
             seen: set[int] = set()
             for req, t in g.tables.items():
+                assert all(p >= 0 for p in t[g.first_live_page(self.computed.get(req, 0)):]), f"{req!r} lacks a live page"
                 for p in t:
                     if p >= 0:
                         assert p not in seen, f"page {p} is in two block tables"

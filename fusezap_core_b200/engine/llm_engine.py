@@ -142,10 +142,10 @@ class LLMEngine:
     def _portions(self, so: SchedulerOutput) -> tuple[list[Portion], list[Sequence]]:
         portions, owners = [], []
         for seq in so.decode:
-            portions.append(Portion(seq.seq_id, [seq.tokens[seq.num_computed]], [0]))
+            portions.append(Portion(seq.seq_id, [seq.token_at(seq.num_computed)], [0]))
             owners.append(seq)
         for seq, start, n in so.prefill:
-            toks = seq.tokens[start:start + n]
+            toks = seq.tokens_between(start, start + n)
             portions.append(Portion(seq.seq_id, toks, [n - 1] if start + n == seq.num_tokens else []))
             owners.append(seq)
         return portions, owners
@@ -197,11 +197,13 @@ class LLMEngine:
         ids = None
         if n_w:
             self._ids_h[:n_w].copy_(self._ids_d[:n_w], non_blocking=True)
-            if self.model.device.type == "cuda":
-                torch.cuda.current_stream(self.model.device).synchronize()
+        ops.errors_to_host()
+        if self.model.device.type == "cuda":
+            torch.cuda.current_stream(self.model.device).synchronize()
+        if n_w:
             ids = self._ids_h[:n_w].numpy()
-            self.stats["d2h_bytes"] += n_w * 4
-        ops.check_errors()
+        self.stats["d2h_bytes"] += n_w * 4 + 4
+        ops.check_errors(copied=True)
         return ids, logits
 
     def _eager(self, n_wanted: int) -> torch.Tensor:

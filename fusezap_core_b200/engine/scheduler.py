@@ -56,6 +56,18 @@ class Sequence:
     def num_tokens(self) -> int:
         return len(self.prompt) + len(self.output)
 
+    def token_at(self, i: int) -> int:
+        n = len(self.prompt)
+        return self.prompt[i] if i < n else self.output[i - n]
+
+    def tokens_between(self, lo: int, hi: int) -> list[int]:
+        n = len(self.prompt)
+        if hi <= n:
+            return self.prompt[lo:hi]
+        if lo >= n:
+            return self.output[lo - n: hi - n]
+        return self.prompt[lo:] + self.output[: hi - n]
+
     @property
     def num_pending(self) -> int:
         return self.num_tokens - self.num_computed

@@ -157,10 +157,10 @@ class StepMeta:
         for g in range(self.num_groups):
             t = a[self.o_tab + g * self.max_segments * self.mb: self.o_tab + (g + 1) * self.max_segments * self.mb]
             t = t.reshape(self.max_segments, self.mb)
-            t[:len(portions)] = -1
             for s, p in enumerate(portions):
-                pages = cache.table(g, p.req)
-                t[s, :len(pages)] = pages
+                row, used = cache.table_row(g, p.req)
+                t[s, :used] = row[:used]
+                t[s, used:] = -1
         # 64-row tiles of the portions with at least LONG_PORTION tokens, the ones that see the most keys first
         tl = [(sg.pos0 + min(r + TILE_ROWS, sg.n), sg.seq_row, r) for sg in self.segments if sg.n >= LONG_PORTION
               for r in range(0, sg.n, TILE_ROWS)]

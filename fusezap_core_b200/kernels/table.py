@@ -43,6 +43,7 @@ class CudaOps(Ops):
             raise KernelError("no CUDA device is available; this engine has no CPU path")
         self.core = load("fzb200_core")
         self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._err_host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
         self.launches = 0
         self._argmax_scratch = None
         self.tc = None
@@ -71,9 +72,14 @@ class CudaOps(Ops):
         if dims is not None and t.dim() != dims:
             raise KernelError(f"{name} has {t.dim()} dimensions, expected {dims}")
 
-    def check_errors(self) -> None:
-        """Waits for the device, then raises if any kernel since the last check flagged bad data."""
-        word = int(self.err.item())
+    def errors_to_host(self) -> None:
+        """Enqueues the copy of the error word to pinned memory on the current stream; after the caller's own
+        synchronisation `check_errors(copied=True)` reads it without another round trip."""
+        self._err_host.copy_(self.err, non_blocking=True)
+
+    def check_errors(self, copied: bool = False) -> None:
+        """Raises if any kernel since the last check flagged bad data. copied=False waits for the device first."""
+        word = int(self._err_host[0]) if copied else int(self.err.item())
         if word:
             self.err.zero_()
             raise KernelError("a kernel reported: " + "; ".join(m for b, m in _DEVICE_ERRORS.items() if word & b))

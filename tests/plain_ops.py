@@ -113,5 +113,8 @@ class PlainOps:
             res[r] = int(np.searchsorted(c, float(uniform[r]) * c[-1], side="right").clip(0, len(c) - 1))
         out.copy_(torch.from_numpy(res))
 
-    def check_errors(self) -> None:
+    def errors_to_host(self) -> None:
+        pass
+
+    def check_errors(self, copied: bool = False) -> None:
         pass
