@@ -1,7 +1,7 @@
 // Causal flash attention for prompt portions over the paged bf16 cache, on tensor cores.
 //
-// grid (tiles, query heads), 128 threads. A tile is 64 consecutive token rows of one portion (the host lists the
-// tiles, the ones with the most keys first); warp w owns rows 16 w .. 16 w + 15. The keys of the portion's request,
+// grid (tiles, query heads, 2), 128 threads. The host lists tiles of 128 consecutive token rows of one portion (the ones
+// with the most keys first); a CTA serves one 64-row half of a tile, warp w owns rows 16 w .. 16 w + 15 of it. The keys of the portion's request,
 // from the start of the window (or 0) to the tile's last row's own position, come from the pages in tiles of 64
 // through a two-stage cp.async ring; S = Q K^T and O += P V run on mma.sync m16n8k16 with float32 accumulators,
 // softmax is online in the exp2 domain with float32 max and sum, and P is rounded to bf16 for the second product (as
@@ -30,10 +30,12 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   const uint32_t s_q = s_base + 4 * TILE_BYTES;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int s_idx = tiles[2 * blockIdx.x], r_off = tiles[2 * blockIdx.x + 1];
+  // the host lists 128-row tiles; blockIdx.z picks the 64-row half this CTA serves
+  const int s_idx = tiles[2 * blockIdx.x], r_off = tiles[2 * blockIdx.x + 1] + BM * (int)blockIdx.z;
   if (s_idx < 0) return;
   const int h = blockIdx.y, kvh = h / (Hq / Hkv);
   const int row0 = seg[4 * s_idx], n_rows = seg[4 * s_idx + 1], pos0 = seg[4 * s_idx + 2];
+  if (r_off >= n_rows) return;
   const int valid_rows = min(BM, n_rows - r_off);
   const int qpos0 = pos0 + r_off;                               // position of the tile's first row
   const int last_pos = qpos0 + valid_rows - 1;
@@ -180,7 +182,7 @@ int launch(const void* q, const void* k_pool, const void* v_pool, const int* seg
     if (e != cudaSuccess) return (int)e;
     raised = true;
   }
-  dim3 grid(n_tiles, Hq);
+  dim3 grid(n_tiles, Hq, 2);
   fz_launch(attn_prefill_kernel<HD>, grid, dim3(THREADS), smem, stream, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
             (const __nv_bfloat16*)v_pool, seg, tiles, table, mb, page_stride, page_size, (__nv_bfloat16*)out, Hq, Hkv,
             scale * 1.4426950408889634f, window);
@@ -195,7 +197,7 @@ FZ_API int fz_attn_prefill_check(int Hq, int Hkv, int hd) {
   return FZ_OK;
 }
 
-// tiles: int32 [n_tiles][2] = (segment index or -1, first row of the tile within the portion).
+// tiles: int32 [n_tiles][2] = (segment index or -1, first row of the 128-row tile within the portion).
 FZ_API int fz_attn_prefill(const void* q, const void* k_pool, const void* v_pool, const int* seg, const int* tiles,
                            int n_tiles, const int* table, int mb, long long page_stride, int page_size, void* out,
                            int Hq, int Hkv, int hd, float scale, int window, cudaStream_t stream) {

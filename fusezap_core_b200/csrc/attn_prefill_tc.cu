@@ -1,0 +1,382 @@
+// Causal flash attention for prompt portions over the paged bf16 cache on the 5th-generation tensor cores.
+//
+// grid (tiles, query heads), 192 threads, one CTA per SM. A tile is 128 consecutive token rows of one portion (the host
+// lists the tiles, the ones with the most keys first); the 128 rows are the 128 TMEM lanes. Keys come in tiles of 128:
+//   warp 0      TMA producer: the Q tile once; per key tile the pages' boxes of K and V (a page's rows of one kv head are
+//               one box of the pool seen as a 2-D array of rows; 128-byte swizzle) into a two-stage ring;
+//   warp 1      one lane issues tcgen05.mma: S = Q K^T (128 x 128 x hd, both operands K-major) into TMEM, and, once the
+//               softmax warps have written P, PV = P V (128 x hd x 128; V is the MN-major operand, as TMA delivers it);
+//   warps 2..5  one thread per row: read the row's scores from TMEM, scale, mask (causal by position, window), online
+//               softmax in the exp2 domain with float32 max and sum, write P as bf16 into shared memory in the swizzled
+//               K-major layout, then read PV from TMEM and fold it into the row's float32 output registers with the
+//               rescale factor; at the end normalise and store the row.
+// Key tiles start at multiples of 128 in absolute position, so a row's sums do not depend on how the prompt was cut.
+// Waits on the CTA's own mbarriers are bounded; a wait that gives up sets the error bit. No multicast.
+// (The reference's paged prefill kernel is an mma.sync kernel with 64-row tiles: fusezap/device/cuda_kernels/
+// attention.py:255-326; `attn_prefill.cu` here is its counterpart and serves the page sizes this kernel refuses.)
+#include "tma.cuh"
+#include <math.h>
+
+namespace {
+using namespace fztma;
+
+constexpr int BM = 128, BN = 128, NUM_THREADS = 192, KV_STAGES = 2;
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// 32 consecutive float32 columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// K-major operand tile, rows of 128 bytes, 8-row groups 1024 bytes apart, 128-byte swizzle (as in gemm_tc.cu).
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// MN-major operand (V as TMA delivers it: one row of 128 bytes per key, 64 head-dim columns per row). Along K (keys)
+// rows are 128 bytes apart and 8-row groups 1024 bytes apart (stride offset); along MN the next 64 columns are
+// `mn_stride` bytes further (leading offset). 128-byte swizzle.
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr, uint32_t mn_stride) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)((mn_stride >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// D float32, A and B bf16; `b_mn` sets B MN-major (bit 16).
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n, bool b_mn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn ? (1u << 16) : 0u) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+template <int HD, int BOX>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map,
+                       const int* __restrict__ seg, const int* __restrict__ tiles, const int* __restrict__ table, int mb,
+                       int page_size, __nv_bfloat16* __restrict__ out, int Hq, int Hkv, float scale_log2, int window,
+                       int* err) {
+  constexpr int HALVES = HD / 64;                     // 64-column halves of a head
+  constexpr int HALF_BYTES = 128 * 128;               // 128 rows of 128 bytes
+  constexpr int Q_BYTES = HALVES * HALF_BYTES, KV_BYTES = HALVES * HALF_BYTES, P_BYTES = (BN / 64) * HALF_BYTES;
+  constexpr int STAGE_BYTES = 2 * KV_BYTES;           // K then V
+  constexpr int TMEM_COLS = 256;                      // S: columns 0..127, PV: columns 128..128+HD
+  constexpr int OPS = (BN / BOX) * 2 * HALVES;        // TMA boxes per key tile
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t s_q = smem_u32(smem), s_kv = s_q + Q_BYTES, s_p = s_kv + KV_STAGES * STAGE_BYTES;
+  uint64_t* bars = (uint64_t*)(smem + Q_BYTES + KV_STAGES * STAGE_BYTES + P_BYTES);
+  uint64_t* q_full = bars;                 // 1
+  uint64_t* kv_full = bars + 1;            // KV_STAGES
+  uint64_t* kv_empty = kv_full + KV_STAGES;
+  uint64_t* s_ready = kv_empty + KV_STAGES;
+  uint64_t* p_ready = s_ready + 1;
+  uint64_t* pv_ready = p_ready + 1;
+  uint32_t* tmem_slot = (uint32_t*)(pv_ready + 1);
+  int* flag = (int*)(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < KV_STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    mbar_init(s_ready, 1);
+    mbar_init(p_ready, 128);
+    mbar_init(pv_ready, 1);
+    flag[0] = 0;
+    mbar_init_fence();
+  }
+  // zeros in the key / value stages: a box that is not fetched (keys past the portion's last position) must not hold
+  // another block's bits, since P = 0 times NaN is NaN
+  for (int e = tid; e < KV_STAGES * STAGE_BYTES / 16; e += NUM_THREADS) ((uint4*)(smem + Q_BYTES))[e] = make_uint4(0u, 0u, 0u, 0u);
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  fz_grid_wait();
+  fz_grid_launch_dependents();
+
+  const int s_idx = tiles[2 * blockIdx.x], r_off = tiles[2 * blockIdx.x + 1];
+  const int h = blockIdx.y, kvh = h / (Hq / Hkv);
+  int n_key_tiles = 0, row0 = 0, valid_rows = 0, qpos0 = 0, last_pos = 0, lo_tile = 0, k_begin = 0;
+  if (s_idx >= 0) {
+    row0 = seg[4 * s_idx];
+    const int n_rows = seg[4 * s_idx + 1], pos0 = seg[4 * s_idx + 2];
+    valid_rows = min(BM, n_rows - r_off);
+    qpos0 = pos0 + r_off;
+    last_pos = qpos0 + valid_rows - 1;
+    lo_tile = window > 0 ? max(0, qpos0 - window + 1) : 0;
+    k_begin = lo_tile & ~(BN - 1);
+    n_key_tiles = (last_pos - k_begin) / BN + 1;
+  }
+
+  if (warp == 0) {
+    // ---------------- TMA producer
+    if (n_key_tiles > 0) {
+      if (lane == 0) {
+        mbar_expect_tx(q_full, Q_BYTES);
+#pragma unroll
+        for (int hf = 0; hf < HALVES; ++hf) tma_load_2d_u32(s_q + hf * HALF_BYTES, &q_map, smem_u32(q_full), h * HD + 64 * hf, row0 + r_off);
+      }
+      const int* trow = table + (size_t)s_idx * mb;
+      const int rows_per_page = 2 * Hkv * page_size;
+      bool ok = true;
+      for (int t = 0; t < n_key_tiles && ok; ++t) {
+        const int s = t % KV_STAGES, round = t / KV_STAGES;
+        if (round > 0) ok = __all_sync(0xffffffffu, mbar_wait(&kv_empty[s], (round - 1) & 1));
+        if (!ok) { if (lane == 0) flag[0] = 1; break; }
+        const int key0 = k_begin + t * BN;
+        // op -> (page box, K or V, column half); a box is fetched if any of its keys lies in [lo_tile, last_pos]
+        int op_row[(OPS + 31) / 32];
+        uint32_t bytes = 0;
+#pragma unroll
+        for (int i = 0; i < (OPS + 31) / 32; ++i) {
+          const int op = lane + 32 * i;
+          op_row[i] = -1;
+          if (op < OPS) {
+            const int box = op / (2 * HALVES);
+            const int key = key0 + box * BOX;
+            if (key <= last_pos && key + BOX - 1 >= lo_tile) {
+              const int pi = key / page_size;
+              const int page = trow[pi];
+              if (page >= 0) op_row[i] = page * rows_per_page + kvh * page_size + (key - pi * page_size);
+              else atomicOr(err, FZ_ERR_NO_PAGE);
+            }
+          }
+          bytes += op_row[i] >= 0 ? BOX * 128u : 0u;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) bytes += __shfl_xor_sync(0xffffffffu, bytes, o);
+        if (lane == 0) mbar_expect_tx(&kv_full[s], bytes);
+        __syncwarp();
+        const uint32_t sk = s_kv + s * STAGE_BYTES, bar = smem_u32(&kv_full[s]);
+#pragma unroll
+        for (int i = 0; i < (OPS + 31) / 32; ++i) {
+          const int op = lane + 32 * i;
+          if (op < OPS && op_row[i] >= 0) {
+            const int box = op / (2 * HALVES), rest = op % (2 * HALVES), is_v = rest / HALVES, hf = rest % HALVES;
+            tma_load_2d_u32(sk + is_v * KV_BYTES + hf * HALF_BYTES + box * BOX * 128, &kv_map, bar, 64 * hf,
+                            op_row[i] + is_v * Hkv * page_size);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer
+    if (lane == 0 && n_key_tiles > 0) {
+      constexpr uint32_t idesc_s = make_idesc(BM, BN, false), idesc_pv = make_idesc(BM, HD, true);
+      const uint32_t tmem_s = tmem_base, tmem_pv = tmem_base + 128;
+      bool ok = mbar_wait(q_full, 0);
+      for (int t = 0; t < n_key_tiles && ok; ++t) {
+        const int s = t % KV_STAGES;
+        if (!mbar_wait(&kv_full[s], (t / KV_STAGES) & 1)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t sk = s_kv + s * STAGE_BYTES, sv = sk + KV_BYTES;
+        // S = Q K^T over hd = HALVES x 64
+#pragma unroll
+        for (int hf = 0; hf < HALVES; ++hf) {
+          const uint64_t dq = desc_k_major(s_q + hf * HALF_BYTES), dk = desc_k_major(sk + hf * HALF_BYTES);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) umma_bf16(tmem_s, dq + (uint64_t)(2 * k), dk + (uint64_t)(2 * k), idesc_s, (hf | k) ? 1u : 0u);
+        }
+        umma_commit(s_ready);
+        if (!mbar_wait(p_ready, t & 1)) { ok = false; break; }
+        tc_fence_after();
+        // PV = P V over the tile's 128 keys, 16 per instruction
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk) {
+          const uint64_t dp = desc_k_major(s_p + (kk >> 2) * HALF_BYTES) + (uint64_t)(2 * (kk & 3));
+          const uint64_t dv = desc_mn_major(sv + kk * 16 * 128, HALF_BYTES);
+          umma_bf16(tmem_pv, dp, dv, idesc_pv, kk ? 1u : 0u);
+        }
+        umma_commit(pv_ready);
+        umma_commit(&kv_empty[s]);
+      }
+      if (!ok) flag[0] = 1;
+    }
+  } else {
+    // ---------------- softmax and output: one thread per row
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const uint32_t lane_sel = (uint32_t)(quad * 32) << 16;
+    const uint32_t t_s = tmem_base + lane_sel, t_pv = tmem_base + 128 + lane_sel;
+    const int qpos = qpos0 + r;
+    float o[HD];
+#pragma unroll
+    for (int i = 0; i < HD; ++i) o[i] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    for (int t = 0; t < n_key_tiles && ok; ++t) {
+      ok = __all_sync(0xffffffffu, mbar_wait(s_ready, t & 1));
+      if (!ok) break;
+      tc_fence_after();
+      const int key0 = k_begin + t * BN;
+      const int lo_key = window > 0 ? max(lo_tile, qpos - window + 1) : lo_tile;
+      float v[32];
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        tmem_ld32(t_s + (uint32_t)c, v);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int key = key0 + c + i;
+          if (key <= qpos && key >= lo_key) mx = fmaxf(mx, v[i]);
+        }
+      }
+      const float mn = fmaxf(m_run, mx * scale_log2);
+      const float mu = mn == -INFINITY ? 0.f : mn;
+      const float corr = exp2f(m_run - mu);
+      m_run = mn;
+      float sum = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        tmem_ld32(t_s + (uint32_t)c, v);
+        uint32_t w[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const int key = key0 + c + i;
+          const float e0 = (key <= qpos && key >= lo_key) ? exp2f(v[i] * scale_log2 - mu) : 0.f;
+          const float e1 = (key + 1 <= qpos && key + 1 >= lo_key) ? exp2f(v[i + 1] * scale_log2 - mu) : 0.f;
+          sum += e0 + e1;
+          const __nv_bfloat162 pk = __floats2bfloat162_rn(e0, e1);
+          w[i >> 1] = *(const uint32_t*)&pk;
+        }
+        // columns c..c+31 of row r: column half c / 64, 16-byte chunks (c % 64) / 8 .. + 3, swizzled by the row
+        const uint32_t base = s_p + (c >> 6) * HALF_BYTES + r * 128;
+        const int ch = (c & 63) >> 3;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint32_t addr = base + (((ch + j) ^ (r & 7)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[4 * j]), "r"(w[4 * j + 1]), "r"(w[4 * j + 2]), "r"(w[4 * j + 3]) : "memory");
+        }
+      }
+      l_run = l_run * corr + sum;
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor core (async proxy)
+      tc_fence_before();
+      mbar_arrive(p_ready);
+      ok = __all_sync(0xffffffffu, mbar_wait(pv_ready, t & 1));
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < HD; c += 32) {
+        tmem_ld32(t_pv + (uint32_t)c, v);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[c + i] = fmaf(o[c + i], corr, v[i]);
+      }
+      tc_fence_before();
+    }
+    if (!ok) flag[0] = 1;
+    if (ok && n_key_tiles > 0 && r < valid_rows) {
+      const float inv = 1.0f / l_run;
+      __nv_bfloat16* orow = out + (size_t)(row0 + r_off + r) * Hq * HD + (size_t)h * HD;
+#pragma unroll
+      for (int c = 0; c < HD; c += 8) {
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const __nv_bfloat162 pk = __floats2bfloat162_rn(o[c + 2 * j] * inv, o[c + 2 * j + 1] * inv);
+          w[j] = *(const uint32_t*)&pk;
+        }
+        *(uint4*)(orow + c) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  if (tid == 0 && flag[0]) atomicOr(err, FZ_ERR_WAIT_TIMEOUT);
+}
+
+template <int HD, int BOX>
+int launch(const void* q, int N, const void* k_pool, long long pool_rows, const int* seg, const int* tiles, int n_tiles,
+           const int* table, int mb, int page_size, void* out, int Hq, int Hkv, float scale, int window, int* err,
+           cudaStream_t stream) {
+  CUtensorMap qm, kvm;
+  int st = get_map_bf16(q, N, Hq * HD, BM, &qm);
+  if (st != FZ_OK) return st;
+  if ((st = get_map_bf16(k_pool, pool_rows, HD, BOX, &kvm)) != FZ_OK) return st;
+  constexpr int HALVES = HD / 64, HALF_BYTES = 128 * 128;
+  constexpr size_t smem = (size_t)HALVES * HALF_BYTES + KV_STAGES * 2 * HALVES * HALF_BYTES + (BN / 64) * HALF_BYTES + 8 * 16 + 1024;
+  static bool raised = false;
+  if (!raised) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD, BOX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    raised = true;
+  }
+  dim3 grid(n_tiles, Hq);
+  fz_launch(attn_prefill_tc_kernel<HD, BOX>, grid, dim3(NUM_THREADS), smem, stream, qm, kvm, seg, tiles, table, mb, page_size,
+            (__nv_bfloat16*)out, Hq, Hkv, scale * 1.4426950408889634f, window, err);
+  FZ_LAUNCH_CHECK();
+  return FZ_OK;
+}
+}  // namespace
+
+// Takes head sizes 64 and 128 and page sizes 8, 16 and multiples of 16, with the pool laid out as (pages, 2, Hkv,
+// page_size, hd); anything else is refused and the mma.sync kernel runs instead.
+FZ_API int fz_attn_prefill_tc_check(int Hq, int Hkv, int hd, int page_size) {
+  if (Hq <= 0 || Hkv <= 0 || Hq % Hkv) return FZ_BAD_SHAPE;
+  if (hd != 64 && hd != 128) return FZ_BAD_SHAPE;
+  if (!(page_size == 8 || (page_size > 0 && page_size % 16 == 0))) return FZ_BAD_SHAPE;
+  return FZ_OK;
+}
+
+// tiles: int32 [n_tiles][2] = (portion index or -1, first row of the 128-row tile within the portion). q: [N, Hq * hd].
+FZ_API int fz_attn_prefill_tc(const void* q, int N, const void* k_pool, const void* v_pool, long long page_stride,
+                              int num_pages, const int* seg, const int* tiles, int n_tiles, const int* table, int mb,
+                              int page_size, void* out, int Hq, int Hkv, int hd, float scale, int window, int* err,
+                              cudaStream_t stream) {
+  if (n_tiles <= 0) return FZ_OK;
+  if (fz_attn_prefill_tc_check(Hq, Hkv, hd, page_size) != FZ_OK || Hq > 65535) return FZ_BAD_SHAPE;
+  if (page_stride != 2LL * Hkv * page_size * hd ||
+      (const __nv_bfloat16*)v_pool != (const __nv_bfloat16*)k_pool + (long long)Hkv * page_size * hd)
+    return FZ_BAD_SHAPE;
+  if ((((uintptr_t)q) | ((uintptr_t)k_pool) | ((uintptr_t)out)) & 15) return FZ_BAD_ALIGNMENT;
+  const long long pool_rows = (long long)num_pages * 2 * Hkv * page_size;
+#define FZ_T(HD_, BOX_) return launch<HD_, BOX_>(q, N, k_pool, pool_rows, seg, tiles, n_tiles, table, mb, page_size, out, Hq, Hkv, scale, window, err, stream)
+  if (hd == 64 && page_size == 8) FZ_T(64, 8);
+  if (hd == 64) FZ_T(64, 16);
+  if (page_size == 8) FZ_T(128, 8);
+  FZ_T(128, 16);
+#undef FZ_T
+}

@@ -24,7 +24,7 @@ from .model import DecoderModel
 
 
 LONG_PORTION = 8    # portions of at least this many tokens go to the tile (prefill) attention kernel
-TILE_ROWS = 64      # token rows per tile of that kernel
+TILE_ROWS = 128     # token rows per tile of that kernel
 
 
 @dataclass
@@ -95,7 +95,7 @@ class StepMeta:
         self.segments: list[Segment] = []
         self.max_context = 0      # the longest context (position + 1) among the step's rows
         self.max_portion = 0      # the longest portion
-        self.n_tiles = 0          # 64-row tiles of the long portions (tile kernels); the other rows are "short"
+        self.n_tiles = 0          # TILE_ROWS-row tiles of the long portions (tile kernels); the other rows are "short"
         self.n_short_rows = 0     # rows of short portions, padding rows included
 
     # device views (static addresses; sliced to the step's sizes)
@@ -161,7 +161,7 @@ class StepMeta:
                 row, used = cache.table_row(g, p.req)
                 t[s, :used] = row[:used]
                 t[s, used:] = -1
-        # 64-row tiles of the portions with at least LONG_PORTION tokens, the ones that see the most keys first
+        # TILE_ROWS-row tiles of the portions with at least LONG_PORTION tokens, the ones that see the most keys first
         tl = [(sg.pos0 + min(r + TILE_ROWS, sg.n), sg.seq_row, r) for sg in self.segments if sg.n >= LONG_PORTION
               for r in range(0, sg.n, TILE_ROWS)]
         tl.sort(key=lambda x: -x[0])

@@ -22,9 +22,9 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 LIBRARIES: dict[str, list[str]] = {
     "fzb200_core": ["rowwise.cu", "gemm_simt.cu", "attn_simt.cu"],
-    "fzb200_tc": ["gemm_tc.cu", "attn_decode.cu", "attn_prefill.cu"],          # bfloat16 only: tcgen05 / TMA kernels
+    "fzb200_tc": ["gemm_tc.cu", "attn_decode.cu", "attn_prefill.cu", "attn_prefill_tc.cu"],          # bfloat16 only: tcgen05 / TMA kernels
 }
-_HEADERS = ["common.cuh", "attn_mma.cuh"]
+_HEADERS = ["common.cuh", "attn_mma.cuh", "tma.cuh"]
 _loaded: dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
 

@@ -50,6 +50,7 @@ class CudaOps(Ops):
         if self.dtype == torch.bfloat16:
             self.tc = load("fzb200_tc")      # tcgen05 / TMA kernels
         self.use_tensor_cores = self.tc is not None
+        self.prefill_tcgen05 = True        # False: long portions on the mma.sync flash-attention kernel
         self._attn_scratch: torch.Tensor | None = None      # float32 partial outputs of the split decode attention
 
     # ---- plumbing
@@ -200,7 +201,15 @@ class CudaOps(Ops):
                     c_int(hq), c_int(hkv), c_int(hd), c_float(scale), c_int(window), c_int(meta.max_context),
                     c_int(LONG_PORTION), c_int(k.shape[0]), _p(self.err), self._stream()), "paged_attention (decode)")
                 self.launches += 1    # the combine kernel
-            if meta.n_tiles > 0:
+            if meta.n_tiles > 0 and self.prefill_tcgen05 and \
+                    self.tc.fz_attn_prefill_tc_check(c_int(hq), c_int(hkv), c_int(hd), c_int(cache.page_size)) == 0:
+                # rows of long portions on the tcgen05 flash-attention kernel
+                self._check(self.tc.fz_attn_prefill_tc(
+                    _p(q), c_int(n), _p(k), _p(v), c_longlong(page_stride), c_int(k.shape[0]), _p(meta.seg), _p(meta.tiles),
+                    c_int(meta.n_tiles), _p(table), c_int(table.shape[1]), c_int(cache.page_size), _p(out), c_int(hq),
+                    c_int(hkv), c_int(hd), c_float(scale), c_int(window), _p(self.err), self._stream()),
+                    "paged_attention (prefill, tcgen05)")
+            elif meta.n_tiles > 0:
                 self._check(self.tc.fz_attn_prefill(
                     _p(q), _p(k), _p(v), _p(meta.seg), _p(meta.tiles), c_int(meta.n_tiles), _p(table),
                     c_int(table.shape[1]), c_longlong(page_stride), c_int(cache.page_size), _p(out), c_int(hq),
