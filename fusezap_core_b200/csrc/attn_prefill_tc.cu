@@ -3,9 +3,11 @@
 // grid (tiles, query heads), 192 threads, one CTA per SM. A tile is 128 consecutive token rows of one portion (the host
 // lists the tiles, the ones with the most keys first); the 128 rows are the 128 TMEM lanes. Keys come in tiles of 128:
 //   warp 0      TMA producer: the Q tile once; per key tile the pages' boxes of K and V (a page's rows of one kv head are
-//               one box of the pool seen as a 2-D array of rows; 128-byte swizzle) into a two-stage ring;
-//   warp 1      one lane issues tcgen05.mma: S = Q K^T (128 x 128 x hd, both operands K-major) into TMEM, and, once the
-//               softmax warps have written P, PV = P V (128 x hd x 128; V is the MN-major operand, as TMA delivers it);
+//               one box of the pool seen as a 2-D array of rows; 128-byte swizzle) into a two-stage ring of K tiles and
+//               one of V tiles (a key stage is free again as soon as its score product is done);
+//   warp 1      one lane issues tcgen05.mma: S = Q K^T (128 x 128 x hd, both operands K-major) into one of two TMEM
+//               buffers, one key tile ahead of the softmax warps, and, once they have written P, PV = P V (128 x hd x
+//               128; V is the MN-major operand, as TMA delivers it);
 //   warps 2..5  one thread per row: read the row's scores from TMEM, scale, mask (causal by position, window), online
 //               softmax in the exp2 domain with float32 max and sum, write P as bf16 into shared memory in the swizzled
 //               K-major layout, then read PV from TMEM and fold it into the row's float32 output registers with the
@@ -43,6 +45,12 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint
 }
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// 2^x on the special-function unit (ex2.approx: about 2 ulp; -inf gives 0)
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 // 32 consecutive float32 columns of this thread's TMEM lane
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
@@ -96,18 +104,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
   constexpr int HALVES = HD / 64;                     // 64-column halves of a head
   constexpr int HALF_BYTES = 128 * 128;               // 128 rows of 128 bytes
   constexpr int Q_BYTES = HALVES * HALF_BYTES, KV_BYTES = HALVES * HALF_BYTES, P_BYTES = (BN / 64) * HALF_BYTES;
-  constexpr int STAGE_BYTES = 2 * KV_BYTES;           // K then V
-  constexpr int TMEM_COLS = 256;                      // S: columns 0..127, PV: columns 128..128+HD
-  constexpr int OPS = (BN / BOX) * 2 * HALVES;        // TMA boxes per key tile
+  constexpr int TMEM_COLS = 512;                      // S buffers: columns 0..127 and 128..255, PV: columns 256..256+HD
+  constexpr int OPS = (BN / BOX) * HALVES;            // TMA boxes per key tile, for K and again for V
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  const uint32_t s_q = smem_u32(smem), s_kv = s_q + Q_BYTES, s_p = s_kv + KV_STAGES * STAGE_BYTES;
-  uint64_t* bars = (uint64_t*)(smem + Q_BYTES + KV_STAGES * STAGE_BYTES + P_BYTES);
+  // [Q][K ring][V ring][P]
+  const uint32_t s_q = smem_u32(smem), s_k = s_q + Q_BYTES, s_v = s_k + KV_STAGES * KV_BYTES, s_p = s_v + KV_STAGES * KV_BYTES;
+  uint64_t* bars = (uint64_t*)(smem + Q_BYTES + 2 * KV_STAGES * KV_BYTES + P_BYTES);
   uint64_t* q_full = bars;                 // 1
-  uint64_t* kv_full = bars + 1;            // KV_STAGES
-  uint64_t* kv_empty = kv_full + KV_STAGES;
-  uint64_t* s_ready = kv_empty + KV_STAGES;
-  uint64_t* p_ready = s_ready + 1;
+  uint64_t* k_full = bars + 1;             // KV_STAGES each
+  uint64_t* k_empty = k_full + KV_STAGES;
+  uint64_t* v_full = k_empty + KV_STAGES;
+  uint64_t* v_empty = v_full + KV_STAGES;
+  uint64_t* s_ready = v_empty + KV_STAGES; // 2: one per S buffer
+  uint64_t* p_ready = s_ready + 2;
   uint64_t* pv_ready = p_ready + 1;
   uint32_t* tmem_slot = (uint32_t*)(pv_ready + 1);
   int* flag = (int*)(tmem_slot + 1);
@@ -115,8 +125,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < KV_STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
-    mbar_init(s_ready, 1);
+    for (int s = 0; s < KV_STAGES; ++s) {
+      mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
+    }
+    mbar_init(&s_ready[0], 1);
+    mbar_init(&s_ready[1], 1);
     mbar_init(p_ready, 128);
     mbar_init(pv_ready, 1);
     flag[0] = 0;
@@ -124,7 +137,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
   }
   // zeros in the key / value stages: a box that is not fetched (keys past the portion's last position) must not hold
   // another block's bits, since P = 0 times NaN is NaN
-  for (int e = tid; e < KV_STAGES * STAGE_BYTES / 16; e += NUM_THREADS) ((uint4*)(smem + Q_BYTES))[e] = make_uint4(0u, 0u, 0u, 0u);
+  for (int e = tid; e < 2 * KV_STAGES * KV_BYTES / 16; e += NUM_THREADS) ((uint4*)(smem + Q_BYTES))[e] = make_uint4(0u, 0u, 0u, 0u);
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
   tc_fence_before();
@@ -161,10 +174,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
       bool ok = true;
       for (int t = 0; t < n_key_tiles && ok; ++t) {
         const int s = t % KV_STAGES, round = t / KV_STAGES;
-        if (round > 0) ok = __all_sync(0xffffffffu, mbar_wait(&kv_empty[s], (round - 1) & 1));
-        if (!ok) { if (lane == 0) flag[0] = 1; break; }
         const int key0 = k_begin + t * BN;
-        // op -> (page box, K or V, column half); a box is fetched if any of its keys lies in [lo_tile, last_pos]
+        // op -> (page box, column half); a box is fetched if any of its keys lies in [lo_tile, last_pos]
         int op_row[(OPS + 31) / 32];
         uint32_t bytes = 0;
 #pragma unroll
@@ -172,7 +183,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
           const int op = lane + 32 * i;
           op_row[i] = -1;
           if (op < OPS) {
-            const int box = op / (2 * HALVES);
+            const int box = op / HALVES;
             const int key = key0 + box * BOX;
             if (key <= last_pos && key + BOX - 1 >= lo_tile) {
               const int pi = key / page_size;
@@ -185,42 +196,57 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) bytes += __shfl_xor_sync(0xffffffffu, bytes, o);
-        if (lane == 0) mbar_expect_tx(&kv_full[s], bytes);
-        __syncwarp();
-        const uint32_t sk = s_kv + s * STAGE_BYTES, bar = smem_u32(&kv_full[s]);
 #pragma unroll
-        for (int i = 0; i < (OPS + 31) / 32; ++i) {
-          const int op = lane + 32 * i;
-          if (op < OPS && op_row[i] >= 0) {
-            const int box = op / (2 * HALVES), rest = op % (2 * HALVES), is_v = rest / HALVES, hf = rest % HALVES;
-            tma_load_2d_u32(sk + is_v * KV_BYTES + hf * HALF_BYTES + box * BOX * 128, &kv_map, bar, 64 * hf,
-                            op_row[i] + is_v * Hkv * page_size);
+        for (int is_v = 0; is_v < 2; ++is_v) {     // keys first: the score product needs them first
+          uint64_t* full = is_v ? &v_full[s] : &k_full[s];
+          uint64_t* empty = is_v ? &v_empty[s] : &k_empty[s];
+          if (round > 0) ok = __all_sync(0xffffffffu, mbar_wait(empty, (round - 1) & 1));
+          if (!ok) break;
+          if (lane == 0) mbar_expect_tx(full, bytes);
+          __syncwarp();
+          const uint32_t dst = (is_v ? s_v : s_k) + s * KV_BYTES, bar = smem_u32(full);
+#pragma unroll
+          for (int i = 0; i < (OPS + 31) / 32; ++i) {
+            const int op = lane + 32 * i;
+            if (op < OPS && op_row[i] >= 0) {
+              const int box = op / HALVES, hf = op % HALVES;
+              tma_load_2d_u32(dst + hf * HALF_BYTES + box * BOX * 128, &kv_map, bar, 64 * hf, op_row[i] + is_v * Hkv * page_size);
+            }
           }
         }
+        if (!ok && lane == 0) flag[0] = 1;
       }
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer
     if (lane == 0 && n_key_tiles > 0) {
       constexpr uint32_t idesc_s = make_idesc(BM, BN, false), idesc_pv = make_idesc(BM, HD, true);
-      const uint32_t tmem_s = tmem_base, tmem_pv = tmem_base + 128;
+      const uint32_t tmem_pv = tmem_base + 256;
       bool ok = mbar_wait(q_full, 0);
-      for (int t = 0; t < n_key_tiles && ok; ++t) {
+      auto issue_s = [&](int t) -> bool {      // S(t) = Q K(t)^T into S buffer t & 1; frees the key stage when done
         const int s = t % KV_STAGES;
-        if (!mbar_wait(&kv_full[s], (t / KV_STAGES) & 1)) { ok = false; break; }
+        if (!mbar_wait(&k_full[s], (t / KV_STAGES) & 1)) return false;
         tc_fence_after();
-        const uint32_t sk = s_kv + s * STAGE_BYTES, sv = sk + KV_BYTES;
-        // S = Q K^T over hd = HALVES x 64
+        const uint32_t sk = s_k + s * KV_BYTES, tmem_s = tmem_base + (uint32_t)(t & 1) * 128u;
 #pragma unroll
         for (int hf = 0; hf < HALVES; ++hf) {
           const uint64_t dq = desc_k_major(s_q + hf * HALF_BYTES), dk = desc_k_major(sk + hf * HALF_BYTES);
 #pragma unroll
           for (int k = 0; k < 4; ++k) umma_bf16(tmem_s, dq + (uint64_t)(2 * k), dk + (uint64_t)(2 * k), idesc_s, (hf | k) ? 1u : 0u);
         }
-        umma_commit(s_ready);
+        umma_commit(&s_ready[t & 1]);
+        umma_commit(&k_empty[s]);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int t = 0; t < n_key_tiles && ok; ++t) {
+        // the next tile's scores run on the tensor core while the softmax warps work on this tile's
+        if (t + 1 < n_key_tiles && !issue_s(t + 1)) { ok = false; break; }
+        const int s = t % KV_STAGES;
+        if (!mbar_wait(&v_full[s], (t / KV_STAGES) & 1)) { ok = false; break; }
         if (!mbar_wait(p_ready, t & 1)) { ok = false; break; }
         tc_fence_after();
-        // PV = P V over the tile's 128 keys, 16 per instruction
+        const uint32_t sv = s_v + s * KV_BYTES;
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk) {
           const uint64_t dp = desc_k_major(s_p + (kk >> 2) * HALF_BYTES) + (uint64_t)(2 * (kk & 3));
@@ -228,7 +254,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
           umma_bf16(tmem_pv, dp, dv, idesc_pv, kk ? 1u : 0u);
         }
         umma_commit(pv_ready);
-        umma_commit(&kv_empty[s]);
+        umma_commit(&v_empty[s]);
       }
       if (!ok) flag[0] = 1;
     }
@@ -237,7 +263,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     const int quad = warp & 3;
     const int r = quad * 32 + lane;
     const uint32_t lane_sel = (uint32_t)(quad * 32) << 16;
-    const uint32_t t_s = tmem_base + lane_sel, t_pv = tmem_base + 128 + lane_sel;
+    const uint32_t t_pv = tmem_base + 256 + lane_sel;
     const int qpos = qpos0 + r;
     float o[HD];
 #pragma unroll
@@ -245,39 +271,56 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
     for (int t = 0; t < n_key_tiles && ok; ++t) {
-      ok = __all_sync(0xffffffffu, mbar_wait(s_ready, t & 1));
+      ok = __all_sync(0xffffffffu, mbar_wait(&s_ready[t & 1], (t >> 1) & 1));
       if (!ok) break;
       tc_fence_after();
+      const uint32_t t_s = tmem_base + (uint32_t)(t & 1) * 128u + lane_sel;
       const int key0 = k_begin + t * BN;
       const int lo_key = window > 0 ? max(lo_tile, qpos - window + 1) : lo_tile;
+      const bool full = key0 + BN - 1 <= qpos && key0 >= lo_key;     // every key of the tile is visible to this row
       float v[32];
       float mx = -INFINITY;
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         tmem_ld32(t_s + (uint32_t)c, v);
+        if (full) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int key = key0 + c + i;
-          if (key <= qpos && key >= lo_key) mx = fmaxf(mx, v[i]);
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, v[i]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int key = key0 + c + i;
+            if (key <= qpos && key >= lo_key) mx = fmaxf(mx, v[i]);
+          }
         }
       }
       const float mn = fmaxf(m_run, mx * scale_log2);
       const float mu = mn == -INFINITY ? 0.f : mn;
-      const float corr = exp2f(m_run - mu);
+      const float corr = fast_exp2(m_run - mu);
       m_run = mn;
       float sum = 0.f;
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         tmem_ld32(t_s + (uint32_t)c, v);
         uint32_t w[16];
+        if (full) {
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const int key = key0 + c + i;
-          const float e0 = (key <= qpos && key >= lo_key) ? exp2f(v[i] * scale_log2 - mu) : 0.f;
-          const float e1 = (key + 1 <= qpos && key + 1 >= lo_key) ? exp2f(v[i + 1] * scale_log2 - mu) : 0.f;
-          sum += e0 + e1;
-          const __nv_bfloat162 pk = __floats2bfloat162_rn(e0, e1);
-          w[i >> 1] = *(const uint32_t*)&pk;
+          for (int i = 0; i < 32; i += 2) {
+            const float e0 = fast_exp2(fmaf(v[i], scale_log2, -mu)), e1 = fast_exp2(fmaf(v[i + 1], scale_log2, -mu));
+            sum += e0 + e1;
+            const __nv_bfloat162 pk = __floats2bfloat162_rn(e0, e1);
+            w[i >> 1] = *(const uint32_t*)&pk;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const int key = key0 + c + i;
+            const float e0 = (key <= qpos && key >= lo_key) ? fast_exp2(fmaf(v[i], scale_log2, -mu)) : 0.f;
+            const float e1 = (key + 1 <= qpos && key + 1 >= lo_key) ? fast_exp2(fmaf(v[i + 1], scale_log2, -mu)) : 0.f;
+            sum += e0 + e1;
+            const __nv_bfloat162 pk = __floats2bfloat162_rn(e0, e1);
+            w[i >> 1] = *(const uint32_t*)&pk;
+          }
         }
         // columns c..c+31 of row r: column half c / 64, 16-byte chunks (c % 64) / 8 .. + 3, swizzled by the row
         const uint32_t base = s_p + (c >> 6) * HALF_BYTES + r * 128;
@@ -337,7 +380,7 @@ int launch(const void* q, int N, const void* k_pool, long long pool_rows, const 
   if (st != FZ_OK) return st;
   if ((st = get_map_bf16(k_pool, pool_rows, HD, BOX, &kvm)) != FZ_OK) return st;
   constexpr int HALVES = HD / 64, HALF_BYTES = 128 * 128;
-  constexpr size_t smem = (size_t)HALVES * HALF_BYTES + KV_STAGES * 2 * HALVES * HALF_BYTES + (BN / 64) * HALF_BYTES + 8 * 16 + 1024;
+  constexpr size_t smem = (size_t)HALVES * HALF_BYTES + KV_STAGES * 2 * HALVES * HALF_BYTES + (BN / 64) * HALF_BYTES + 8 * 24 + 1024;
   static bool raised = false;
   if (!raised) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD, BOX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
