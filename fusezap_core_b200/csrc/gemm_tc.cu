@@ -7,7 +7,9 @@
 //                             from HBM once), the instruction's N (BN = 16..128) are the token rows; the tile is stored
 //                             transposed. Nothing is padded to 128 tokens. (The reference's decode GEMM swaps operands the
 //                             same way on sm_90a wgmma: fusezap/device/cuda_kernels/wgmma.py:182-317.)
-// A CTA computes one 128 x BN tile over one range of K:
+// Rows mode is persistent: one CTA per SM walks the 128 x 256 output tiles (token tiles fastest, so the CTAs running at one
+// time share a few weight tiles in L2), the MMA lane alternates between two TMEM accumulators, and the epilogue warps
+// store one tile while the next one is being computed. Swap mode: a CTA computes one 128 x BN tile over one range of K:
 //   warp 0  one lane issues the TMA loads (cp.async.bulk.tensor.2d, 128-byte swizzle, 64 k per stage) into a ring of
 //           shared-memory stages guarded by full/empty mbarriers; no multicast;
 //   warp 1  allocates the TMEM accumulator; one lane issues tcgen05.mma (128 x BN x 16, 4 per stage) and commits each
@@ -19,36 +21,18 @@
 // stores the result. The sum has one fixed order (as the reference's split-K has: wgmma.py:209-239) and no partial ever
 // goes to global memory. Waits on this CTA's own mbarriers are bounded by a time limit after which the kernel sets an
 // error bit and leaves; the cluster barriers are hardware barriers, not spins.
-#include "tma.cuh"
+#include "umma.cuh"
 
 namespace {
 using namespace fztma;
+using namespace fzumma;
 
 constexpr int BM = 128;           // TMEM lanes = rows of the 128-row operand
 constexpr int BK = 64;            // k per stage: 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int NUM_THREADS = 192;  // warp 0 TMA, warp 1 MMA, warps 2..5 epilogue
 
-// ---------------------------------------------------------------------------------------------- PTX wrappers
-__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(cols) : "memory");
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
-}
+// ---------------------------------------------------------------------------------------------- cluster helpers
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
@@ -66,37 +50,6 @@ __device__ __forceinline__ float ld_dsmem(uint32_t addr, uint32_t rank) {
   asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
   return v;
 }
-// 16 consecutive float32 columns of this thread's TMEM lane
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
-  uint32_t r[16];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-
-// Shared-memory operand descriptor: K-major tile of rows x 64 bf16 with the 128-byte swizzle; rows are 128 bytes apart,
-// groups of 8 rows 1024 bytes apart. Bits: [0,14) address >> 4, [16,30) leading offset >> 4 (1: unused with a swizzle),
-// [32,46) stride offset >> 4 (1024 >> 4), [46,48) version 1, [61,64) layout 2 = 128-byte swizzle.
-__device__ __forceinline__ uint64_t make_smem_desc(const void* tile) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_u32(tile) & 0x3FFFF) >> 4);
-  d |= (uint64_t)1 << 16;
-  d |= (uint64_t)(1024 >> 4) << 32;
-  d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
-  return d;
-}
-// Instruction descriptor: D float32 (bits [4,6) = 1), A and B bf16 ([7,10) = 1, [10,13) = 1), both K-major ([15], [16]
-// = 0), N >> 3 at [17,23), M >> 4 at [24,29).
-__host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-
 struct Params {
   float* c_f32;            // exactly one of c_f32 / c_bf16 is set
   __nv_bfloat16* c_bf16;
@@ -184,7 +137,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (!mbar_wait(&full[s], round & 1)) { flag[1] = 1; ok = false; break; }
         tc_fence_after();
         const uint8_t* sa = smem + (size_t)s * STAGE_BYTES;
-        const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + A_BYTES);
+        const uint64_t da = desc_k_major(smem_u32(sa)), db = desc_k_major(smem_u32(sa + A_BYTES));
 #pragma unroll
         for (int k = 0; k < BK / UMMA_K; ++k)   // 32 bytes further along the swizzled row per 16 k
           umma_bf16(tmem_d, da + (uint64_t)(k * UMMA_K * 2 / 16), db + (uint64_t)(k * UMMA_K * 2 / 16), idesc,
@@ -300,6 +253,181 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   if (threadIdx.x == 0 && flag[1]) atomicOr(p.err, FZ_ERR_WAIT_TIMEOUT);
 }
 
+// ---------------------------------------------------------------------------------------------- rows mode, persistent
+// C[rows, feats] = X . W^T (+ bias) for many token rows. grid = min(tiles, SMs); tile i of a CTA is tile number
+// blockIdx.x + i * gridDim.x, token tile = number % tiles_m, feature tile = number / tiles_m.
+template <int BN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const Params p,
+                    int tiles_m, int tiles_n) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;      // two accumulators
+  uint64_t* full = (uint64_t*)(smem + (size_t)p.stages * STAGE_BYTES);
+  uint64_t* empty = full + p.stages;
+  uint64_t* acc_full = empty + p.stages;     // [2]
+  uint64_t* acc_empty = acc_full + 2;        // [2]
+  uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+  int* flag = (int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kblocks = (p.K + BK - 1) / BK;
+  const int total = tiles_m * tiles_n;
+  const int my_tiles = total > (int)blockIdx.x ? (total - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 128); }
+    flag[0] = 0;
+    mbar_init_fence();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  fz_grid_launch_dependents();
+  if (warp != 0) fz_grid_wait();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // weights of the first stages before the wait on the previous kernel (they do not depend on it)
+      const int first = (int)blockIdx.x;
+      const int early = my_tiles > 0 ? (kblocks < p.stages ? kblocks : p.stages) : 0;
+      for (int i = 0; i < early; ++i) {
+        mbar_expect_tx(&full[i], STAGE_BYTES);
+        tma_load_2d(smem + (size_t)i * STAGE_BYTES + A_BYTES, &map_w, &full[i], i * BK, (first / tiles_m) * BN);
+      }
+      fz_grid_wait();
+      int it = 0;
+      bool ok = true;
+      for (int j = 0; j < my_tiles && ok; ++j) {
+        const int tile = (int)blockIdx.x + j * (int)gridDim.x;
+        const int tm = tile % tiles_m, tn = tile / tiles_m;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int s = it % p.stages, round = it / p.stages;
+          uint8_t* sa = smem + (size_t)s * STAGE_BYTES;
+          if (it >= early) {
+            if (round > 0 && !mbar_wait(&empty[s], (round - 1) & 1)) { flag[0] = 1; ok = false; break; }
+            mbar_expect_tx(&full[s], STAGE_BYTES);
+            tma_load_2d(sa + A_BYTES, &map_w, &full[s], kb * BK, tn * BN);
+          }
+          tma_load_2d(sa, &map_x, &full[s], kb * BK, tm * BM);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(BM, BN);
+      int it = 0;
+      bool ok = true;
+      for (int j = 0; j < my_tiles && ok; ++j) {
+        const int acc = j & 1;
+        if (j >= 2 && !mbar_wait(&acc_empty[acc], ((j >> 1) - 1) & 1)) { flag[0] = 1; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int s = it % p.stages, round = it / p.stages;
+          if (!mbar_wait(&full[s], round & 1)) { flag[0] = 1; ok = false; break; }
+          tc_fence_after();
+          const uint8_t* sa = smem + (size_t)s * STAGE_BYTES;
+          const uint64_t da = desc_k_major(smem_u32(sa)), db = desc_k_major(smem_u32(sa + A_BYTES));
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_bf16(tmem_d, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          umma_commit(&empty[s]);
+        }
+        umma_commit(&acc_full[acc]);
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    bool ok = true;
+    for (int j = 0; j < my_tiles && ok; ++j) {
+      const int tile = (int)blockIdx.x + j * (int)gridDim.x;
+      const int tm = tile % tiles_m, tn = tile / tiles_m;
+      const int acc = j & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(&acc_full[acc], (j >> 1) & 1));
+      if (!ok) { flag[0] = 1; break; }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(quad * 32) << 16);
+      const int row = tm * BM + r, n0 = tn * BN;
+      float v[16];
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 16) {
+        tmem_ld16(taddr + (uint32_t)c, v);
+        if (row >= p.rows) continue;
+        const int n = n0 + c;
+        if (p.vec_ok && n + 16 <= p.feats) {
+          if (p.bias) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] += p.bias[n + i];
+          }
+          if (p.c_f32) {
+            float4* dst = (float4*)(p.c_f32 + (size_t)row * p.feats + n);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+          } else {
+            uint32_t w[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const __nv_bfloat162 h2 = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+              w[i] = *(const uint32_t*)&h2;
+            }
+            uint4* dst = (uint4*)(p.c_bf16 + (size_t)row * p.feats + n);
+            dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+            dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            if (n + i < p.feats) {
+              const float y = v[i] + (p.bias ? p.bias[n + i] : 0.f);
+              if (p.c_f32) p.c_f32[(size_t)row * p.feats + n + i] = y;
+              else p.c_bf16[(size_t)row * p.feats + n + i] = __float2bfloat16_rn(y);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&acc_empty[acc]);      // this thread has read its lane of the accumulator
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && flag[0]) atomicOr(p.err, FZ_ERR_WAIT_TIMEOUT);
+}
+
+template <int BN>
+int launch_rows(const CUtensorMap& mx, const CUtensorMap& mw, const Params& p, int tiles_m, int tiles_n, cudaStream_t stream) {
+  constexpr int STAGE_BYTES = (BM + BN) * BK * 2;
+  const size_t smem = (size_t)p.stages * STAGE_BYTES + 1024 + 8 * (2 * p.stages + 4) + 16;
+  static size_t allowed = 48 * 1024;
+  if (smem > allowed) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_rows_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    allowed = smem;
+  }
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+  }
+  const int total = tiles_m * tiles_n;
+  dim3 grid(total < sms ? total : sms);
+  fz_launch(gemm_tc_rows_kernel<BN>, grid, dim3(NUM_THREADS), smem, stream, mx, mw, p, tiles_m, tiles_n);
+  FZ_LAUNCH_CHECK();
+  return FZ_OK;
+}
+
 // ---------------------------------------------------------------------------------------------- host side
 template <int BN>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, dim3 grid, cudaStream_t stream) {
@@ -395,17 +523,16 @@ FZ_API int fz_gemm_tc(const void* x, const void* w, const float* bias, void* c, 
       default: return launch<128>(ma, mb, p, grid, stream);
     }
   }
-  // rows mode: token rows are the 128 lanes
+  // rows mode: token rows are the 128 lanes; persistent CTAs with two accumulators
   p.swap = 0;
   const int bn = N >= 256 ? 256 : N >= 128 ? 128 : 64;
   p.stages = pick_stages(bn);
   if ((st = get_map_bf16(x, M, K, BM, &ma)) != FZ_OK) return st;
   if ((st = get_map_bf16(w, N, K, bn, &mb)) != FZ_OK) return st;
-  dim3 grid((M + BM - 1) / BM, (N + bn - 1) / bn, 1);
-  if (grid.y > 65535) return FZ_TOO_LARGE;
+  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + bn - 1) / bn;
   switch (bn) {
-    case 256: return launch<256>(ma, mb, p, grid, stream);
-    case 128: return launch<128>(ma, mb, p, grid, stream);
-    default: return launch<64>(ma, mb, p, grid, stream);
+    case 256: return launch_rows<256>(ma, mb, p, tiles_m, tiles_n, stream);
+    case 128: return launch_rows<128>(ma, mb, p, tiles_m, tiles_n, stream);
+    default: return launch_rows<64>(ma, mb, p, tiles_m, tiles_n, stream);
   }
 }

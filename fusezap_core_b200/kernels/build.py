@@ -24,7 +24,7 @@ LIBRARIES: dict[str, list[str]] = {
     "fzb200_core": ["rowwise.cu", "gemm_simt.cu", "attn_simt.cu"],
     "fzb200_tc": ["gemm_tc.cu", "attn_decode.cu", "attn_prefill.cu", "attn_prefill_tc.cu"],          # bfloat16 only: tcgen05 / TMA kernels
 }
-_HEADERS = ["common.cuh", "attn_mma.cuh", "tma.cuh"]
+_HEADERS = ["common.cuh", "attn_mma.cuh", "tma.cuh", "umma.cuh"]
 _loaded: dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
 
