@@ -1,0 +1,115 @@
+"""Real layer sizes with random weights (fewer layers than the published models, so that the plain CPU reference stays
+fast): Qwen2.5-0.5B shapes (14 heads / 2 kv heads, head 64, width 896, tied vocabulary of 151,936) and Llama-3.1-8B
+shapes (32 / 8 heads, head 128, width 4096, llama3 rope scaling). Logits of whole, token-by-token, chunked and mixed
+cuttings against the plain implementation, and a continuous-batching stream against the same requests run alone."""
+import numpy as np
+import pytest
+import torch
+
+import plain_model
+from fusezap_core_b200.cli import load_preset
+from fusezap_core_b200.weights import write_random_model
+from util import assert_close, read_weights
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def qwen_small(tmp_path_factory):
+    cfg = load_preset("qwen2.5-0.5b")
+    cfg["num_hidden_layers"] = 2
+    d = str(tmp_path_factory.mktemp("qwen05b"))
+    write_random_model(cfg, d, seed=5, dtype="bfloat16", std_scale=1.5)
+    return d, cfg
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_qwen_sizes_all_cuttings(qwen_small, dtype):
+    from fusezap_core_b200.cache import CacheManager
+    from fusezap_core_b200.engine import Portion, StepRunner, load_model
+    d, cfg = qwen_small
+    w = read_weights(d)
+    rng = np.random.default_rng(2)
+    P = [rng.integers(0, cfg["vocab_size"], n).tolist() for n in (150, 37, 64)]
+    wf = {k: v.float() for k, v in w.items()}
+    ref = [plain_model.forward(cfg, wf if dtype == "float32" else w, ids, torch.float32 if dtype == "float32" else torch.bfloat16).numpy()
+           for ids in P]
+    model = load_model(d, dtype, "cuda:0", max_len=256)
+    cache = CacheManager(model.cache_needs(), model.state_needs(), 16, 24, 4, 256, model.ops.dtype, model.device)
+    run = StepRunner(model, cache, max_rows=256)
+    def logits(portions):
+        return run.run(portions).float().cpu().numpy().copy()
+    # whole
+    got = logits([Portion("a", P[0], list(range(150)))])
+    assert_close(got, ref[0], dtype, f"whole {dtype}", longest_sum=cfg["intermediate_size"])
+    cache.free("a")
+    # most in one step, the last 32 one by one, beside portions of a second request and the whole third (mixed)
+    rows = {0: [], 1: [], 2: []}
+    out = logits([Portion("a", P[0][:118], list(range(118))), Portion("b", P[1][:9], list(range(9)))])
+    rows[0].append(out[:118]); rows[1].append(out[118:])
+    at_b = 9
+    for t in range(118, 150):
+        portions = [Portion("a", P[0][t:t + 1], [0])]
+        if at_b < len(P[1]):
+            n = min(3, len(P[1]) - at_b)
+            portions.append(Portion("b", P[1][at_b:at_b + n], list(range(n))))
+        if t == 130:
+            portions.append(Portion("c", P[2], list(range(64))))
+        out = logits(portions)
+        rows[0].append(out[:1]); k = 1
+        if len(portions) > 1 and portions[1].req == "b":
+            n = len(portions[1].tokens); rows[1].append(out[k:k + n]); k += n; at_b += n
+        if t == 130:
+            rows[2].append(out[k:k + 64])
+    for i in range(3):
+        assert_close(np.concatenate(rows[i]), ref[i], dtype, f"mixed {dtype} request {i}", longest_sum=cfg["intermediate_size"])
+    model.ops.check_errors()
+
+
+def test_continuous_batching_stream_equals_running_alone(qwen_small):
+    """32 requests with prompts of 16 to 300 tokens and 24 new tokens each arrive over time; in float32 every request's
+    greedy tokens are the ones it gets when it runs alone (rows do not depend on the batch or on the cut)."""
+    from fusezap_core_b200 import LLMEngine, SamplingParams, load_model
+    d, cfg = qwen_small
+    model = load_model(d, "float32", "cuda:0", max_len=512)
+    rng = np.random.default_rng(9)
+    prompts = [rng.integers(0, cfg["vocab_size"], int(n)).tolist() for n in rng.integers(16, 300, 32)]
+    params = SamplingParams(max_tokens=24, ignore_eos=True)
+    eng = LLMEngine(model, num_blocks=160, block_size=16, max_num_seqs=8, max_prefill_tokens=128, max_model_len=512)
+    done, rids, nxt, steps = {}, [], 0, 0
+    while nxt < len(prompts) or eng.has_unfinished():
+        for _ in range(2):                       # two arrivals per step
+            if nxt < len(prompts):
+                rids.append(eng.add_request(prompts[nxt], params)); nxt += 1
+        for o in eng.step():
+            if o.finished:
+                done[o.request_id] = o.token_ids
+        steps += 1
+        assert steps < 5000
+    assert eng.stats["mixed_steps"] > 0 and eng.cache.num_free_pages == 160
+    alone = LLMEngine(model, num_blocks=40, block_size=16, max_num_seqs=1, max_prefill_tokens=512, max_model_len=512)
+    for i in (0, 5, 13, 31):
+        assert alone.generate([prompts[i]], params)[0] == done[rids[i]], f"request {i}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_llama8b_layer_sizes(tmp_path, dtype):
+    from fusezap_core_b200.cache import CacheManager
+    from fusezap_core_b200.engine import Portion, StepRunner, load_model
+    cfg = load_preset("llama-3.1-8b")
+    cfg["num_hidden_layers"] = 1
+    cfg["vocab_size"] = 2048            # the vocabulary only sizes the embedding and the output matrix
+    d = str(tmp_path / "l8b")
+    write_random_model(cfg, d, seed=8, dtype="bfloat16", std_scale=1.0)
+    w = read_weights(d)
+    ids = np.random.default_rng(4).integers(0, 2048, 200).tolist()
+    wf = {k: v.float() for k, v in w.items()} if dtype == "float32" else w
+    ref = plain_model.forward(cfg, wf, ids, torch.float32 if dtype == "float32" else torch.bfloat16).numpy()
+    model = load_model(d, dtype, "cuda:0", max_len=256)
+    cache = CacheManager(model.cache_needs(), model.state_needs(), 16, 16, 2, 256, model.ops.dtype, model.device)
+    run = StepRunner(model, cache, max_rows=256)
+    a = run.run([Portion("x", ids[:130], list(range(130)))]).float().cpu().numpy().copy()
+    b = run.run([Portion("x", ids[130:199], list(range(69)))]).float().cpu().numpy().copy()
+    c = run.run([Portion("x", ids[199:], [0])]).float().cpu().numpy().copy()
+    assert_close(np.concatenate([a, b, c]), ref, dtype, f"llama 8B sizes {dtype}", longest_sum=cfg["intermediate_size"])
+    model.ops.check_errors()
