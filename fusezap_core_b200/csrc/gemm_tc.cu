@@ -50,6 +50,8 @@ __device__ __forceinline__ float ld_dsmem(uint32_t addr, uint32_t rank) {
   asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
   return v;
 }
+__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + __expf(-g)) * u; }
+
 struct Params {
   float* c_f32;            // exactly one of c_f32 / c_bf16 is set
   __nv_bfloat16* c_bf16;
@@ -62,6 +64,7 @@ struct Params {
   int splits;
   int stages;
   int vec_ok;              // rows mode: C rows are 16-byte aligned, so full groups of 16 columns go out as vectors
+  int swiglu;              // W holds [64 gate rows | 64 up rows] blocks: store silu(gate) * up as bf16 [rows, feats / 2]
 };
 
 template <int BN>
@@ -158,7 +161,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int b_limit = p.swap ? p.rows : p.feats;
     const int b0 = tile_b * BN;
     const uint32_t taddr = tmem_d + ((uint32_t)(quad * 32) << 16);
-    const bool direct = p.splits == 1;
+    const bool direct = p.splits == 1 && !p.swiglu;
     float* part = (float*)smem + r;          // split K: partial tile as [column][row] in the (now idle) stage buffers
     float v[16];
     auto store16 = [&](const float* x, int c) {   // columns c..c+15 of this thread's row, final values
@@ -221,28 +224,53 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
     }
   }
-  if (p.splits > 1) {
-    // every thread of every CTA of the cluster passes both barriers; only the epilogue warps work between them
-    cluster_sync_all();
+  if (p.splits > 1 || p.swiglu) {
+    // split K: every thread of every CTA of the cluster passes both cluster barriers; only the epilogue warps work
+    // between them. Without a split (fused SwiGLU only) the epilogue warps synchronise among themselves.
+    if (p.splits > 1) cluster_sync_all();
     if (warp >= 2) {
+      if (p.splits == 1) asm volatile("bar.sync 1, 128;" ::: "memory");
       const int r = (warp & 3) * 32 + lane;
       const int feat = tile_a * BM + r;
-      const uint32_t rank = cluster_rank();
+      const uint32_t rank = p.splits > 1 ? cluster_rank() : 0u;
       const int cols = min(BN, p.rows - tile_b * BN);
       const float bv = (p.bias && feat < p.feats) ? p.bias[feat] : 0.f;
       const uint32_t base = smem_u32(smem) + (uint32_t)r * 4u;
-      for (int c = (int)rank; c < cols; c += p.splits) {
-        float acc = 0.f;
-        for (int sp = 0; sp < p.splits; ++sp) acc += ld_dsmem(base + (uint32_t)(c * BM) * 4u, (uint32_t)sp);   // split order
-        if (feat < p.feats) {
-          const int m = tile_b * BN + c;
+      float* ex = (float*)smem + BN * BM;            // [16][128]: a group of columns, for the gate / up exchange
+      const int n_my = cols > (int)rank ? (cols - (int)rank + p.splits - 1) / p.splits : 0;   // columns rank, rank + S, ...
+      for (int i0 = 0; i0 < n_my; i0 += 16) {
+        const int ni = min(16, n_my - i0);
+        for (int i = 0; i < ni; ++i) {
+          const int c = (int)rank + (i0 + i) * p.splits;
+          float acc = 0.f;
+          if (p.splits > 1) {
+            for (int sp = 0; sp < p.splits; ++sp) acc += ld_dsmem(base + (uint32_t)(c * BM) * 4u, (uint32_t)sp);   // split order
+          } else {
+            acc = ((const float*)smem)[c * BM + r];
+          }
           const float y = acc + bv;
-          if (p.c_f32) p.c_f32[(size_t)m * p.feats + feat] = y;
-          else p.c_bf16[(size_t)m * p.feats + feat] = __float2bfloat16_rn(y);
+          if (p.swiglu) {
+            ex[i * BM + r] = y;
+          } else if (feat < p.feats) {
+            const int m = tile_b * BN + c;
+            if (p.c_f32) p.c_f32[(size_t)m * p.feats + feat] = y;
+            else p.c_bf16[(size_t)m * p.feats + feat] = __float2bfloat16_rn(y);
+          }
+        }
+        if (p.swiglu) {
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (r < 64) {
+            const int half = p.feats >> 1;
+            for (int i = 0; i < ni; ++i) {
+              const int m = tile_b * BN + (int)rank + (i0 + i) * p.splits;
+              p.c_bf16[(size_t)m * half + tile_a * 64 + r] = __float2bfloat16_rn(silu_mul(ex[i * BM + r], ex[i * BM + r + 64]));
+            }
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
         }
       }
     }
-    cluster_sync_all();    // nobody leaves while its shared memory may still be read
+    if (p.splits > 1) cluster_sync_all();    // nobody leaves while its shared memory may still be read
   }
   tc_fence_before();
   __syncthreads();
@@ -355,6 +383,32 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       const uint32_t taddr = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(quad * 32) << 16);
       const int row = tm * BM + r, n0 = tn * BN;
       float v[16];
+      if (p.swiglu) {
+        // columns [128 b, 128 b + 64) are gate, [128 b + 64, 128 b + 128) up of output features 64 (n0 / 128 + b) ..
+        float u[16];
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 16) {
+          if ((c & 64) != 0) continue;
+          tmem_ld16(taddr + (uint32_t)c, v);
+          tmem_ld16(taddr + (uint32_t)(c + 64), u);
+          const int n = n0 + c;                       // packed index of the gate column
+          if (row >= p.rows || n >= p.feats) continue;
+          uint32_t w[8];
+#pragma unroll
+          for (int i = 0; i < 16; i += 2) {
+            const float g0 = v[i] + (p.bias ? p.bias[n + i] : 0.f), g1 = v[i + 1] + (p.bias ? p.bias[n + i + 1] : 0.f);
+            const float u0 = u[i] + (p.bias ? p.bias[n + 64 + i] : 0.f), u1 = u[i + 1] + (p.bias ? p.bias[n + 64 + i + 1] : 0.f);
+            const __nv_bfloat162 h2 = __floats2bfloat162_rn(silu_mul(g0, u0), silu_mul(g1, u1));
+            w[i >> 1] = *(const uint32_t*)&h2;
+          }
+          uint4* dst = (uint4*)(p.c_bf16 + (size_t)row * (p.feats >> 1) + (n >> 7) * 64 + (n & 63));
+          dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+          dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+        }
+        tc_fence_before();
+        mbar_arrive(&acc_empty[acc]);
+        continue;
+      }
 #pragma unroll 1
       for (int c = 0; c < BN; c += 16) {
         tmem_ld16(taddr + (uint32_t)c, v);
@@ -493,8 +547,25 @@ FZ_API int fz_gemm_tc_splits(int N, int K) {
 }
 
 // x: [M, K] bf16, w: [N, K] bf16, bias: [N] float32 or null, c: [M, N] float32 (out_dtype 0) or bf16 (1).
+static int gemm_tc_impl(const void* x, const void* w, const float* bias, void* c, int out_dtype, int M, int N, int K,
+                        int swiglu, int* err, cudaStream_t stream);
+
 FZ_API int fz_gemm_tc(const void* x, const void* w, const float* bias, void* c, int out_dtype, int M, int N, int K,
                       int* err, cudaStream_t stream) {
+  return gemm_tc_impl(x, w, bias, c, out_dtype, M, N, K, 0, err, stream);
+}
+
+// Fused gate/up product and SwiGLU: w is [2 I, K] with rows in blocks of 128 = [64 gate rows | 64 up rows] of the same 64
+// features (bias packed the same way, or null); out is bf16 [M, I] = silu(x . gate^T) * (x . up^T). I % 64 == 0.
+FZ_API int fz_gemm_tc_swiglu(const void* x, const void* w_packed, const float* bias_packed, void* out, int M, int I, int K,
+                             int* err, cudaStream_t stream) {
+  if (I <= 0 || I % 64) return FZ_BAD_SHAPE;
+  if (((uintptr_t)out) & 15) return FZ_BAD_ALIGNMENT;
+  return gemm_tc_impl(x, w_packed, bias_packed, out, FZ_BF16, M, 2 * I, K, 1, err, stream);
+}
+
+static int gemm_tc_impl(const void* x, const void* w, const float* bias, void* c, int out_dtype, int M, int N, int K,
+                        int swiglu, int* err, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return FZ_OK;
   int st = fz_gemm_tc_check(x, w, M, N, K);
   if (st != FZ_OK) return st;
@@ -504,6 +575,7 @@ FZ_API int fz_gemm_tc(const void* x, const void* w, const float* bias, void* c, 
   p.c_bf16 = out_dtype == FZ_BF16 ? (__nv_bfloat16*)c : nullptr;
   p.bias = bias; p.err = err; p.rows = M; p.feats = N; p.K = K;
   p.splits = 1;
+  p.swiglu = swiglu;
   p.vec_ok = (N % 8 == 0 && ((uintptr_t)c & 15) == 0) ? 1 : 0;
   CUtensorMap ma, mb;
   if (M <= 128) {
@@ -525,7 +597,7 @@ FZ_API int fz_gemm_tc(const void* x, const void* w, const float* bias, void* c, 
   }
   // rows mode: token rows are the 128 lanes; persistent CTAs with two accumulators
   p.swap = 0;
-  const int bn = N >= 256 ? 256 : N >= 128 ? 128 : 64;
+  const int bn = N >= 256 ? 256 : N >= 128 ? 128 : 64;     // with the fused SwiGLU N = 2 I >= 128, so a tile holds whole blocks
   p.stages = pick_stages(bn);
   if ((st = get_map_bf16(x, M, K, BM, &ma)) != FZ_OK) return st;
   if ((st = get_map_bf16(w, N, K, bn, &mb)) != FZ_OK) return st;

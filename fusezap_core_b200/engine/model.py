@@ -122,6 +122,9 @@ class DecoderModel:
                 for v in vars(o).values():
                     if isinstance(v, torch.Tensor):
                         add(v)
+                    elif isinstance(v, (tuple, list)):
+                        for t in v:
+                            add(t)
                     elif hasattr(v, "bind") and hasattr(v, "tensors"):
                         stack.append(v)
         add(self.lm_head)

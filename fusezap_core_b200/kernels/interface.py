@@ -38,6 +38,17 @@ class Ops:
         accumulation in float32, one rounding into out."""
         raise NotImplementedError
 
+    def pack_gate_up(self, gate: torch.Tensor, up: torch.Tensor, gate_bias: torch.Tensor | None = None,
+                     up_bias: torch.Tensor | None = None):
+        """Prepares the gate and up matrices ((I, K) each) for `linear_swiglu` in whatever layout the kernels want, or
+        returns None if this table has no fused kernel for these sizes (the part then runs `linear` + `swiglu`)."""
+        return None
+
+    def linear_swiglu(self, a: torch.Tensor, packed: Any, out: torch.Tensor) -> None:
+        """out[m, i] = T(silu(a[m] . gate[i] + gate_bias[i]) * (a[m] . up[i] + up_bias[i])); `packed` from `pack_gate_up`.
+        The products are accumulated in float32 and are not rounded before the activation."""
+        raise NotImplementedError
+
     def rope_kv_write(self, qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, meta: Any, cache: Any,
                       q_out: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int) -> None:
         """qkv: (N, (Hq + 2 Hkv) * hd) float32, heads [q | k | v]. Rotates q and k heads by the row's position

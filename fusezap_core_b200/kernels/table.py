@@ -51,6 +51,7 @@ class CudaOps(Ops):
             self.tc = load("fzb200_tc")      # tcgen05 / TMA kernels
         self.use_tensor_cores = self.tc is not None
         self.prefill_tcgen05 = True        # False: long portions on the mma.sync flash-attention kernel
+        self.fuse_swiglu = True            # gate/up product and SwiGLU in one kernel where the sizes allow it
         self._attn_scratch: torch.Tensor | None = None      # float32 partial outputs of the split decode attention
 
     # ---- plumbing
@@ -143,6 +144,28 @@ class CudaOps(Ops):
         self._check(self.core.fz_gemm_simt(_p(a), _p(w), _p(bias), _p(out), c_int(_CODE[a.dtype]),
                                            c_int(_CODE[out.dtype]), c_int(m), c_int(n), c_int(k), self._stream()),
                     "linear")
+
+    def pack_gate_up(self, gate, up, gate_bias=None, up_bias=None):
+        """Rows in blocks of 128 = [64 gate rows | 64 up rows] of the same 64 features, so that one 128-row tile of the
+        tensor-core product holds both halves of its outputs. None when the fused kernel does not apply."""
+        i, k = gate.shape
+        if not self.use_tensor_cores or not self.fuse_swiglu or gate.dtype != torch.bfloat16 or i % 64 or k % 8:
+            return None
+        w = torch.stack([gate.view(i // 64, 64, k), up.view(i // 64, 64, k)], 1).reshape(2 * i, k).contiguous()
+        b = None
+        if gate_bias is not None:
+            b = torch.stack([gate_bias.float().view(i // 64, 64), up_bias.float().view(i // 64, 64)], 1).reshape(2 * i).contiguous()
+        return (w, b, i)
+
+    def linear_swiglu(self, a, packed, out) -> None:
+        w, b, i = packed
+        self._want(a, "linear input", (torch.bfloat16,), 2)
+        self._want(out, "swiglu output", (torch.bfloat16,), 2)
+        m, k = a.shape
+        if w.shape != (2 * i, k) or out.shape != (m, i):
+            raise KernelError(f"linear_swiglu: a {tuple(a.shape)}, packed {tuple(w.shape)}, out {tuple(out.shape)}")
+        self._check(self.tc.fz_gemm_tc_swiglu(_p(a), _p(w), _p(b), _p(out), c_int(m), c_int(i), c_int(k), _p(self.err),
+                                              self._stream()), "linear_swiglu (tensor cores)")
 
     def _pool(self, cache, hkv: int, hd: int):
         k, v = cache.keys, cache.values

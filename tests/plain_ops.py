@@ -90,6 +90,9 @@ class PlainOps:
                 o[i, h] = torch.softmax(s, 0) @ V[:, h // G, :]
         out.copy_(o.reshape(n, Hq * hd).to(out.dtype))
 
+    def pack_gate_up(self, gate, up, gate_bias=None, up_bias=None):
+        return None
+
     def swiglu(self, gate_up, out) -> None:
         I = out.shape[1]
         g, u = gate_up[:, :I].float(), gate_up[:, I:].float()

@@ -81,3 +81,31 @@ def test_refused_shapes_fall_back_to_the_plain_kernel():
     out = torch.empty(5, 20, device="cuda")
     ops.linear(a, w, None, out)
     assert float((out.double() - a.double() @ w.double().T).abs().max()) < 1e-3
+
+
+@pytest.mark.parametrize("M", [1, 8, 40, 128, 129, 700])
+@pytest.mark.parametrize("I,K", [(128, 64), (448, 96), (4864, 896), (1024, 4096)])
+def test_fused_gate_up_swiglu(M, I, K):
+    """The fused product + SwiGLU against silu(x.gate^T + bg) * (x.up^T + bu) in float64, in both modes (few rows: with
+    and without a split of K; many rows: persistent tiles)."""
+    from fusezap_core_b200.kernels import cuda_ops
+    ops = cuda_ops("bfloat16")
+    g = torch.Generator().manual_seed(M + I + K)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    wg = (torch.randn(I, K, generator=g) * K ** -0.5).to(torch.bfloat16).cuda()
+    wu = (torch.randn(I, K, generator=g) * K ** -0.5).to(torch.bfloat16).cuda()
+    for bias in (False, True):
+        bg = torch.randn(I, generator=g).cuda() if bias else None
+        bu = torch.randn(I, generator=g).cuda() if bias else None
+        packed = ops.pack_gate_up(wg, wu, bg, bu)
+        assert packed is not None
+        out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device="cuda")
+        ops.linear_swiglu(x, packed, out)
+        ops.check_errors()
+        gg = x.double() @ wg.double().T + (bg.double() if bias else 0)
+        uu = x.double() @ wu.double().T + (bu.double() if bias else 0)
+        ref = gg / (1 + torch.exp(-gg)) * uu
+        err = float((out.double() - ref).abs().max())
+        lim = 2.0 ** -8 * float(ref.abs().max()) * 1.01
+        assert torch.isfinite(out.float()).all() and err <= lim, f"M={M} I={I} K={K} bias={bias}: {err:.3e} > {lim:.3e}"
+    assert ops.pack_gate_up(wg[:100], wu[:100]) is None, "I must be a multiple of 64"
