@@ -144,7 +144,7 @@ def main() -> int:
         # prefill_first: while prompts are pending the requests that already decode wait, so all of them start
         # decoding together, at equal contexts
         return LLMEngine(model, num_blocks=pages, block_size=page, max_num_seqs=batch, max_prefill_tokens=a.prefill_tokens,
-                         max_model_len=a.context, prefill_first=1 << 30)
+                         max_model_len=a.context, prefill_first=1 << 30, lookahead=False)
 
     def prefill_to(eng: LLMEngine, batch: int, n_prompt: int, max_tokens: int) -> list[int]:
         """Admits `batch` requests of n_prompt seeded tokens and steps until every one decodes."""
@@ -192,6 +192,7 @@ def main() -> int:
                    launches=steps * eng.launches_per_graph.get((bucket, True), 0) + (model.ops.launches - launches0),
                    bytes=model.weight_bytes() + batch * ctx_mean * kv_bytes_per_token)
         if e2e:
+            eng.lookahead = True        # the entry point's default; off above, where the steps are driven by hand
             for _ in range(warmup):
                 eng.step()
             torch.cuda.synchronize()

@@ -41,6 +41,7 @@ def add_engine_options(s: argparse.ArgumentParser) -> None:
     s.add_argument("--num-blocks", type=int, default=1024, help="cache pages (shared by all requests)")
     s.add_argument("--block-size", type=int, default=16, help="tokens per page")
     s.add_argument("--no-cuda-graphs", action="store_true", help="launch decode steps kernel by kernel")
+    s.add_argument("--no-lookahead", action="store_true", help="read each decode step's tokens before launching the next")
 
 
 def build_parser() -> argparse.ArgumentParser:
@@ -83,7 +84,7 @@ def build_engine(a: argparse.Namespace):
     model = load_model(a.model, resolve_dtype(a.dtype), a.device, max_len=a.max_model_len)
     return LLMEngine(model, num_blocks=a.num_blocks, block_size=a.block_size, max_num_seqs=a.max_num_seqs,
                      max_prefill_tokens=a.max_prefill_tokens, max_model_len=a.max_model_len,
-                     cuda_graphs=not a.no_cuda_graphs)
+                     cuda_graphs=not a.no_cuda_graphs, lookahead=not a.no_lookahead)
 
 
 def cmd_generate(a: argparse.Namespace) -> int:

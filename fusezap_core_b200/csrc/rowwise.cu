@@ -9,13 +9,16 @@
 #include <math.h>
 
 // ------------------------------------------------------------------------------------------------ embedding
+// src (may be null): src[n] >= 0 takes the row's token from prev_ids[src[n]] (the ids the previous step chose, still on
+// the device) instead of tokens[n].
 template <typename T>
-__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tokens, float* __restrict__ x,
-                             int D, int V, int* err) {
+__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tokens, const int* __restrict__ src,
+                             const int* __restrict__ prev_ids, float* __restrict__ x, int D, int V, int* err) {
   fz_grid_wait();
   fz_grid_launch_dependents();
   const int n = blockIdx.x;
-  const int tok = tokens[n];
+  int tok = tokens[n];
+  if (src != nullptr && src[n] >= 0) tok = prev_ids[src[n]];
   float* xr = x + (size_t)n * D;
   if (tok < 0 || tok >= V) {
     if (threadIdx.x == 0) atomicOr(err, FZ_ERR_TOKEN_RANGE);
@@ -26,13 +29,13 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
   for (int d = threadIdx.x; d < D; d += blockDim.x) xr[d] = Cvt<T>::to_f(tr[d]);
 }
 
-FZ_API int fz_embed(const void* table, int table_dtype, const int* tokens, float* x, int N, int D, int V, int* err,
-                    cudaStream_t stream) {
+FZ_API int fz_embed(const void* table, int table_dtype, const int* tokens, const int* src, const int* prev_ids, float* x,
+                    int N, int D, int V, int* err, cudaStream_t stream) {
   if (N <= 0) return FZ_OK;
   if (table_dtype == FZ_F32)
-    fz_launch(embed_kernel<float>, dim3(N), dim3(256), 0, stream, (const float*)table, tokens, x, D, V, err);
+    fz_launch(embed_kernel<float>, dim3(N), dim3(256), 0, stream, (const float*)table, tokens, src, prev_ids, x, D, V, err);
   else if (table_dtype == FZ_BF16)
-    fz_launch(embed_kernel<__nv_bfloat16>, dim3(N), dim3(256), 0, stream, (const __nv_bfloat16*)table, tokens, x, D, V, err);
+    fz_launch(embed_kernel<__nv_bfloat16>, dim3(N), dim3(256), 0, stream, (const __nv_bfloat16*)table, tokens, src, prev_ids, x, D, V, err);
   else
     return FZ_BAD_DTYPE;
   FZ_LAUNCH_CHECK();

@@ -12,7 +12,9 @@ The Python entry point, with the reference's names (fusezap/serve/engine.py:1-8,
 
 A step is: schedule -> pack the batch's int32 metadata in pinned memory -> one host-to-device copy -> the model's step
 function -> device sampling -> one device-to-host copy of the chosen ids -> emit. Decode-only steps replay a CUDA graph
-captured per batch-size bucket (1, 2, 4, ... max_num_seqs), so their cost on the host is one copy and one launch.
+captured per batch-size bucket (1, 2, 4, ... max_num_seqs), so their cost on the host is one copy and one launch; and
+while requests only decode, the next step is launched (fed from the ids still on the device) before the host reads the
+last one's tokens, so the device does not idle between steps.
 """
 from __future__ import annotations
 import itertools
@@ -39,10 +41,20 @@ class RequestOutput:
     num_prompt_tokens: int = 0
 
 
+@dataclass
+class _Launched:
+    """A step that is on the stream and whose tokens the host has not read yet."""
+    rows: list            # (request, index of its token among the step's chosen ids), for every request that gets one
+    slot: int             # which of the two pinned id buffers the ids arrive in
+    logits: torch.Tensor | None
+    event: "torch.cuda.Event | None"
+    all_produce: bool     # every running request gets a token from this step
+
+
 class LLMEngine:
     def __init__(self, model: DecoderModel, num_blocks: int = 1024, block_size: int = 16, max_num_seqs: int = 32,
                  max_prefill_tokens: int | None = None, max_model_len: int | None = None,
-                 max_num_batched_tokens: int | None = None, prefill_first: int = 0, cuda_graphs: bool = True):
+                 max_num_batched_tokens: int | None = None, prefill_first: int = 0, cuda_graphs: bool = True, lookahead: bool = True):
         self.model = model
         self.max_model_len = int(max_model_len or model.max_len)
         if self.max_model_len > model.max_len:
@@ -62,19 +74,25 @@ class LLMEngine:
         pin = dev.type == "cuda"
         R = max_num_seqs
         # per-step sampling inputs and outputs: pinned on the host, fixed buffers on the device
-        self._temp_h = torch.zeros(R, dtype=torch.float32, pin_memory=pin)
-        self._unif_h = torch.zeros(R, dtype=torch.float64, pin_memory=pin)
-        self._ids_h = torch.zeros(R, dtype=torch.int32, pin_memory=pin)
+        # (two of each host buffer: a step may be launched while the one before it is still in flight)
+        self._temp_h = torch.zeros(2, R, dtype=torch.float32, pin_memory=pin)
+        self._unif_h = torch.zeros(2, R, dtype=torch.float64, pin_memory=pin)
+        self._ids_h = torch.zeros(2, R, dtype=torch.int32, pin_memory=pin)
+        self._events = [torch.cuda.Event() for _ in range(2)] if pin else None
+        self._slot = 0
+        self._pending: _Launched | None = None
+        self.lookahead = bool(lookahead)
         self._temp_d = torch.zeros(R, dtype=torch.float32, device=dev)
         self._unif_d = torch.zeros(R, dtype=torch.float64, device=dev)
         self._ids_d = torch.zeros(R, dtype=torch.int32, device=dev)
+        self.runner.prev_ids = self._ids_d
         self.cuda_graphs = bool(cuda_graphs) and pin and model.graph_safe()
         self._graphs: dict[tuple, torch.cuda.CUDAGraph] = {}     # (bucket, all rows greedy) -> captured step
         self.launches_per_graph: dict[tuple, int] = {}           # kernels of this package in one replay of it
         self._greedy_step = True
         self._buckets = sorted({min(1 << i, R) for i in range(R.bit_length() + 1)})
         self.stats = {"steps": 0, "decode_steps": 0, "prefill_steps": 0, "mixed_steps": 0, "tokens": 0,
-                      "preemptions": 0, "graph_replays": 0, "h2d_bytes": 0, "d2h_bytes": 0}
+                      "preemptions": 0, "graph_replays": 0, "lookahead_steps": 0, "h2d_bytes": 0, "d2h_bytes": 0}
 
     # ---- requests
     def add_request(self, prompt_ids: Seq[int], params: SamplingParams | None = None, request_id: int | None = None) -> int:
@@ -115,25 +133,75 @@ class LLMEngine:
 
     # ---- one step
     def step(self) -> list[RequestOutput]:
-        so = self.scheduler.schedule()
-        self.stats["preemptions"] += len(so.preempted)
-        if so.empty:
-            return []
-        portions, owners = self._portions(so)
-        producing = [s for s, p in zip(owners, portions) if p.want]
-        ids, logits = self._forward_and_sample(portions, producing, decode_only=not so.prefill)
+        """Completes one model step and returns its tokens. With `lookahead`, the step after it is launched first
+        whenever it is certain what it holds (see `_speculate`), so the device never waits for the host between
+        decode steps."""
+        cur, self._pending = self._pending, None
+        if cur is not None and not any(s.status == SeqStatus.RUNNING for s, _ in cur.rows):
+            cur = None            # launched ahead for requests that have all ended since: nothing to read from it
+        if cur is None:
+            so = self.scheduler.schedule()
+            self.stats["preemptions"] += len(so.preempted)
+            if so.empty:
+                return []
+            portions, owners = self._portions(so)
+            rows = [(s, i) for i, s in enumerate(s for s, p in zip(owners, portions) if p.want)]
+            kind = "decode_steps" if not so.prefill else "prefill_steps" if not so.decode else "mixed_steps"
+            cur = self._launch(portions, rows, decode_only=not so.prefill,
+                               all_produce=len(rows) == len(self.scheduler.running), kind=kind)
+        nxt = self._speculate(cur) if self.lookahead else None
+        outs = self._complete(cur)
+        self._pending = nxt
+        return outs
+
+    def _speculate(self, cur: "_Launched") -> "_Launched | None":
+        """Launches the decode step that follows `cur` before cur's tokens are known to the host: each row takes its
+        token from the ids cur leaves on the device. Only when that step is certain: nothing waits for admission, every
+        running request gets a token from cur, all of them are sampled on the device, and the pages are there. A request
+        that cur ends by length is left out; one that cur ends by a stop token runs one token too many, which
+        `_complete` drops (its pages are given back in stream order, so nobody reads what it wrote)."""
+        sch, cache = self.scheduler, self.cache
+        if sch.waiting or not cur.all_produce or not cur.rows:
+            return None
+        rows = []
+        for seq, i in cur.rows:
+            p = seq.params
+            if seq.status != SeqStatus.RUNNING or not p.on_device:
+                return None
+            if len(seq.output) + 1 >= p.max_tokens or seq.num_tokens + 1 >= self.max_model_len:
+                continue
+            rows.append((seq, i))
+        if not rows or len(rows) > self.cfg.token_budget:
+            return None
+        # the pages of all rows together: count them before taking any
+        need = [0] * len(cache.groups)
+        for seq, _ in rows:
+            for g, n in enumerate(cache.pages_needed(seq.seq_id, seq.num_computed + 1)):
+                need[g] += n
+        if any(n > g.allocator.num_free for n, g in zip(need, cache.groups)):
+            return None
+        portions = []
+        for seq, i in rows:
+            cache.ensure(seq.seq_id, seq.num_computed + 1)
+            portions.append(Portion(seq.seq_id, [0], [0], src=i))
+        sch.steps += 1
+        self.stats["lookahead_steps"] += 1
+        return self._launch(portions, [(s, j) for j, (s, _) in enumerate(rows)], decode_only=True, all_produce=True)
+
+    def _complete(self, cur: "_Launched") -> list[RequestOutput]:
         st = self.stats
-        st["steps"] += 1
-        st["tokens"] += so.num_tokens
-        st["decode_steps" if not so.prefill else "prefill_steps" if not so.decode else "mixed_steps"] += 1
+        if cur.event is not None:
+            cur.event.synchronize()
+        self.ops.check_errors(copied=True)
+        ids = self._ids_h[cur.slot].numpy()
         outs = []
-        for i, seq in enumerate(producing):
-            if seq.status != SeqStatus.RUNNING:
+        for seq, i in cur.rows:
+            if seq.status != SeqStatus.RUNNING:        # aborted meanwhile, or ended by the step before
                 continue
             if seq.params.on_device:
                 tok = int(ids[i])
             else:
-                row = logits[i].detach().to("cpu", torch.float32).numpy()
+                row = cur.logits[i].detach().to("cpu", torch.float32).numpy()
                 st["d2h_bytes"] += row.nbytes
                 tok = seq.sampler.host_choice(row, seq.tokens)
             outs.append(self._emit(seq, tok))
@@ -150,16 +218,20 @@ class LLMEngine:
             owners.append(seq)
         return portions, owners
 
-    def _forward_and_sample(self, portions, producing, decode_only: bool):
-        runner, ops = self.runner, self.ops
-        R = len(producing)
-        for i, seq in enumerate(producing):
+    def _launch(self, portions, rows, decode_only: bool, all_produce: bool, kind: str = "decode_steps") -> "_Launched":
+        """Puts one step on the stream: metadata and sampling inputs up, the model's step, the choice of tokens, the
+        ids and the error word down. Does not wait for it."""
+        runner, ops, st = self.runner, self.ops, self.stats
+        slot = self._slot = (self._slot + 1) % 2
+        temp_h, unif_h = self._temp_h[slot], self._unif_h[slot]
+        R = len(rows)
+        for seq, i in rows:
             p = seq.params
             device_row = p.on_device and not p.greedy
-            self._temp_h[i] = p.temperature if device_row else 0.0
-            self._unif_h[i] = seq.sampler.next_uniform() if device_row else 0.0
+            temp_h[i] = p.temperature if device_row else 0.0
+            unif_h[i] = seq.sampler.next_uniform() if device_row else 0.0
         # all rows greedy: the row-split argmax kernel picks the tokens; else the sampling kernel (argmax for its greedy rows)
-        self._greedy_step = all(s.params.greedy or not s.params.on_device for s in producing)
+        self._greedy_step = all(s.params.greedy or not s.params.on_device for s, _ in rows)
         bucket = next((b for b in self._buckets if b >= len(portions)), None) if decode_only and self.cuda_graphs else None
         pad = bucket or 0
         starts = runner.prepare(portions, pad_rows=pad, pad_wanted=pad)
@@ -168,17 +240,19 @@ class LLMEngine:
             runner.meta.max_context = self.max_model_len
         n_w = runner.meta.n_wanted
         if n_w:
-            self._temp_h[R:n_w] = 0.0
-            self._temp_d[:n_w].copy_(self._temp_h[:n_w], non_blocking=True)
-            self._unif_d[:n_w].copy_(self._unif_h[:n_w], non_blocking=True)
-        self.stats["h2d_bytes"] += runner.meta.size * 4 + n_w * 12
-        logits = None
+            temp_h[R:n_w] = 0.0
+            self._temp_d[:n_w].copy_(temp_h[:n_w], non_blocking=True)
+            self._unif_d[:n_w].copy_(unif_h[:n_w], non_blocking=True)
+        st["h2d_bytes"] += runner.meta.size * 4 + n_w * 12
         if bucket is not None:
             key = (bucket, self._greedy_step)
             g = self._graphs.get(key)
             if g is None:
-                logits = self._eager(n_w)              # warm-up: builds, sets kernel attributes, sizes the buffers
+                # warm-up (builds, sets kernel attributes, sizes the buffers) on a copy of the ids the step may read
+                keep = self._ids_d.clone()
+                self._eager(n_w)
                 torch.cuda.synchronize()
+                self._ids_d.copy_(keep)
                 g = torch.cuda.CUDAGraph()
                 before = ops.launches
                 with torch.cuda.graph(g):
@@ -187,24 +261,27 @@ class LLMEngine:
                 self._graphs[key] = g
             g.replay()
             ops.launches += self.launches_per_graph[key]
-            self.stats["graph_replays"] += 1
+            st["graph_replays"] += 1
             logits = runner.ws.get("logits", (n_w, self.model.spec.vocab_size), torch.float32)
         else:
             logits = self._eager(n_w)
         runner.commit(portions, starts)
+        n_tokens = 0
         for p, s in zip(portions, starts):
             self.seqs[p.req].num_computed = s + len(p.tokens)
-        ids = None
+            n_tokens += len(p.tokens)
         if n_w:
-            self._ids_h[:n_w].copy_(self._ids_d[:n_w], non_blocking=True)
+            self._ids_h[slot][:n_w].copy_(self._ids_d[:n_w], non_blocking=True)
         ops.errors_to_host()
+        event = None
         if self.model.device.type == "cuda":
-            torch.cuda.current_stream(self.model.device).synchronize()
-        if n_w:
-            ids = self._ids_h[:n_w].numpy()
-        self.stats["d2h_bytes"] += n_w * 4 + 4
-        ops.check_errors(copied=True)
-        return ids, logits
+            event = self._events[slot]
+            event.record(torch.cuda.current_stream(self.model.device))
+        st["d2h_bytes"] += n_w * 4 + 4
+        st["steps"] += 1
+        st["tokens"] += n_tokens
+        st[kind] += 1
+        return _Launched(rows, slot, logits, event, all_produce)
 
     def _eager(self, n_wanted: int) -> torch.Tensor:
         logits = self.runner.forward()

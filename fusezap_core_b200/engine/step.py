@@ -7,7 +7,7 @@ two fixed-shape forwards over one packed int32 upload (fusezap/serve/engine.py:1
 fusezap/serve/kv_cache.py:382-405, 471-513); here it is one forward of any shape.
 
 Per step the host packs one int32 block and copies it to the device once:
-  tokens[N] | pos[N] | seq_row[N] | sel[R] | segments[S x 4] | one block table (S x MB) per cache group
+  tokens[N] | pos[N] | seq_row[N] | src[N] | sel[R] | segments[S x 4] | one block table (S x MB) per cache group | tiles
 seq_row[n] is the row of the request's block table in this step (-1: padding row), sel the rows whose logits are
 wanted (-1: none), a segment is (first row, rows, first position, state slot) of one request's portion.
 """
@@ -33,6 +33,8 @@ class Portion:
     req: Hashable
     tokens: Sequence[int]
     want: Sequence[int] = ()
+    src: int = -1      # >= 0 (single-token portions only): the token is the id the previous step chose for its wanted
+                       # row `src`, taken on the device; `tokens` then only gives the count
 
 
 @dataclass
@@ -75,6 +77,7 @@ class StepMeta:
         self.o_tokens, o = o, o + max_rows
         self.o_pos, o = o, o + max_rows
         self.o_row, o = o, o + max_rows
+        self.o_src, o = o, o + max_rows
         self.o_sel, o = o, o + max_wanted
         self.o_seg, o = o, o + 4 * max_segments
         self.o_tab, o = o, o + num_groups * max_segments * pages_per_request
@@ -106,6 +109,8 @@ class StepMeta:
     @property
     def seq_row(self) -> torch.Tensor: return self.dev[self.o_row: self.o_row + self.n_rows]
     @property
+    def src(self) -> torch.Tensor: return self.dev[self.o_src: self.o_src + self.n_rows]
+    @property
     def sel(self) -> torch.Tensor: return self.dev[self.o_sel: self.o_sel + self.n_wanted]
     @property
     def seg(self) -> torch.Tensor: return self.dev[self.o_seg: self.o_seg + 4 * self.max_segments].view(self.max_segments, 4)
@@ -130,7 +135,8 @@ class StepMeta:
         if n_rows > self.max_rows or n_wanted > self.max_wanted or len(portions) > self.max_segments:
             raise ValueError(f"step of {n_rows} rows, {n_wanted} wanted, {len(portions)} requests exceeds the capacity "
                              f"({self.max_rows}, {self.max_wanted}, {self.max_segments})")
-        tok, pos, row = (a[o: o + n_rows] for o in (self.o_tokens, self.o_pos, self.o_row))
+        tok, pos, row, src = (a[o: o + n_rows] for o in (self.o_tokens, self.o_pos, self.o_row, self.o_src))
+        src[:] = -1
         sel = a[self.o_sel: self.o_sel + n_wanted]
         seg = a[self.o_seg: self.o_seg + 4 * self.max_segments].reshape(self.max_segments, 4)
         tok[n:], pos[n:], row[n:], sel[r:] = 0, 0, -1, -1
@@ -141,6 +147,10 @@ class StepMeta:
         for s, (p, start) in enumerate(zip(portions, starts)):
             k = len(p.tokens)
             tok[at: at + k] = np.asarray(p.tokens, dtype=np.int64)
+            if p.src >= 0:
+                if k != 1:
+                    raise ValueError(f"request {p.req!r}: only a single token can come from the previous step's ids")
+                src[at] = p.src
             pos[at: at + k] = np.arange(start, start + k)
             row[at: at + k] = s
             for j in p.want:
@@ -198,6 +208,7 @@ class StepRunner:
                              cache.max_pages_per_request)
         self.ws = Workspace(dev, max_rows)
         self.ctx = StepContext(self.ops, self.ws, self.meta, model.positions, model)
+        self.prev_ids: torch.Tensor | None = None     # device int32: the ids the previous step chose (see Portion.src)
         self.layer_caches: list[LayerCache] = []
         for n, e in enumerate(model.spec.schedule):
             need = model.layers[e.layer].mixer.cache_need()
@@ -214,7 +225,7 @@ class StepRunner:
         model, ctx, meta = self.model, self.ctx, self.meta
         spec = model.spec
         x = self.ws.get("x", (meta.n_rows, spec.hidden_size), torch.float32)
-        self.ops.embed(model.embed, meta.tokens, x)
+        self.ops.embed(model.embed, meta.tokens, x, meta.src if self.prev_ids is not None else None, self.prev_ids)
         delta = None
         for e, lc in zip(spec.schedule, self.layer_caches):
             x, delta = model.layers[e.layer].forward(ctx, x, delta, lc)

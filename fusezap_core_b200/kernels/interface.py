@@ -23,8 +23,10 @@ class Ops:
         """Raise ValueError if the attention kernels cannot take these sizes (nothing is ever computed wrongly)."""
         raise NotImplementedError
 
-    def embed(self, table: torch.Tensor, tokens: torch.Tensor, x: torch.Tensor) -> None:
-        """x[n, :] = float32(table[tokens[n], :]). tokens: int32 (N,). A token outside the table is an error."""
+    def embed(self, table: torch.Tensor, tokens: torch.Tensor, x: torch.Tensor, src: torch.Tensor | None = None,
+              prev_ids: torch.Tensor | None = None) -> None:
+        """x[n, :] = float32(table[tokens[n], :]). tokens: int32 (N,). A token outside the table is an error.
+        With src (int32 (N,)) and prev_ids (int32): a row with src[n] >= 0 uses token prev_ids[src[n]] instead."""
         raise NotImplementedError
 
     def add_rmsnorm(self, x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float,

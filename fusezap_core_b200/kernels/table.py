@@ -94,14 +94,18 @@ class CudaOps(Ops):
                              f"{head_dim} (need heads % kv_heads == 0, heads / kv_heads <= 32, head_dim <= 256)")
 
     # ---- kernels
-    def embed(self, table, tokens, x) -> None:
+    def embed(self, table, tokens, x, src=None, prev_ids=None) -> None:
         self._want(table, "embedding table", (torch.float32, torch.bfloat16), 2)
         self._want(tokens, "tokens", (torch.int32,), 1)
         self._want(x, "x", (torch.float32,), 2)
         n, d = x.shape
         if tokens.shape[0] != n or table.shape[1] != d:
             raise KernelError(f"embed: tokens {tuple(tokens.shape)}, table {tuple(table.shape)}, x {tuple(x.shape)}")
-        self._check(self.core.fz_embed(_p(table), c_int(_CODE[table.dtype]), _p(tokens), _p(x), c_int(n), c_int(d),
+        if src is not None:
+            self._want(src, "src", (torch.int32,), 1)
+            self._want(prev_ids, "prev_ids", (torch.int32,), 1)
+        self._check(self.core.fz_embed(_p(table), c_int(_CODE[table.dtype]), _p(tokens), _p(src),
+                                       _p(prev_ids if src is not None else None), _p(x), c_int(n), c_int(d),
                                        c_int(table.shape[0]), _p(self.err), self._stream()), "embed")
 
     def add_rmsnorm(self, x, delta, weight, eps, h, rows=None) -> None:

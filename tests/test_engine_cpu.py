@@ -9,7 +9,7 @@ from fusezap_core_b200 import LLMEngine, SamplingParams, load_model
 from fusezap_core_b200.cache import CacheManager, OutOfPages
 from fusezap_core_b200.engine import Portion, StepRunner
 from plain_ops import PlainOps
-from util import make_model_dir, prompts, read_weights
+from util import lookahead_scenario, make_model_dir, prompts, read_weights
 
 
 @pytest.fixture(scope="module")
@@ -182,3 +182,17 @@ def test_layer_order_is_data(models, tmp_path):
     np.testing.assert_allclose(cut, whole, rtol=1e-4, atol=2e-5)
     own = plain_model.forward(cfg, w, ids, schedule=[0, 1, 1]).numpy()
     assert np.abs(whole - own).max() > 1e-3
+
+
+def test_launching_ahead_changes_no_token(models):
+    """A decode step launched before the host has read the one before it (its tokens taken from the ids on the device)
+    gives the same tokens, ends and reasons as stepping one at a time: through a stop token (the extra token is
+    dropped), a length limit (the request is left out), an arrival (looking ahead pauses) and an abort."""
+    model, cfg, opts, w = models["tiny_llama"]
+    plain, _, _ = lookahead_scenario(model, opts["page_size"], cfg)
+    stop = plain[3][12][0]          # request 3's 13th token: it stops there, or earlier if the token comes before
+    a, b, eng = lookahead_scenario(model, opts["page_size"], cfg, stop_from=stop)
+    assert a == b
+    assert eng.stats["lookahead_steps"] > 5
+    assert a[3][-1][1:] == (True, "stop") and len(a[3]) <= 13
+    assert a[1][-1] == ((), True, "abort") and a[0][-1][1:] == (True, "length") and len(a[2]) == 17

@@ -10,7 +10,7 @@ import pytest
 import torch
 
 import plain_model
-from util import ROOT, make_model_dir, plain_logits, prompts, read_weights
+from util import ROOT, lookahead_scenario, make_model_dir, plain_logits, prompts, read_weights
 
 pytestmark = pytest.mark.gpu
 
@@ -74,6 +74,27 @@ def test_long_decoding_and_first_tokens(folders, dtype):
     toks = eng.generate([[17]], SamplingParams(max_tokens=200, ignore_eos=True))[0]
     assert len(toks) == 200
     follows_plain_model(cfg, w, dtype, [17], toks, 1e-3 if dtype == "float32" else 0.15)
+
+
+@pytest.mark.parametrize("dtype,graphs", [("float32", True), ("float32", False), ("bfloat16", True)])
+def test_launching_ahead_changes_no_token(folders, dtype, graphs):
+    """Decode steps launched before the host has read the step before (their tokens taken from the ids on the device)
+    give the same tokens, ends and reasons as one step at a time, through a stop token, length limits, a late arrival
+    and an abort. In bfloat16 without the stop token: a request that runs one token too many would change the batch
+    size of that step, and with it the rounding of the others."""
+    from fusezap_core_b200 import load_model
+    d, cfg, opts = folders["tiny_llama"]
+    model = load_model(d, dtype, "cuda:0", max_len=128)
+    stop = None
+    if dtype == "float32":
+        plain, _, _ = lookahead_scenario(model, opts["page_size"], cfg, graphs)
+        stop = plain[3][12][0]
+    a, b, eng = lookahead_scenario(model, opts["page_size"], cfg, graphs, stop_from=stop)
+    assert a == b
+    assert eng.stats["lookahead_steps"] > 5
+    if stop is not None:
+        assert a[3][-1][1:] == (True, "stop")
+    assert a[1][-1] == ((), True, "abort") and a[0][-1][1:] == (True, "length") and len(a[2]) == 17
 
 
 def test_seeded_sampling_on_the_device(folders):

@@ -74,6 +74,13 @@ def test_embed(dtype):
     pl.embed(table, tok, xr)
     assert torch.equal(x.cpu(), xr)
     cu.check_errors()
+    # some rows take their token from another buffer on the device (the ids the step before chose)
+    src = torch.full((37,), -1, dtype=torch.int32); src[[0, 9, 36]] = torch.tensor([4, 0, 2], dtype=torch.int32)
+    prev = torch.tensor([100, 7, 508, 3, 250], dtype=torch.int32)
+    cu.embed(table.cuda(), tok.cuda(), x, src.cuda(), prev.cuda())
+    pl.embed(table, tok, xr, src, prev)
+    assert torch.equal(x.cpu(), xr) and torch.equal(xr[9], table[100].float()) and torch.equal(xr[1], table[tok[1]].float())
+    cu.check_errors()
     bad = tok.clone(); bad[5] = 509
     cu.embed(table.cuda(), bad.cuda(), x)
     from fusezap_core_b200.kernels.table import KernelError

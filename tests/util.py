@@ -131,3 +131,34 @@ class TraceBuilder:
             for (rid, p), row in zip(where, a):
                 got.setdefault(rid, {})[p] = row
         return got
+
+
+def lookahead_scenario(model, page_size, cfg, graphs=True, stop_from=None):
+    """Runs one fixed story (different lengths, a stop token, a device-sampled request, a late arrival, an abort) with
+    and without launching steps ahead and returns both per-request records and the engine that looked ahead."""
+    from fusezap_core_b200 import LLMEngine, SamplingParams
+    P = prompts(cfg, (5, 11, 3, 8, 6), seed=21)
+    res = {}
+    for ahead in (False, True):
+        eng = LLMEngine(model, num_blocks=96, block_size=page_size, max_num_seqs=4, max_prefill_tokens=16,
+                        max_model_len=96, cuda_graphs=graphs, lookahead=ahead)
+        ps = [SamplingParams(max_tokens=3, ignore_eos=True), SamplingParams(max_tokens=25, ignore_eos=True),
+              SamplingParams(max_tokens=17, temperature=0.7, seed=3, ignore_eos=True),
+              SamplingParams(max_tokens=30, ignore_eos=True, stop_token_ids=list(stop_from or ())),
+              SamplingParams(max_tokens=9, ignore_eos=True)]
+        rids = [eng.add_request(P[i], ps[i]) for i in range(4)]
+        rec = {r: [] for r in rids}
+        n = 0
+        while eng.has_unfinished():
+            for o in eng.step():
+                rec[o.request_id].append((tuple(o.new_token_ids), o.finished, o.finish_reason))
+            n += 1
+            if n == 7:
+                r = eng.add_request(P[4], ps[4]); rec[r] = []; rids.append(r)
+            if n == 15:
+                o = eng.abort(rids[1])
+                rec[rids[1]].append(((), o.finished, o.finish_reason))
+        assert eng.cache.num_free_pages == 96
+        eng.cache.check()
+        res[ahead] = (rec, eng)
+    return res[False][0], res[True][0], res[True][1]
