@@ -1,21 +1,19 @@
-// Paged attention for decoded tokens and short portions, bf16 cache, on tensor cores, split over key partitions.
+// Paged attention for decoded tokens and short portions, bf16 cache, on tensor cores, split along the keys.
 //
-// grid (partitions, kv heads, token rows), 128 threads. A CTA serves one token row, one kv head and one partition of
-// PART = 256 consecutive key positions (partition i holds keys 256 i .. 256 i + 255, whatever the batch: a row's sums
-// have one order that depends only on its own position). All G = Hq / Hkv query heads of the kv head are the rows of
-// the 16-row MMA tile, so the keys and values of the partition are read once for the whole group (the reference's
-// default decode kernel lays the group out the same way: fusezap/device/cuda_kernels/attention.py:860-1043).
-// Keys and values come in tiles of 64 through a three-stage cp.async ring; warp w owns keys 16 w .. 16 w + 15 of each
-// tile: S = Q K^T and O += P V with mma.sync m16n8k16, softmax online in the exp2 domain with float32 max and sum, P
-// rounded to bf16 for the second product. The four warps' (max, sum, O) are merged in warp order, and the partition's
-// unnormalised O with its (max, sum) goes to a float32 scratch; `attn_combine_kernel` merges a row's partitions in
-// rising order and normalises. Rows of portions with at least `long_from` tokens are left to the prefill kernel.
+// All G = Hq / Hkv query heads of a kv head are the rows of the 16-row MMA tile, so keys and values are read once for the
+// whole group (the reference's default decode kernel lays the group out the same way:
+// fusezap/device/cuda_kernels/attention.py:860-1043). S = Q K^T and O += P V with mma.sync m16n8k16 on 16 keys at a
+// time, softmax online in the exp2 domain with float32 max and sum, P rounded to bf16 for the second product. The key
+// axis is cut at fixed positions (the same for every request and batch: a row's sums have one order that depends on
+// its own position only); each piece leaves its unnormalised O and (max, sum) in a float32 scratch, and a combine
+// kernel merges a row's pieces in rising order and normalises. Rows of portions with at least `long_from` tokens are
+// left to the prefill kernel.
 //
-// Two variants load the keys and values. `attn_decode_tma_kernel` (page sizes 8, 16 and multiples of 16): every warp
-// fetches its own 16-key groups with TMA tile loads (a page's rows of one kv head are one box of the pool seen as a
-// 2-D array of rows; 128-byte swizzle) into a two-deep ring of its own, guarded by mbarriers, with no block-wide
-// barrier in the loop; this is what keeps enough bytes in flight for HBM3e. `attn_decode_kernel` (any page size)
-// gathers 64-key tiles with cp.async through a three-stage ring.
+// Two variants. `attn_decode_units_kernel` (page sizes 8, 16 and multiples of 16; see there): a persistent grid whose
+// warps each take an equal share of the step's 64-key units and fetch them with TMA tile loads through rings of their
+// own; this is what keeps HBM3e busy at small and large batches alike. `attn_decode_kernel` (any page size): grid
+// (partitions of 256 keys, kv heads, token rows); a CTA gathers its partition in 64-key tiles with cp.async through a
+// three-stage ring, warp w owns keys 16 w .. 16 w + 15 of each tile, and the four warps' results are merged in warp order.
 #include "attn_mma.cuh"
 #include "tma.cuh"
 #include <math.h>
@@ -85,6 +83,61 @@ __device__ __forceinline__ void attend16(const uint32_t (&qf)[HD / 16][4], KAddr
   }
 }
 
+// The same for groups of at most 8 query heads, with the products transposed so that no MMA row is padding: the 16 keys
+// are the rows of S^T = K Q^T (16 x 8 heads), and O^T += V^T P^T has 16 head dimensions as rows and the heads as its 8
+// columns. Half the MMAs, half the accumulators and half the exponentials of `attend16`. A thread holds, of S^T, keys
+// lane / 4 and lane / 4 + 8 for heads 2 (lane % 4) + {0, 1}; of O^T block i, dimensions 16 i + lane / 4 (+ 8) for the
+// same two heads. m_run / l_run are per head (l_run: this thread's keys only; the caller adds the lanes of a head up).
+// qf[ks] = Q[head lane / 4][16 ks + 2 (lane % 4) + {0, 1}] and the same + 8 (zero for heads past the group).
+template <int HD, typename KAddr, typename VAddr>
+__device__ __forceinline__ void attend16_small(const uint32_t (&qf)[HD / 16][2], KAddr kaddr, VAddr vaddr, int key_first,
+                                               int lo, int p, float scale_log2, float (&o)[HD / 16][4], float (&m_run)[2],
+                                               float (&l_run)[2], int lane) {
+  constexpr int KSTEPS = HD / 16, DB = HD / 16;
+  float s[4] = {0.f, 0.f, 0.f, 0.f}, s2[4] = {0.f, 0.f, 0.f, 0.f};    // even and odd k-steps: two chains in flight
+#pragma unroll
+  for (int ks = 0; ks < KSTEPS; ks += 2) {
+    uint32_t kf[4], kg[4];
+    ldmatrix_x4(kf, kaddr(lane & 15, ks * 2 + (lane >> 4)));
+    ldmatrix_x4(kg, kaddr(lane & 15, ks * 2 + 2 + (lane >> 4)));
+    mma_bf16(s, kf, qf[ks][0], qf[ks][1]);
+    mma_bf16(s2, kg, qf[ks + 1][0], qf[ks + 1][1]);
+  }
+  const int key_a = key_first + (lane >> 2), key_b = key_a + 8;
+  const bool va = key_a >= lo && key_a <= p, vb = key_b >= lo && key_b <= p;
+  s[0] = va ? (s[0] + s2[0]) * scale_log2 : -INFINITY;
+  s[1] = va ? (s[1] + s2[1]) * scale_log2 : -INFINITY;
+  s[2] = vb ? (s[2] + s2[2]) * scale_log2 : -INFINITY;
+  s[3] = vb ? (s[3] + s2[3]) * scale_log2 : -INFINITY;
+  float corr[2], mu[2];
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    float mx = fmaxf(s[j], s[j + 2]);
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+    const float mn = fmaxf(m_run[j], mx);
+    mu[j] = mn == -INFINITY ? 0.f : mn;        // no visible key yet: every exponent below is exp2(-inf) = 0
+    corr[j] = exp2f(m_run[j] - mu[j]);
+    m_run[j] = mn;
+  }
+  const float e0 = exp2f(s[0] - mu[0]), e1 = exp2f(s[1] - mu[1]), e2 = exp2f(s[2] - mu[0]), e3 = exp2f(s[3] - mu[1]);
+  l_run[0] = l_run[0] * corr[0] + (e0 + e2);
+  l_run[1] = l_run[1] * corr[1] + (e1 + e3);
+  // P (keys x heads, in the accumulator layout) -> P^T as the B operand: one 8 x 8 transpose per 8 keys
+  uint32_t pb0, pb1;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(pb0) : "r"(pack_bf16(e0, e1)));
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(pb1) : "r"(pack_bf16(e2, e3)));
+#pragma unroll
+  for (int i = 0; i < DB; ++i) { o[i][0] *= corr[0]; o[i][1] *= corr[1]; o[i][2] *= corr[0]; o[i][3] *= corr[1]; }
+#pragma unroll
+  for (int i = 0; i < DB; ++i) {
+    uint32_t vf[4];      // V^T: dimensions 16 i .. + 15 as rows, the 16 keys as columns
+    ldmatrix_x4_trans(vf, vaddr((lane & 7) + 8 * (lane >> 4), 2 * i + ((lane >> 3) & 1)));
+    mma_bf16(o[i], vf, pb0, pb1);
+  }
+}
+
 // Merges the four warps' (max, sum, O) in warp order and writes the partition's unnormalised O and (max, sum).
 // `scratch` is shared memory for [4][16][HD] + [4][16][2] floats; the caller has synchronised the block before.
 template <int HD>
@@ -139,8 +192,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                    const int* __restrict__ seq_row, const int* __restrict__ seg, const int* __restrict__ table, int mb,
                    long long page_stride, int page_size, float* __restrict__ part_o, float* __restrict__ part_ml,
                    int Hq, int Hkv, float scale_log2, int window, int long_from) {
-  fz_grid_wait();
   fz_grid_launch_dependents();
+  fz_grid_wait();
   constexpr int KSTEPS = HD / 16;      // k-steps of Q K^T
   constexpr int NB = HD / 8;           // 8-wide output blocks of P V
   extern __shared__ __align__(128) uint8_t smem[];
@@ -211,86 +264,163 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 }
 
 // ---------------------------------------------------------------------------------------------- TMA variant
+// Key positions are cut into *units*, the same for every request and every batch: keys [0, 4096) in units of 64, later
+// keys in units of 256. One warp computes one unit on its own (its 16-key groups one after the other, online softmax)
+// and writes the unit's unnormalised O and (max, sum) from its registers; nothing is merged inside the kernel, so a
+// row's arithmetic depends on its own position only. The grid is persistent: all units of all (row, kv head) pairs
+// of the step are numbered (row, then kv head, then position), and warp w of W takes the units [T w / W, T (w + 1) / W),
+// so the SMs stay equally loaded whatever the batch and the contexts are. Every warp runs a TMA ring of its own
+// (NSTAGE groups of 16 keys, K and V) that runs ahead across unit boundaries: the loads of the next unit are in flight
+// while this one's partial is written.
+//
 // kv_map: the cache slot's pool seen as a row-major [pages * 2 * Hkv * page_size, HD] bf16 array (row of key `off` of kv
 // head `kvh` of page `pg`: pg * 2 Hkv bs + kvh * bs + off; its value row: + Hkv * bs), boxes of BOX rows x 64 columns.
-// Shared memory per warp: 2 stages x [K | V], each HD / 64 column halves of [16 rows][128 bytes], swizzled by TMA.
-constexpr int TMA_DEPTH = 2;
+// Shared memory per warp: NSTAGE x [K | V], each HD / 64 column halves of [16 rows][128 bytes], swizzled by TMA.
+constexpr int UNIT_SMALL = 64, UNIT_BIG = 256, SMALL_UNITS = 64;
+constexpr int SMALL_KEYS = UNIT_SMALL * SMALL_UNITS;
+constexpr int MAX_UNIT_ROWS = 4096;      // token rows the unit kernel numbers in shared memory
 
-template <int HD, int BOX>
-__global__ void __launch_bounds__(THREADS)
-attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bfloat16* __restrict__ q,
-                       const int* __restrict__ pos, const int* __restrict__ seq_row, const int* __restrict__ seg,
-                       const int* __restrict__ table, int mb, int page_size, float* __restrict__ part_o,
-                       float* __restrict__ part_ml, int Hq, int Hkv, float scale_log2, int window, int long_from,
-                       int* err) {
-  constexpr int KSTEPS = HD / 16, NB = HD / 8, HALVES = HD / 64;
+__host__ __device__ __forceinline__ int unit_of(int key) {
+  return key < SMALL_KEYS ? key / UNIT_SMALL : SMALL_UNITS + (key - SMALL_KEYS) / UNIT_BIG;
+}
+__host__ __device__ __forceinline__ int unit_start(int u) {
+  return u < SMALL_UNITS ? u * UNIT_SMALL : SMALL_KEYS + (u - SMALL_UNITS) * UNIT_BIG;
+}
+__host__ __device__ __forceinline__ int unit_len(int u) { return u < SMALL_UNITS ? UNIT_SMALL : UNIT_BIG; }
+
+// Where a warp stands in its list of units: the unit's row, kv head and key range, and the next 16-key group.
+struct UnitCursor {
+  int u;            // number of the unit among the step's units
+  int n, kvh;       // token row, kv head
+  int unit;         // which unit of the key axis
+  int p, lo;        // the row attends keys lo .. p
+  int key0;         // first key of the unit
+  int g, g_end;     // next group of 16 keys in the unit, one past the last
+  int page0;        // first block-table entry the unit's groups need ...
+  int pages;        // ... and entry page0 + lane of the table (-1 past the row's position), one per lane
+  bool valid;
+};
+
+template <int HD, int BOX, int NSTAGE, int MINB, bool SMALLG>
+__global__ void __launch_bounds__(THREADS, MINB)
+attn_decode_units_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bfloat16* __restrict__ q,
+                         const int* __restrict__ pos, const int* __restrict__ seq_row, const int* __restrict__ seg,
+                         const int* __restrict__ table, int mb, int page_size, float* __restrict__ part_o,
+                         float* __restrict__ part_ml, int N, int Hq, int Hkv, int NPU, float scale_log2, int window,
+                         int long_from, int* err) {
+  // SMALLG (at most 8 query heads per kv head): the transposed products of `attend16_small`
+  constexpr int KSTEPS = HD / 16, OB = SMALLG ? HD / 16 : HD / 8, QW = SMALLG ? 2 : 4, HALVES = HD / 64;
   constexpr int HALF_BYTES = 16 * 128;                 // one column half of a 16-key group
   constexpr int KV_BYTES = HALVES * HALF_BYTES;        // keys (or values) of a group
   constexpr int STAGE_BYTES = 2 * KV_BYTES;
-  constexpr int WARP_BYTES = TMA_DEPTH * STAGE_BYTES;
+  constexpr int WARP_BYTES = NSTAGE * STAGE_BYTES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t s_base = smem_u32(smem);
-  const uint32_t s_q = s_base + 4 * WARP_BYTES;
-  uint64_t* bars = (uint64_t*)(smem + 4 * WARP_BYTES + 16 * HD * 2);    // [4 warps][TMA_DEPTH]
+  uint64_t* bars = (uint64_t*)(smem + 4 * WARP_BYTES);                   // [4 warps][NSTAGE]
+  int* s_pre = (int*)(bars + 4 * NSTAGE);                                // [N + 1]: units before row n
 
   // Prologue that depends on nothing another kernel writes: barriers, and zeros in the staging buffers (a box that is
-  // not fetched because it lies past the row's position must not hold another block's bits: P = 0 times NaN is NaN).
+  // not fetched because it lies past the row's position must hold finite bits: P = 0 times NaN is NaN).
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
-    for (int i = 0; i < 4 * TMA_DEPTH; ++i) fztma::mbar_init(&bars[i], 1);
+    for (int i = 0; i < 4 * NSTAGE; ++i) fztma::mbar_init(&bars[i], 1);
     fztma::mbar_init_fence();
   }
   for (int e = tid; e < 4 * WARP_BYTES / 16; e += THREADS) ((uint4*)smem)[e] = make_uint4(0u, 0u, 0u, 0u);
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   __syncthreads();
-  fz_grid_wait();
   fz_grid_launch_dependents();
+  // What follows up to the wait reads only the step's metadata (positions, rows, block tables): the host wrote it before
+  // the step's first kernel started and no kernel changes it, so it may be read while the kernel before this one runs.
 
-  const int part = blockIdx.x, kvh = blockIdx.y, n = blockIdx.z, NP = gridDim.x;
   const int G = Hq / Hkv;
-  const int row = seq_row[n];
-  if (row < 0) return;
-  if (seg[row * 4 + 1] >= long_from) return;
-  const int p = pos[n];
-  const int lo = window > 0 ? max(0, p - window + 1) : 0;
-  const int k_begin = max(part * PART, lo & ~(TILE - 1)), k_end = min((part + 1) * PART, p + 1);
-  float* ml_out = part_ml + (((size_t)n * Hq + (size_t)kvh * G) * NP + part) * 2;
-  if (k_begin >= k_end) {
-    for (int g = tid; g < G; g += THREADS) { ml_out[(size_t)g * NP * 2] = -INFINITY; ml_out[(size_t)g * NP * 2 + 1] = 0.f; }
-    return;
-  }
-  const int* trow = table + (size_t)row * mb;
-  const int rows_per_page = 2 * Hkv * page_size;
-  {
-    const __nv_bfloat16* qrow = q + (size_t)n * Hq * HD + (size_t)kvh * G * HD;
-    for (int e = tid; e < 16 * (HD / 8); e += THREADS) {
-      const int r = e / (HD / 8), c = e - r * (HD / 8);
-      cp_async16(s_q + swz<HD>(r, c), qrow + (size_t)r * HD + c * 8, r < G);
+  // units of every row (0 for padding rows and for rows of long portions), then their running sum
+  for (int n = tid; n < N; n += THREADS) {
+    const int row = seq_row[n];
+    int cnt = 0;
+    if (row >= 0 && seg[row * 4 + 1] < long_from) {
+      const int p = pos[n];
+      const int lo = window > 0 ? max(0, p - window + 1) : 0;
+      cnt = (unit_of(p) - unit_of(lo) + 1) * Hkv;
     }
-    cp_async_commit();
+    s_pre[n + 1] = cnt;
   }
-  // this warp's groups of 16 keys: group g holds keys k_begin + 16 g .., g = warp, warp + 4, ...
-  const int n_groups = (k_end - k_begin + 15) / 16;
-  const int my_groups = n_groups > warp ? (n_groups - warp + 3) / 4 : 0;
+  if (tid == 0) s_pre[0] = 0;
+  __syncthreads();
+  if (warp == 0) {
+    int carry = 0;
+    for (int base = 0; base < N; base += 32) {
+      const int i = base + lane;
+      int v = i < N ? s_pre[i + 1] : 0;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, v, d);
+        if (lane >= d) v += t;
+      }
+      if (i < N) s_pre[i + 1] = v + carry;
+      carry += __shfl_sync(0xffffffffu, v, 31);
+    }
+  }
+  __syncthreads();
+  // from here on the warps go their own ways: no block-wide barrier below
+  const long long T = s_pre[N];
+  const long long gw = (long long)blockIdx.x * 4 + warp, W = (long long)gridDim.x * 4;
+  const int u_begin = (int)(T * gw / W), u_end = (int)(T * (gw + 1) / W);
+  if (u_begin >= u_end) { fz_grid_wait(); return; }
+
+  auto load_unit = [&](UnitCursor& c, int u, int n_hint, bool with_pages) {
+    c.u = u;
+    c.valid = u < u_end;
+    if (!c.valid) return;
+    int n = n_hint;
+    if (!(s_pre[n] <= u && u < s_pre[n + 1])) {      // the largest n with s_pre[n] <= u
+      int a = 0, b = N - 1;
+      while (a < b) {
+        const int mid = (a + b + 1) >> 1;
+        if (s_pre[mid] <= u) a = mid; else b = mid - 1;
+      }
+      n = a;
+    }
+    const int r = u - s_pre[n], per_head = (s_pre[n + 1] - s_pre[n]) / Hkv;
+    c.n = n;
+    c.kvh = r / per_head;
+    c.p = pos[n];
+    c.lo = window > 0 ? max(0, c.p - window + 1) : 0;
+    c.unit = unit_of(c.lo) + (r - c.kvh * per_head);
+    c.key0 = unit_start(c.unit);
+    c.g = c.lo > c.key0 ? (c.lo - c.key0) >> 4 : 0;
+    c.g_end = min(unit_len(c.unit) >> 4, ((c.p - c.key0) >> 4) + 1);
+    // the unit's block-table entries, one per lane (at most 32: 256 keys in pages of 8), asked for now and used
+    // when the unit's loads are issued
+    if (!with_pages) return;
+    c.page0 = (c.key0 + 16 * c.g) / page_size;
+    const int pi = c.page0 + lane;
+    c.pages = (pi < mb && pi * page_size <= c.p) ? __ldg(table + (size_t)seq_row[n] * mb + pi) : -1;
+  };
+
   const uint32_t s_warp = s_base + warp * WARP_BYTES;
-  auto issue = [&](int j) {        // lane 0 only
-    const int stage = j % TMA_DEPTH;
-    const int key0 = k_begin + 16 * (warp + 4 * j);
-    uint64_t* bar = &bars[warp * TMA_DEPTH + stage];
+  uint64_t* wbars = bars + warp * NSTAGE;
+  const int rows_per_page = 2 * Hkv * page_size;
+  // keys and values are read once per step: they should leave L2 before the partial results, which are read again
+  const uint64_t stream_once = fztma::l2_evict_first();
+  auto issue = [&](const UnitCursor& c, int stage) {        // the whole warp (the pages sit in the lanes); lane 0 loads
+    const int key0 = c.key0 + 16 * c.g;
+    uint64_t* bar = &wbars[stage];
     int rows[16 / BOX];
     uint32_t bytes = 0;
 #pragma unroll
     for (int sub = 0; sub < 16 / BOX; ++sub) {
       const int key = key0 + sub * BOX;
       rows[sub] = -1;
-      if (key > p || key + BOX - 1 < lo) continue;       // nothing visible in this box
       const int pi = key / page_size;
-      const int page = trow[pi];
-      if (page < 0) { atomicOr(err, FZ_ERR_NO_PAGE); continue; }
-      rows[sub] = page * rows_per_page + kvh * page_size + (key - pi * page_size);
+      const int page = __shfl_sync(0xffffffffu, c.pages, (pi - c.page0) & 31);
+      if (key > c.p || key + BOX - 1 < c.lo) continue;       // nothing visible in this box
+      if (page < 0) { if (lane == 0) atomicOr(err, FZ_ERR_NO_PAGE); continue; }
+      rows[sub] = page * rows_per_page + c.kvh * page_size + (key - pi * page_size);
       bytes += 2 * HALVES * BOX * 128;
     }
+    if (lane != 0) return;
     fztma::mbar_expect_tx(bar, bytes);
     const uint32_t sk = s_warp + stage * STAGE_BYTES, sv = sk + KV_BYTES, b = smem_u32(bar);
 #pragma unroll
@@ -298,48 +428,172 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bf
       if (rows[sub] < 0) continue;
 #pragma unroll
       for (int h = 0; h < HALVES; ++h) {
-        fztma::tma_load_2d_u32(sk + h * HALF_BYTES + sub * BOX * 128, &kv_map, b, 64 * h, rows[sub]);
-        fztma::tma_load_2d_u32(sv + h * HALF_BYTES + sub * BOX * 128, &kv_map, b, 64 * h, rows[sub] + Hkv * page_size);
+        fztma::tma_load_2d_u32_hint(sk + h * HALF_BYTES + sub * BOX * 128, &kv_map, b, 64 * h, rows[sub], stream_once);
+        fztma::tma_load_2d_u32_hint(sv + h * HALF_BYTES + sub * BOX * 128, &kv_map, b, 64 * h, rows[sub] + Hkv * page_size, stream_once);
       }
     }
   };
-  if (lane == 0) {
+
+  // where the arithmetic stands, where the loads stand, and the unit after that one (its block-table entries are on
+  // their way while the loads of the unit before it are issued)
+  UnitCursor cc, ci, cn;
+  load_unit(cc, u_begin, 0, false);
+  load_unit(ci, u_begin, 0, true);
+  load_unit(cn, u_begin + 1, ci.n, true);
+  fz_grid_wait();      // the queries and the newest keys and values come from the kernels before
+  auto advance_loads = [&]() {
+    if (++ci.g >= ci.g_end) {
+      ci = cn;
+      if (ci.valid) load_unit(cn, ci.u + 1, ci.n, true);
+    }
+  };
+  int issued = 0, consumed = 0;
+  int q_n = -1, q_kvh = -1;
+  uint32_t qf[KSTEPS][QW];
+  float o[OB][4];
+  float m_run[2], l_run[2];
+  bool fresh = true;
+  while (cc.valid) {
+    while (ci.valid && issued - consumed < NSTAGE) {
+      issue(ci, issued % NSTAGE);
+      ++issued;
+      advance_loads();
+    }
+    if (cc.n != q_n || cc.kvh != q_kvh) {
+      // another row or kv head: its G query heads, read from global memory straight into the MMA fragments
+      q_n = cc.n; q_kvh = cc.kvh;
+      const uint32_t* qw = (const uint32_t*)(q + ((size_t)q_n * Hq + (size_t)q_kvh * G) * HD);
+      const int r0 = lane >> 2, cw = lane & 3;
+      if constexpr (SMALLG) {
+        // B operand (Q^T): head lane / 4, dimensions 2 (lane % 4) + {0, 1} and + 8 of every 16; zero past the group
 #pragma unroll
-    for (int j = 0; j < TMA_DEPTH; ++j)
-      if (j < my_groups) issue(j);
-  }
-  cp_async_wait<0>();
-  __syncthreads();
-  uint32_t qf[KSTEPS][4];
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+          qf[ks][0] = r0 < G ? qw[(r0 * HD + 16 * ks) / 2 + cw] : 0u;
+          qf[ks][1] = r0 < G ? qw[(r0 * HD + 16 * ks + 8) / 2 + cw] : 0u;
+        }
+      } else {
+        // A operand: lane l holds rows (heads) l / 4 and l / 4 + 8, columns 2 (l % 4) + {0, 1} and + 8 of every 16
 #pragma unroll
-  for (int ks = 0; ks < KSTEPS; ++ks) ldmatrix_x4(qf[ks], s_q + swz<HD>(lane & 15, ks * 2 + (lane >> 4)));
-  float o[NB][4];
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+          qf[ks][0] = r0 < G ? qw[(r0 * HD + 16 * ks) / 2 + cw] : 0u;
+          qf[ks][1] = r0 + 8 < G ? qw[((r0 + 8) * HD + 16 * ks) / 2 + cw] : 0u;
+          qf[ks][2] = r0 < G ? qw[(r0 * HD + 16 * ks + 8) / 2 + cw] : 0u;
+          qf[ks][3] = r0 + 8 < G ? qw[((r0 + 8) * HD + 16 * ks + 8) / 2 + cw] : 0u;
+        }
+      }
+    }
+    if (fresh) {
 #pragma unroll
-  for (int i = 0; i < NB; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
-  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
-  bool timed_out = false;
-  for (int j = 0; j < my_groups; ++j) {
-    const int stage = j % TMA_DEPTH;
-    if (!__all_sync(0xffffffffu, fztma::mbar_wait(&bars[warp * TMA_DEPTH + stage], (j / TMA_DEPTH) & 1))) { timed_out = true; break; }
+      for (int i = 0; i < OB; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+      m_run[0] = m_run[1] = -INFINITY;
+      l_run[0] = l_run[1] = 0.f;
+      fresh = false;
+    }
+    const int stage = consumed % NSTAGE;
+    if (!__all_sync(0xffffffffu, fztma::mbar_wait(&wbars[stage], (consumed / NSTAGE) & 1))) {
+      if (lane == 0) atomicOr(err, FZ_ERR_WAIT_TIMEOUT);
+      return;
+    }
     const uint32_t sk = s_warp + stage * STAGE_BYTES, sv = sk + KV_BYTES;
     // chunk c of row r: column half c >> 3, 16-byte chunk (c & 7) ^ (r & 7) of the 128-byte row (TMA's swizzle)
-    attend16<HD>(qf, [&](int r, int c) { return sk + (c >> 3) * HALF_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4); },
-                 [&](int r, int c) { return sv + (c >> 3) * HALF_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4); },
-                 k_begin + 16 * (warp + 4 * j), lo, p, scale_log2, o, m_run, l_run, lane);
-    __syncwarp();
-    if (lane == 0 && j + TMA_DEPTH < my_groups) issue(j + TMA_DEPTH);
+    auto kaddr = [&](int r, int c) { return sk + (c >> 3) * HALF_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4); };
+    auto vaddr = [&](int r, int c) { return sv + (c >> 3) * HALF_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4); };
+    if constexpr (SMALLG) attend16_small<HD>(qf, kaddr, vaddr, cc.key0 + 16 * cc.g, cc.lo, cc.p, scale_log2, o, m_run, l_run, lane);
+    else attend16<HD>(qf, kaddr, vaddr, cc.key0 + 16 * cc.g, cc.lo, cc.p, scale_log2, o, m_run, l_run, lane);
+    __syncwarp();        // every lane has read the stage: it may be refilled
+    ++consumed;
+    if (cc.g + 1 >= cc.g_end) {
+      // the unit is complete: its unnormalised O and (max, sum), straight from the MMA fragments
+      const size_t head0 = (size_t)cc.n * Hq + (size_t)cc.kvh * G;
+      if constexpr (SMALLG) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          l_run[j] += __shfl_xor_sync(0xffffffffu, l_run[j], 4);
+          l_run[j] += __shfl_xor_sync(0xffffffffu, l_run[j], 8);
+          l_run[j] += __shfl_xor_sync(0xffffffffu, l_run[j], 16);
+          const int g = 2 * (lane & 3) + j;
+          if (g < G) {
+            const size_t slot = (head0 + g) * NPU + cc.unit;
+            float* dst = part_o + slot * HD + (lane >> 2);
+#pragma unroll
+            for (int i = 0; i < OB; ++i) { dst[16 * i] = o[i][j]; dst[16 * i + 8] = o[i][2 + j]; }
+            if ((lane >> 2) == 0) *(float2*)(part_ml + slot * 2) = make_float2(m_run[j], l_run[j]);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+          l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int g = (lane >> 2) + 8 * h;
+          if (g < G) {
+            const size_t slot = (head0 + g) * NPU + cc.unit;
+            float* dst = part_o + slot * HD + 2 * (lane & 3);
+#pragma unroll
+            for (int i = 0; i < OB; ++i) *(float2*)(dst + 8 * i) = make_float2(o[i][2 * h], o[i][2 * h + 1]);
+            if ((lane & 3) == 0) *(float2*)(part_ml + slot * 2) = make_float2(m_run[h], l_run[h]);
+          }
+        }
+      }
+      fresh = true;
+    }
+    if (++cc.g >= cc.g_end) load_unit(cc, cc.u + 1, cc.n, false);
   }
-  if (timed_out && lane == 0) atomicOr(err, FZ_ERR_WAIT_TIMEOUT);
-  __syncthreads();     // every warp has consumed all it requested: the staging buffers are free for the merge
-  merge_and_store<HD>((float*)smem, o, m_run, l_run, part_o, ml_out, n, Hq, kvh, G, NP, part, tid);
+}
+
+// One block per (token row, query head): merges the row's units in rising order, normalises, rounds to bf16. The
+// units a row has follow from its position and the window alone, as in the kernel above.
+__global__ void attn_combine_units_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                          const int* __restrict__ pos, const int* __restrict__ seq_row,
+                                          const int* __restrict__ seg, __nv_bfloat16* __restrict__ out, int Hq, int HD,
+                                          int NPU, int window, int long_from) {
+  extern __shared__ float s_f[];      // [units of the row]: exp2(max_i - max), then 2 floats of scratch per warp
+  fz_grid_launch_dependents();
+  fz_grid_wait();
+  const int n = blockIdx.y, h = blockIdx.x, tid = threadIdx.x, nthreads = blockDim.x;
+  __nv_bfloat16* orow = out + ((size_t)n * Hq + h) * HD;
+  const int row = seq_row[n];
+  if (row < 0) {
+    for (int d = tid; d < HD; d += nthreads) orow[d] = __float2bfloat16_rn(0.f);
+    return;
+  }
+  if (seg[row * 4 + 1] >= long_from) return;
+  const int p = pos[n];
+  const int lo = window > 0 ? max(0, p - window + 1) : 0;
+  const int u0 = unit_of(lo), cnt = unit_of(p) - u0 + 1;
+  const float* ml = part_ml + (((size_t)n * Hq + h) * NPU + u0) * 2;
+  const float* po = part_o + (((size_t)n * Hq + h) * NPU + u0) * HD;
+  float* s_red = s_f + NPU;
+  float M = -INFINITY;
+  for (int i = tid; i < cnt; i += nthreads) M = fmaxf(M, ml[2 * i]);
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, d));
+  if ((tid & 31) == 0) s_red[tid >> 5] = M;
+  __syncthreads();
+  M = s_red[0];
+  for (int w = 1; w < (nthreads >> 5); ++w) M = fmaxf(M, s_red[w]);
+  for (int i = tid; i < cnt; i += nthreads) s_f[i] = exp2f(ml[2 * i] - M);
+  __syncthreads();
+  // the sum of the weights: every thread adds the same terms in the same (rising) order
+  float L = 0.f;
+  for (int i = 0; i < cnt; ++i) L += ml[2 * i + 1] * s_f[i];
+  const float inv = 1.0f / L;
+  for (int d = tid; d < HD; d += nthreads) {
+    float acc = 0.f;
+    for (int i = 0; i < cnt; ++i) acc += po[(size_t)i * HD + d] * s_f[i];
+    orow[d] = __float2bfloat16_rn(acc * inv);
+  }
 }
 
 // One block per (token row, query head): merges the partitions in rising order, normalises, rounds to bf16.
 __global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     const int* __restrict__ seq_row, const int* __restrict__ seg,
                                     __nv_bfloat16* __restrict__ out, int Hq, int HD, int NP, int long_from) {
-  fz_grid_wait();
   fz_grid_launch_dependents();
+  fz_grid_wait();
   const int n = blockIdx.y, h = blockIdx.x;
   __nv_bfloat16* orow = out + ((size_t)n * Hq + h) * HD;
   const int row = seq_row[n];
@@ -365,32 +619,54 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
   }
 }
 
-template <int HD, int BOX>
-int launch_tma(const void* q, const void* k_pool, long long pool_rows, const int* pos, const int* seq_row, const int* seg,
-               const int* table, int mb, int page_size, void* out, float* part_o, float* part_ml, int N, int Hq, int Hkv,
-               float scale, int window, int NP, int long_from, int* err, cudaStream_t stream) {
+template <int HD, int BOX, int NSTAGE, int MINB, bool SMALLG>
+int launch_units(const void* q, const void* k_pool, long long pool_rows, const int* pos, const int* seq_row, const int* seg,
+                 const int* table, int mb, int page_size, void* out, float* part_o, float* part_ml, int N, int Hq, int Hkv,
+                 float scale, int window, int NPU, int long_from, int* err, cudaStream_t stream) {
   CUtensorMap map;
   int st = fztma::get_map_bf16(k_pool, pool_rows, HD, BOX, &map);
   if (st != FZ_OK) return st;
   constexpr size_t stage_bytes = 2 * (HD / 64) * 16 * 128;
-  constexpr size_t smem_pipe = 4 * TMA_DEPTH * stage_bytes + 16 * HD * 2 + 8 * 4 * TMA_DEPTH;
-  constexpr size_t smem_merge = (size_t)4 * 16 * (HD + 4) * 4 + 4 * 16 * 2 * 4;
-  constexpr size_t smem = (smem_pipe > smem_merge ? smem_pipe : smem_merge) + 1024;
-  static bool raised = false;
-  if (smem > 48 * 1024 && !raised) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_tma_kernel<HD, BOX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    raised = true;
+  constexpr size_t fixed = 1024 + 4 * NSTAGE * stage_bytes + 8 * 4 * NSTAGE;
+  const size_t smem = fixed + (size_t)(N + 1) * 4;
+  static int sms = 0;
+  static size_t raised = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   }
-  dim3 grid(NP, Hkv, N);
-  fz_launch(attn_decode_tma_kernel<HD, BOX>, grid, dim3(THREADS), smem, stream, map, (const __nv_bfloat16*)q, pos, seq_row, seg,
-            table, mb, page_size, part_o, part_ml, Hq, Hkv, scale * 1.4426950408889634f, window, long_from, err);
+  if (smem > raised) {
+    // (the size grows with the number of rows: raise the limit to the largest the kernel can be asked for)
+    const size_t most = fixed + (size_t)(MAX_UNIT_ROWS + 1) * 4;
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_units_kernel<HD, BOX, NSTAGE, MINB, SMALLG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most);
+    if (e != cudaSuccess) return (int)e;
+    raised = most;
+  }
+  const long long most_units = (long long)N * Hkv * NPU;
+  long long ctas = (most_units + 3) / 4;
+  if (ctas > (long long)sms * MINB) ctas = (long long)sms * MINB;
+  fz_launch(attn_decode_units_kernel<HD, BOX, NSTAGE, MINB, SMALLG>, dim3((unsigned)ctas), dim3(THREADS), smem, stream, map,
+            (const __nv_bfloat16*)q, pos, seq_row, seg, table, mb, page_size, part_o, part_ml, N, Hq, Hkv, NPU,
+            scale * 1.4426950408889634f, window, long_from, err);
   FZ_LAUNCH_CHECK();
   dim3 cgrid(Hq, N);
-  fz_launch(attn_combine_kernel, cgrid, dim3(HD < 128 ? 64 : 128), 0, stream, (const float*)part_o, (const float*)part_ml,
-            seq_row, seg, (__nv_bfloat16*)out, Hq, HD, NP, long_from);
+  fz_launch(attn_combine_units_kernel, cgrid, dim3(HD < 128 ? 64 : 128), (size_t)(NPU + 8) * 4, stream, (const float*)part_o,
+            (const float*)part_ml, pos, seq_row, seg, (__nv_bfloat16*)out, Hq, HD, NPU, window, long_from);
   FZ_LAUNCH_CHECK();
   return FZ_OK;
+}
+
+template <int HD, int BOX>
+int launch_tma(const void* q, const void* k_pool, long long pool_rows, const int* pos, const int* seq_row, const int* seg,
+               const int* table, int mb, int page_size, void* out, float* part_o, float* part_ml, int N, int Hq, int Hkv,
+               float scale, int window, int NPU, int long_from, int* err, cudaStream_t stream) {
+  static const int cfg = getenv("FZB200_ATTN_CFG") ? atoi(getenv("FZB200_ATTN_CFG")) : 0;
+#define FZ_U(NS_, MB_, SG_) return launch_units<HD, BOX, NS_, MB_, SG_>(q, k_pool, pool_rows, pos, seq_row, seg, table, mb, page_size, out, part_o, part_ml, N, Hq, Hkv, scale, window, NPU, long_from, err, stream)
+  if (Hq / Hkv > 8 || cfg == 3) FZ_U(3, 2, false);
+  if (cfg == 1) FZ_U(2, 3, true);
+  FZ_U(3, 2, true);
+#undef FZ_U
 }
 
 template <int HD>
@@ -427,7 +703,9 @@ FZ_API int fz_attn_decode_check(int Hq, int Hkv, int hd) {
   return FZ_OK;
 }
 
-FZ_API int fz_attn_partitions(int max_context) { return max_context <= 0 ? 1 : (max_context + PART - 1) / PART; }
+// Partial results per (row, head) the scratch must hold for contexts up to max_context: the units of the key axis
+// (never fewer than the 256-key partitions of the cp.async variant).
+FZ_API int fz_attn_partitions(int max_context) { return max_context <= 0 ? 1 : unit_of(max_context - 1) + 1; }
 
 // Float32 scratch the call needs: part_o N * Hq * NP * hd floats, part_ml N * Hq * NP * 2 floats.
 // num_pages > 0 and a pool laid out as (pages, 2, Hkv, page_size, hd) with v_pool = k_pool + Hkv * page_size * hd select
@@ -439,14 +717,16 @@ FZ_API int fz_attn_decode(const void* q, const void* k_pool, const void* v_pool,
   if (N <= 0) return FZ_OK;
   if (fz_attn_decode_check(Hq, Hkv, hd) != FZ_OK || page_size <= 0) return FZ_BAD_SHAPE;
   if (N > 65535 || Hkv > 65535) return FZ_TOO_LARGE;
-  const int NP = fz_attn_partitions(max_context);
+  const int NP = max_context <= 0 ? 1 : (max_context + PART - 1) / PART;
+  const int NPU = fz_attn_partitions(max_context);
   const bool interleaved = page_stride == 2LL * Hkv * page_size * hd &&
                            (const __nv_bfloat16*)v_pool == (const __nv_bfloat16*)k_pool + (long long)Hkv * page_size * hd;
   const bool tma_ok = num_pages > 0 && interleaved && (((uintptr_t)k_pool) & 15) == 0 &&
-                      (page_size == 8 || page_size % 16 == 0) && !getenv("FZB200_NO_TMA_ATTN");
+                      (page_size == 8 || page_size % 16 == 0) && N <= MAX_UNIT_ROWS &&
+                      (long long)N * Hkv * NPU < (1LL << 30) && (size_t)NPU * 4 < 40 * 1024 && !getenv("FZB200_NO_TMA_ATTN");
   if (tma_ok) {
     const long long pool_rows = (long long)num_pages * 2 * Hkv * page_size;
-#define FZ_T(HD_, BOX_) return launch_tma<HD_, BOX_>(q, k_pool, pool_rows, pos, seq_row, seg, table, mb, page_size, out, part_o, part_ml, N, Hq, Hkv, scale, window, NP, long_from, err, stream)
+#define FZ_T(HD_, BOX_) return launch_tma<HD_, BOX_>(q, k_pool, pool_rows, pos, seq_row, seg, table, mb, page_size, out, part_o, part_ml, N, Hq, Hkv, scale, window, NPU, long_from, err, stream)
     if (hd == 64 && page_size == 8) FZ_T(64, 8);
     if (hd == 64) FZ_T(64, 16);
     if (page_size == 8) FZ_T(128, 8);

@@ -22,8 +22,8 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
                     const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ seg,
                     const int* __restrict__ tiles, const int* __restrict__ table, int mb, long long page_stride,
                     int page_size, __nv_bfloat16* __restrict__ out, int Hq, int Hkv, float scale_log2, int window) {
-  fz_grid_wait();
   fz_grid_launch_dependents();
+  fz_grid_wait();
   constexpr int KSTEPS = HD / 16, NB = HD / 8, TILE_BYTES = BN * HD * 2;
   extern __shared__ __align__(128) uint8_t smem[];
   const uint32_t s_base = smem_u32(smem);          // [2 stages][K | V], then Q

@@ -74,8 +74,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  fz_grid_wait();
   fz_grid_launch_dependents();
+  fz_grid_wait();
 
   const int s_idx = tiles[2 * blockIdx.x], r_off = tiles[2 * blockIdx.x + 1];
   const int h = blockIdx.y, kvh = h / (Hq / Hkv);

@@ -23,8 +23,8 @@ __global__ void attn_simt_kernel(const T* __restrict__ q, const T* __restrict__ 
                                  const int* __restrict__ pos, const int* __restrict__ seq_row,
                                  const int* __restrict__ table, int mb, long long page_stride, int page_size,
                                  T* __restrict__ out, int Hq, int Hkv, int hd, float scale, int window, int* err) {
-  fz_grid_wait();
   fz_grid_launch_dependents();
+  fz_grid_wait();
   extern __shared__ float smem[];
   const int n = blockIdx.x, kvh = blockIdx.y;
   const int G = Hq / Hkv;

@@ -17,8 +17,8 @@ template <typename TA, typename TC>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TA* __restrict__ A, const TA* __restrict__ W, const float* __restrict__ bias,
                  TC* __restrict__ C, int M, int N, int K) {
-  fz_grid_wait();
   fz_grid_launch_dependents();
+  fz_grid_wait();
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -81,8 +81,8 @@ template <typename TA, typename TC>
 __global__ void __launch_bounds__(256)
 gemm_simt_small_kernel(const TA* __restrict__ A, const TA* __restrict__ W, const float* __restrict__ bias,
                        TC* __restrict__ C, int M, int N, int K) {
-  fz_grid_wait();
   fz_grid_launch_dependents();
+  fz_grid_wait();
   __shared__ float As[SK][SM_ROWS + 1];
   __shared__ float Ws[SK][SN + 1];
   const int tid = threadIdx.x;

@@ -105,9 +105,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (lane == 0) {
       // The weight operand does not depend on the kernel before this one: its first stages are requested before the
       // wait on that kernel, so the weights stream in while it finishes. (swap mode: A holds the weights; rows mode: B.)
+      const uint64_t stream_once = l2_evict_first();
       auto load_weights = [&](int i, int s) {
         uint8_t* sa = smem + (size_t)s * STAGE_BYTES;
-        if (p.swap) tma_load_2d(sa, &map_a, &full[s], (kb0 + i) * BK, tile_a * BM);
+        // swap mode streams every weight once per step: it should leave L2 before the activations, which are read again
+        if (p.swap) tma_load_2d_u32_hint(smem_u32(sa), &map_a, smem_u32(&full[s]), (kb0 + i) * BK, tile_a * BM, stream_once);
         else tma_load_2d(sa + A_BYTES, &map_b, &full[s], (kb0 + i) * BK, tile_b * BN);
       };
       auto load_activations = [&](int i, int s) {

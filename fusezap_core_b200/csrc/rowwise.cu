@@ -14,8 +14,8 @@
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tokens, const int* __restrict__ src,
                              const int* __restrict__ prev_ids, float* __restrict__ x, int D, int V, int* err) {
-  fz_grid_wait();
   fz_grid_launch_dependents();
+  fz_grid_wait();
   const int n = blockIdx.x;
   int tok = tokens[n];
   if (src != nullptr && src[n] >= 0) tok = prev_ids[src[n]];
@@ -49,8 +49,8 @@ template <typename TW, typename TH>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, const TW* __restrict__ w,
                                    TH* __restrict__ h, const int* __restrict__ rows, int n_src, int D, float eps,
                                    int* err) {
-  fz_grid_wait();
   fz_grid_launch_dependents();
+  fz_grid_wait();
   __shared__ float scratch[32];
   const int r = blockIdx.x;
   int src = r;
@@ -88,8 +88,8 @@ template <typename TW, typename TH, int VPT>
 __global__ void __launch_bounds__(512)
 add_rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ delta, const TW* __restrict__ w,
                        TH* __restrict__ h, const int* __restrict__ rows, int n_src, int D, float eps, int* err) {
-  fz_grid_wait();
   fz_grid_launch_dependents();
+  fz_grid_wait();
   __shared__ float scratch[32];
   const int r = blockIdx.x;
   const int D4 = D >> 2;
@@ -187,8 +187,8 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const float*
                                      T* __restrict__ k_pool, T* __restrict__ v_pool, long long page_stride,
                                      int page_size, int write, T* __restrict__ q_out, int Hq, int Hkv, int hd,
                                      int max_len, int* err) {
-  fz_grid_wait();
   fz_grid_launch_dependents();
+  fz_grid_wait();
   const int n = blockIdx.x;
   const int half = hd >> 1;
   const int row = seq_row[n];
@@ -241,12 +241,103 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const float*
   }
 }
 
+// The same for head sizes that are multiples of 8: grid (rows, blocks of heads); a thread owns four neighbouring pairs of
+// one head (float4 loads, one vector store per half), so a decode step's few rows still spread over many blocks. The
+// row's metadata and angles do not depend on the kernel before and are read ahead of the wait on it.
+__device__ __forceinline__ void store4(float* d, float a, float b, float c, float e) { *(float4*)d = make_float4(a, b, c, e); }
+__device__ __forceinline__ void store4(__nv_bfloat16* d, float a, float b, float c, float e) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, e);
+  *(uint2*)d = make_uint2(*(const uint32_t*)&lo, *(const uint32_t*)&hi);
+}
+
+template <typename T>
+__global__ void rope_kv_write_vec_kernel(const float* __restrict__ qkv, const float* __restrict__ cos_t,
+                                         const float* __restrict__ sin_t, const int* __restrict__ pos,
+                                         const int* __restrict__ seq_row, const int* __restrict__ table, int mb,
+                                         T* __restrict__ k_pool, T* __restrict__ v_pool, long long page_stride,
+                                         int page_size, int write, T* __restrict__ q_out, int Hq, int Hkv, int hd,
+                                         int max_len, int* err) {
+  fz_grid_launch_dependents();
+  const int n = blockIdx.x;
+  const int half = hd >> 1, per_head = half >> 2;
+  const int item = blockIdx.y * blockDim.x + threadIdx.x;
+  const int head = item / per_head, j = (item - head * per_head) * 4;
+  const bool active = head < Hq + 2 * Hkv;
+  const int row = seq_row[n];
+  const int p = pos[n];
+  const bool in_range = p >= 0 && p < max_len;
+  float4 c = make_float4(1.f, 1.f, 1.f, 1.f), sn = make_float4(0.f, 0.f, 0.f, 0.f);
+  long long slot_base = -1;
+  bool no_page = false;
+  if (active && row >= 0 && in_range) {
+    if (head < Hq + Hkv) {
+      c = *(const float4*)(cos_t + (size_t)p * half + j);
+      sn = *(const float4*)(sin_t + (size_t)p * half + j);
+    }
+    if (write && head >= Hq) {
+      const int page = table[(size_t)row * mb + p / page_size];
+      no_page = page < 0;
+      if (!no_page) slot_base = (long long)page * page_stride + (long long)(p % page_size) * hd;
+    }
+  }
+  fz_grid_wait();
+  if (!active) return;
+  if (row < 0 || !in_range) {
+    if (row >= 0 && item == 0) atomicOr(err, FZ_ERR_POS_RANGE);
+    if (head < Hq) {
+      T* qo = q_out + ((size_t)n * Hq + head) * hd;
+      store4(qo + j, 0.f, 0.f, 0.f, 0.f);
+      store4(qo + j + half, 0.f, 0.f, 0.f, 0.f);
+    }
+    return;
+  }
+  if (no_page && j == 0 && head == Hq) atomicOr(err, FZ_ERR_NO_PAGE);
+  const float* in = qkv + ((size_t)n * (Hq + 2 * Hkv) + head) * hd;
+  const float4 x1 = *(const float4*)(in + j), x2 = *(const float4*)(in + j + half);
+  // (for the value heads c = 1 and sn = 0: the values pass unchanged)
+  const float a0 = x1.x * c.x - x2.x * sn.x, a1 = x1.y * c.y - x2.y * sn.y, a2 = x1.z * c.z - x2.z * sn.z, a3 = x1.w * c.w - x2.w * sn.w;
+  const float b0 = x2.x * c.x + x1.x * sn.x, b1 = x2.y * c.y + x1.y * sn.y, b2 = x2.z * c.z + x1.z * sn.z, b3 = x2.w * c.w + x1.w * sn.w;
+  T* dst;
+  if (head < Hq) {
+    dst = q_out + ((size_t)n * Hq + head) * hd;
+  } else {
+    if (slot_base < 0) return;
+    const long long head_stride = (long long)page_size * hd;
+    dst = head < Hq + Hkv ? k_pool + slot_base + (long long)(head - Hq) * head_stride
+                          : v_pool + slot_base + (long long)(head - Hq - Hkv) * head_stride;
+  }
+  if (head < Hq + Hkv) {
+    store4(dst + j, a0, a1, a2, a3);
+    store4(dst + j + half, b0, b1, b2, b3);
+  } else {
+    store4(dst + j, x1.x, x1.y, x1.z, x1.w);
+    store4(dst + j + half, x2.x, x2.y, x2.z, x2.w);
+  }
+}
+
 FZ_API int fz_rope_kv_write(const float* qkv, const float* cos_t, const float* sin_t, const int* pos,
                             const int* seq_row, const int* table, int mb, void* k_pool, void* v_pool,
                             long long page_stride, int page_size, int write, void* q_out, int dtype, int N, int Hq,
                             int Hkv, int hd, int max_len, int* err, cudaStream_t stream) {
   if (N <= 0) return FZ_OK;
   if (hd % 2 || hd <= 0) return FZ_BAD_SHAPE;
+  if (dtype != FZ_F32 && dtype != FZ_BF16) return FZ_BAD_DTYPE;
+  const bool aligned = ((((uintptr_t)qkv | (uintptr_t)cos_t | (uintptr_t)sin_t | (uintptr_t)k_pool | (uintptr_t)v_pool |
+                          (uintptr_t)q_out) & 15) == 0) && page_stride % 8 == 0;
+  if (hd % 8 == 0 && aligned) {
+    const int items = (Hq + 2 * Hkv) * (hd / 8);
+    const int threads = items < 256 ? ((items + 31) / 32) * 32 : 256;
+    dim3 grid(N, (items + threads - 1) / threads);
+    if (dtype == FZ_F32)
+      fz_launch(rope_kv_write_vec_kernel<float>, grid, dim3(threads), 0, stream, qkv, cos_t, sin_t, pos, seq_row, table, mb,
+                (float*)k_pool, (float*)v_pool, page_stride, page_size, write, (float*)q_out, Hq, Hkv, hd, max_len, err);
+    else
+      fz_launch(rope_kv_write_vec_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, qkv, cos_t, sin_t, pos, seq_row,
+                table, mb, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, page_stride, page_size, write,
+                (__nv_bfloat16*)q_out, Hq, Hkv, hd, max_len, err);
+    FZ_LAUNCH_CHECK();
+    return FZ_OK;
+  }
   if (dtype == FZ_F32)
     fz_launch(rope_kv_write_kernel<float>, dim3(N), dim3(256), 0, stream, qkv, cos_t, sin_t, pos, seq_row, table, mb,
               (float*)k_pool, (float*)v_pool, page_stride, page_size, write, (float*)q_out, Hq, Hkv, hd, max_len, err);
@@ -263,8 +354,8 @@ FZ_API int fz_rope_kv_write(const float* qkv, const float* cos_t, const float* s
 // ------------------------------------------------------------------------------------------------ SwiGLU
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, long long total, int I) {
-  fz_grid_wait();
   fz_grid_launch_dependents();
+  fz_grid_wait();
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (long long)gridDim.x * blockDim.x) {
     const long long n = idx / I;
@@ -278,8 +369,8 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, lon
 // 16 bytes of gate and of up per thread (8 bf16 or 4 float32); needs I a multiple of that count and aligned operands.
 template <typename T>
 __global__ void swiglu_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, long long groups, int I) {
-  fz_grid_wait();
   fz_grid_launch_dependents();
+  fz_grid_wait();
   constexpr int V = 16 / sizeof(T);
   const int per_row = I / V;
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < groups;
@@ -375,8 +466,8 @@ __device__ int block_argmax(const float* __restrict__ row, int V, float* s_val, 
 // `partial`; the CTA that arrives last at the row's counter reduces the slices in index order and resets the counter.
 __global__ void argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, float* partial_val,
                               int* partial_idx, int* counters) {
-  fz_grid_wait();
   fz_grid_launch_dependents();
+  fz_grid_wait();
   __shared__ float s_val[32];
   __shared__ int s_idx[32];
   __shared__ int s_last;
@@ -425,8 +516,8 @@ FZ_API int fz_argmax(const float* logits, int* out, int R, int V, float* partial
 // Thread t owns the contiguous range [t * chunk, (t + 1) * chunk), so partial sums are in index order.
 __global__ void sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
                               const double* __restrict__ uniform, int* __restrict__ out, int V) {
-  fz_grid_wait();
   fz_grid_launch_dependents();
+  fz_grid_wait();
   __shared__ float s_val[32];
   __shared__ int s_idx[32];
   __shared__ double s_sum[1024];

@@ -57,6 +57,19 @@ __device__ __forceinline__ void tma_load_2d_u32(uint32_t smem_dst, const CUtenso
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
 }
+// The same with an L2 cache policy (from `l2_evict_first()`): for data that is read once, so that it leaves L2 before
+// lines that will be read again.
+__device__ __forceinline__ uint64_t l2_evict_first() {
+  uint64_t policy;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+  return policy;
+}
+__device__ __forceinline__ void tma_load_2d_u32_hint(uint32_t smem_dst, const CUtensorMap* map, uint32_t bar, int x, int y,
+                                                     uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+      ::"r"(smem_dst), "l"(map), "r"(bar), "r"(x), "r"(y), "l"(policy) : "memory");
+}
 
 // ---------------------------------------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,

@@ -56,6 +56,17 @@ def test_decode_rows_at_long_contexts(Hq, Hkv, hd, bs, window):
     close(o, op, "decode")
 
 
+@pytest.mark.parametrize("Hq,Hkv,hd,bs", [(8, 2, 128, 16), (6, 3, 64, 8), (4, 2, 128, 32)])
+@pytest.mark.parametrize("window", [0, 700])
+def test_decode_rows_past_4096_keys(Hq, Hkv, hd, bs, window):
+    """Beyond key 4096 the key axis is cut into units of 256 instead of 64: rows at both sides of the change, at the
+    edges of the larger units, and with a window that begins among the small units and ends among the large ones."""
+    lengths = [5000, 4400, 4097]
+    rows = [(0, 4999, 1), (0, 4095, 1), (0, 4096, 1), (1, 4351, 1), (1, 4352, 2), (2, 4096, 1), (1, 100, 1), (0, 4700, 5)]
+    o, op, _ = run_both(Hq, Hkv, hd, bs, window, lengths, rows)
+    close(o, op, "decode past 4096")
+
+
 @pytest.mark.parametrize("Hq,Hkv,hd", [(4, 1, 128), (14, 2, 64), (8, 8, 64), (2, 1, 128)])
 @pytest.mark.parametrize("bs,window", [(16, 0), (8, 100), (3, 0)])
 def test_prefill_portions(Hq, Hkv, hd, bs, window):
