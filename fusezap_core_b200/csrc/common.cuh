@@ -36,6 +36,13 @@ enum FzDeviceError : int {
     if (e__ != cudaSuccess) return (int)e__;       \
   } while (0)
 
+// One rotated pair: (x1, x2) turned by the angle whose cosine and sine are c and s. Written with explicit roundings so
+// that every kernel that rotates gives the same bits.
+__device__ __forceinline__ void fz_rope_pair(float x1, float x2, float c, float s, float& o1, float& o2) {
+  o1 = __fmaf_rn(x1, c, -__fmul_rn(x2, s));
+  o2 = __fmaf_rn(x2, c, __fmul_rn(x1, s));
+}
+
 // Programmatic dependent launch. A kernel launched with `fz_launch(..., pdl = true)` may start while the kernel before
 // it in the stream is still running: its blocks become resident and run their prologue early. Every kernel of this
 // package therefore calls `fz_grid_wait()` before it reads or writes anything another kernel of the step touches (on

@@ -65,6 +65,19 @@ struct Params {
   int stages;
   int vec_ok;              // rows mode: C rows are 16-byte aligned, so full groups of 16 columns go out as vectors
   int swiglu;              // W holds [64 gate rows | 64 up rows] blocks: store silu(gate) * up as bf16 [rows, feats / 2]
+  // rope != 0 (swap mode, hd divides 128): the features are [q heads | k heads | v heads] of size hd; q and k are rotated
+  // by the token's position, q goes to c_bf16 [rows, Hq * hd], k and v to the token's slot of the paged pool
+  int rope;
+  const float* cos_t;      // [max_len, hd / 2]
+  const float* sin_t;
+  const int* pos;          // [rows]
+  const int* seq_row;      // [rows], negative: padding (q zeros, nothing stored)
+  const int* table;        // [requests, mb] block table of the layer's cache group
+  int mb;
+  __nv_bfloat16* k_pool;
+  __nv_bfloat16* v_pool;
+  long long page_stride;
+  int page_size, write, Hq, Hkv, hd, max_len;
 };
 
 template <int BN>
@@ -163,7 +176,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int b_limit = p.swap ? p.rows : p.feats;
     const int b0 = tile_b * BN;
     const uint32_t taddr = tmem_d + ((uint32_t)(quad * 32) << 16);
-    const bool direct = p.splits == 1 && !p.swiglu;
+    const bool direct = p.splits == 1 && !p.swiglu && !p.rope;
     float* part = (float*)smem + r;          // split K: partial tile as [column][row] in the (now idle) stage buffers
     float v[16];
     auto store16 = [&](const float* x, int c) {   // columns c..c+15 of this thread's row, final values
@@ -226,7 +239,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
     }
   }
-  if (p.splits > 1 || p.swiglu) {
+  if (p.splits > 1 || p.swiglu || p.rope) {
     // split K: every thread of every CTA of the cluster passes both cluster barriers; only the epilogue warps work
     // between them. Without a split (fused SwiGLU only) the epilogue warps synchronise among themselves.
     if (p.splits > 1) cluster_sync_all();
@@ -251,7 +264,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             acc = ((const float*)smem)[c * BM + r];
           }
           const float y = acc + bv;
-          if (p.swiglu) {
+          if (p.swiglu || p.rope) {
             ex[i * BM + r] = y;
           } else if (feat < p.feats) {
             const int m = tile_b * BN + c;
@@ -266,6 +279,44 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int i = 0; i < ni; ++i) {
               const int m = tile_b * BN + (int)rank + (i0 + i) * p.splits;
               p.c_bf16[(size_t)m * half + tile_a * 64 + r] = __float2bfloat16_rn(silu_mul(ex[i * BM + r], ex[i * BM + r + 64]));
+            }
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
+        if (p.rope) {
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          const int hd = p.hd, half = hd >> 1;
+          const int head = feat / hd, j = feat - head * hd;      // (a tile starts at a head's first feature: hd divides 128)
+          if (feat < p.feats) {
+            for (int i = 0; i < ni; ++i) {
+              const int m = tile_b * BN + (int)rank + (i0 + i) * p.splits;
+              const int row = p.seq_row[m], ps = p.pos[m];
+              const bool in_range = ps >= 0 && ps < p.max_len;
+              if (row >= 0 && !in_range && r == 0) atomicOr(p.err, FZ_ERR_POS_RANGE);
+              const bool live = row >= 0 && in_range;
+              __nv_bfloat16* dst = nullptr;
+              if (head < p.Hq) {
+                dst = p.c_bf16 + ((size_t)m * p.Hq + head) * hd;
+              } else if (live && p.write) {
+                const int page = p.table[(size_t)row * p.mb + ps / p.page_size];
+                if (page < 0) {
+                  if (j == 0 && head == p.Hq) atomicOr(p.err, FZ_ERR_NO_PAGE);
+                } else {
+                  const long long slot = (long long)page * p.page_stride + (long long)(ps % p.page_size) * hd;
+                  const long long head_stride = (long long)p.page_size * hd;
+                  dst = head < p.Hq + p.Hkv ? p.k_pool + slot + (long long)(head - p.Hq) * head_stride
+                                            : p.v_pool + slot + (long long)(head - p.Hq - p.Hkv) * head_stride;
+                }
+              }
+              if (dst == nullptr) continue;
+              if (head >= p.Hq + p.Hkv) {
+                dst[j] = __float2bfloat16_rn(ex[i * BM + r]);
+              } else if (j < half) {
+                float o1 = 0.f, o2 = 0.f;
+                if (live) fz_rope_pair(ex[i * BM + r], ex[i * BM + r + half], p.cos_t[(size_t)ps * half + j], p.sin_t[(size_t)ps * half + j], o1, o2);
+                dst[j] = __float2bfloat16_rn(o1);
+                dst[j + half] = __float2bfloat16_rn(o2);
+              }
             }
           }
           asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -550,11 +601,34 @@ FZ_API int fz_gemm_tc_splits(int N, int K) {
 
 // x: [M, K] bf16, w: [N, K] bf16, bias: [N] float32 or null, c: [M, N] float32 (out_dtype 0) or bf16 (1).
 static int gemm_tc_impl(const void* x, const void* w, const float* bias, void* c, int out_dtype, int M, int N, int K,
-                        int swiglu, int* err, cudaStream_t stream);
+                        const Params& fused, int* err, cudaStream_t stream);
 
 FZ_API int fz_gemm_tc(const void* x, const void* w, const float* bias, void* c, int out_dtype, int M, int N, int K,
                       int* err, cudaStream_t stream) {
-  return gemm_tc_impl(x, w, bias, c, out_dtype, M, N, K, 0, err, stream);
+  return gemm_tc_impl(x, w, bias, c, out_dtype, M, N, K, Params{}, err, stream);
+}
+
+// Can the query/key/value product of M token rows with heads of size hd end in the rotation and the cache write?
+// (the few-token mode only, and a 128-feature tile must hold whole heads)
+FZ_API int fz_gemm_tc_qkv_rope_check(int M, int hd) {
+  return (M >= 1 && M <= 128 && hd >= 2 && hd % 2 == 0 && 128 % hd == 0) ? FZ_OK : FZ_BAD_SHAPE;
+}
+
+// x: [M, K] bf16; w: [(Hq + 2 Hkv) hd, K] bf16, rows [q heads | k heads | v heads]; bias float32 or null. Rotates the q
+// and k heads of every token by its position (pairs j, j + hd / 2; angles from cos_t / sin_t [max_len, hd / 2]) and
+// writes q to q_out [M, Hq hd] bf16 and, if `write`, k and v to the token's slot of the paged pools (as the separate
+// rotation kernel does, with the same roundings). seq_row < 0: a padding row (q zeros, nothing stored).
+FZ_API int fz_gemm_tc_qkv_rope(const void* x, const void* w, const float* bias, int M, int K, const float* cos_t,
+                               const float* sin_t, const int* pos, const int* seq_row, const int* table, int mb,
+                               void* k_pool, void* v_pool, long long page_stride, int page_size, int write, void* q_out,
+                               int Hq, int Hkv, int hd, int max_len, int* err, cudaStream_t stream) {
+  if (fz_gemm_tc_qkv_rope_check(M, hd) != FZ_OK || Hq <= 0 || Hkv <= 0 || page_size <= 0) return FZ_BAD_SHAPE;
+  Params f{};
+  f.rope = 1;
+  f.cos_t = cos_t; f.sin_t = sin_t; f.pos = pos; f.seq_row = seq_row; f.table = table; f.mb = mb;
+  f.k_pool = (__nv_bfloat16*)k_pool; f.v_pool = (__nv_bfloat16*)v_pool; f.page_stride = page_stride;
+  f.page_size = page_size; f.write = write; f.Hq = Hq; f.Hkv = Hkv; f.hd = hd; f.max_len = max_len;
+  return gemm_tc_impl(x, w, bias, q_out, FZ_BF16, M, (Hq + 2 * Hkv) * hd, K, f, err, stream);
 }
 
 // Fused gate/up product and SwiGLU: w is [2 I, K] with rows in blocks of 128 = [64 gate rows | 64 up rows] of the same 64
@@ -563,21 +637,23 @@ FZ_API int fz_gemm_tc_swiglu(const void* x, const void* w_packed, const float* b
                              int* err, cudaStream_t stream) {
   if (I <= 0 || I % 64) return FZ_BAD_SHAPE;
   if (((uintptr_t)out) & 15) return FZ_BAD_ALIGNMENT;
-  return gemm_tc_impl(x, w_packed, bias_packed, out, FZ_BF16, M, 2 * I, K, 1, err, stream);
+  Params f{};
+  f.swiglu = 1;
+  return gemm_tc_impl(x, w_packed, bias_packed, out, FZ_BF16, M, 2 * I, K, f, err, stream);
 }
 
 static int gemm_tc_impl(const void* x, const void* w, const float* bias, void* c, int out_dtype, int M, int N, int K,
-                        int swiglu, int* err, cudaStream_t stream) {
+                        const Params& fused, int* err, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return FZ_OK;
   int st = fz_gemm_tc_check(x, w, M, N, K);
   if (st != FZ_OK) return st;
   if (out_dtype != FZ_F32 && out_dtype != FZ_BF16) return FZ_BAD_DTYPE;
-  Params p{};
+  if (fused.rope && M > 128) return FZ_BAD_SHAPE;
+  Params p = fused;
   p.c_f32 = out_dtype == FZ_F32 ? (float*)c : nullptr;
   p.c_bf16 = out_dtype == FZ_BF16 ? (__nv_bfloat16*)c : nullptr;
   p.bias = bias; p.err = err; p.rows = M; p.feats = N; p.K = K;
   p.splits = 1;
-  p.swiglu = swiglu;
   p.vec_ok = (N % 8 == 0 && ((uintptr_t)c & 15) == 0) ? 1 : 0;
   CUtensorMap ma, mb;
   if (M <= 128) {

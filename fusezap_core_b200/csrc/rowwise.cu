@@ -220,9 +220,8 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const float*
   for (int i = threadIdx.x; i < (Hq + Hkv) * half; i += blockDim.x) {
     const int head = i / half, j = i - head * half;
     const float x1 = in[head * hd + j], x2 = in[head * hd + j + half];
-    const float c = cr[j], s = sr[j];
-    const float o1 = x1 * c - x2 * s;
-    const float o2 = x2 * c + x1 * s;
+    float o1, o2;
+    fz_rope_pair(x1, x2, cr[j], sr[j], o1, o2);
     if (head < Hq) {
       qo[head * hd + j] = Cvt<T>::from_f(o1);
       qo[head * hd + j + half] = Cvt<T>::from_f(o2);
@@ -295,8 +294,11 @@ __global__ void rope_kv_write_vec_kernel(const float* __restrict__ qkv, const fl
   const float* in = qkv + ((size_t)n * (Hq + 2 * Hkv) + head) * hd;
   const float4 x1 = *(const float4*)(in + j), x2 = *(const float4*)(in + j + half);
   // (for the value heads c = 1 and sn = 0: the values pass unchanged)
-  const float a0 = x1.x * c.x - x2.x * sn.x, a1 = x1.y * c.y - x2.y * sn.y, a2 = x1.z * c.z - x2.z * sn.z, a3 = x1.w * c.w - x2.w * sn.w;
-  const float b0 = x2.x * c.x + x1.x * sn.x, b1 = x2.y * c.y + x1.y * sn.y, b2 = x2.z * c.z + x1.z * sn.z, b3 = x2.w * c.w + x1.w * sn.w;
+  float a0, a1, a2, a3, b0, b1, b2, b3;
+  fz_rope_pair(x1.x, x2.x, c.x, sn.x, a0, b0);
+  fz_rope_pair(x1.y, x2.y, c.y, sn.y, a1, b1);
+  fz_rope_pair(x1.z, x2.z, c.z, sn.z, a2, b2);
+  fz_rope_pair(x1.w, x2.w, c.w, sn.w, a3, b3);
   T* dst;
   if (head < Hq) {
     dst = q_out + ((size_t)n * Hq + head) * hd;

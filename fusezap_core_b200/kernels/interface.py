@@ -58,6 +58,14 @@ class Ops:
         and, if cache.write, k and v to the row's page slot of cache.keys / cache.values."""
         raise NotImplementedError
 
+    def linear_rope_kv_write(self, a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, cos: torch.Tensor,
+                             sin: torch.Tensor, meta: Any, cache: Any, q_out: torch.Tensor, num_heads: int,
+                             num_kv_heads: int, head_dim: int) -> bool:
+        """`linear` (a . w^T + bias, w rows = [q heads | k heads | v heads]) followed by `rope_kv_write` on its float32
+        result, as one operation that never writes that result out. Returns False, having done nothing, if this table
+        has no such kernel for these sizes; the caller then runs the two operations."""
+        return False
+
     def paged_attention(self, q: torch.Tensor, cache: Any, meta: Any, out: torch.Tensor, num_heads: int,
                         num_kv_heads: int, head_dim: int, scale: float, window: int) -> None:
         """out[n, h] = softmax_j((q[n, h] . K[j]) * scale) V[j] over the keys j of the row's own request with

@@ -52,6 +52,7 @@ class CudaOps(Ops):
         self.use_tensor_cores = self.tc is not None
         self.prefill_tcgen05 = True        # False: long portions on the mma.sync flash-attention kernel
         self.fuse_swiglu = True            # gate/up product and SwiGLU in one kernel where the sizes allow it
+        self.fuse_rope = True              # q/k/v product, rotation and cache write in one kernel (few-token steps)
         self._attn_scratch: torch.Tensor | None = None      # float32 partial outputs of the split decode attention
 
     # ---- plumbing
@@ -200,6 +201,33 @@ class CudaOps(Ops):
             c_longlong(page_stride), c_int(cache.page_size), c_int(1 if cache.write else 0), _p(q_out),
             c_int(_CODE[self.dtype]), c_int(n), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
             c_int(cos.shape[0]), _p(self.err), self._stream()), "rope_kv_write")
+
+    def linear_rope_kv_write(self, a, w, bias, cos, sin, meta, cache, q_out, num_heads, num_kv_heads, head_dim) -> bool:
+        m, k = a.shape
+        if not (self.use_tensor_cores and self.fuse_rope and self.dtype == torch.bfloat16) or \
+                self.tc.fz_gemm_tc_qkv_rope_check(c_int(m), c_int(head_dim)) != 0 or \
+                self.tc.fz_gemm_tc_check(_p(a), _p(w), c_int(m), c_int(w.shape[0]), c_int(k)) != 0:
+            return False
+        self._want(a, "linear input", (torch.bfloat16,), 2)
+        self._want(w, "linear weight", (torch.bfloat16,), 2)
+        self._want(cos, "cos table", (torch.float32,), 2)
+        self._want(sin, "sin table", (torch.float32,), 2)
+        self._want(q_out, "q", (torch.bfloat16,), 2)
+        if bias is not None:
+            self._want(bias, "linear bias", (torch.float32,), 1)
+        n = (num_heads + 2 * num_kv_heads) * head_dim
+        if w.shape != (n, k) or q_out.shape != (m, num_heads * head_dim) or cos.shape[1] != head_dim // 2 \
+                or sin.shape != cos.shape or (bias is not None and bias.shape[0] != n):
+            raise KernelError(f"linear_rope_kv_write: a {tuple(a.shape)}, w {tuple(w.shape)}, q {tuple(q_out.shape)}, "
+                              f"cos {tuple(cos.shape)}")
+        kp, vp, page_stride = self._pool(cache, num_kv_heads, head_dim)
+        table = meta.table(cache.group)
+        self._check(self.tc.fz_gemm_tc_qkv_rope(
+            _p(a), _p(w), _p(bias), c_int(m), c_int(k), _p(cos), _p(sin), _p(meta.pos), _p(meta.seq_row), _p(table),
+            c_int(table.shape[1]), _p(kp), _p(vp), c_longlong(page_stride), c_int(cache.page_size),
+            c_int(1 if cache.write else 0), _p(q_out), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
+            c_int(cos.shape[0]), _p(self.err), self._stream()), "linear_rope_kv_write (tensor cores)")
+        return True
 
     def paged_attention(self, q, cache, meta, out, num_heads, num_kv_heads, head_dim, scale, window) -> None:
         self._want(q, "q", (self.dtype,), 2)

@@ -57,10 +57,12 @@ class GQAttention(Mixer):
     def forward(self, ctx, h: torch.Tensor, cache: LayerCache) -> torch.Tensor:
         n, ops, ws = h.shape[0], ctx.ops, ctx.ws
         Hq, Hkv, hd = self.Hq, self.Hkv, self.hd
-        qkv = ws.get("qkv", (n, (Hq + 2 * Hkv) * hd), torch.float32)
-        ops.linear(h, self.wqkv, self.bqkv, qkv)
         q = ws.get("q", (n, Hq * hd), ops.dtype)
-        ctx.positions[self.position].rotate_and_store(ctx, qkv, q, cache, Hq, Hkv, hd)
+        position = ctx.positions[self.position]
+        if not position.project_rotate_store(ctx, h, self.wqkv, self.bqkv, q, cache, Hq, Hkv, hd):
+            qkv = ws.get("qkv", (n, (Hq + 2 * Hkv) * hd), torch.float32)
+            ops.linear(h, self.wqkv, self.bqkv, qkv)
+            position.rotate_and_store(ctx, qkv, q, cache, Hq, Hkv, hd)
         o = ws.get("attn_out", (n, Hq * hd), ops.dtype)
         ops.paged_attention(q, cache, ctx.meta, o, Hq, Hkv, hd, self.scale, self.window)
         delta = ws.get("delta", (n, self.D), torch.float32)

@@ -115,6 +115,13 @@ class PositionEncoding(Part):
                          num_heads: int, num_kv_heads: int, head_dim: int) -> None:
         raise NotImplementedError
 
+    def project_rotate_store(self, ctx: "StepContext", h: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None,
+                             q_out: torch.Tensor, cache: LayerCache, num_heads: int, num_kv_heads: int,
+                             head_dim: int) -> bool:
+        """Optional: the mixer's q/k/v product (h . w^T + bias) and `rotate_and_store` as one operation. False (the
+        default) means nothing was done and the mixer runs the product and `rotate_and_store` itself."""
+        return False
+
 
 class Block(Part):
     """Arranges norm(s), mixer and feed-forward. Built with the already built parts of its layer."""

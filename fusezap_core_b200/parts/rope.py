@@ -59,3 +59,10 @@ class RotaryEncoding(PositionEncoding):
         if head_dim != self.head_dim:
             raise ValueError(f"rope was built for head_dim {self.head_dim}, the mixer has {head_dim}")
         ctx.ops.rope_kv_write(qkv, self.cos, self.sin, ctx.meta, cache, q_out, num_heads, num_kv_heads, head_dim)
+
+    def project_rotate_store(self, ctx, h, w, bias, q_out, cache, num_heads, num_kv_heads, head_dim) -> bool:
+        if head_dim != self.head_dim:
+            raise ValueError(f"rope was built for head_dim {self.head_dim}, the mixer has {head_dim}")
+        fused = getattr(ctx.ops, "linear_rope_kv_write", None)      # an optional entry of the kernel table
+        return bool(fused is not None and fused(h, w, bias, self.cos, self.sin, ctx.meta, cache, q_out, num_heads,
+                                                num_kv_heads, head_dim))

@@ -109,3 +109,61 @@ def test_fused_gate_up_swiglu(M, I, K):
         lim = 2.0 ** -8 * float(ref.abs().max()) * 1.01
         assert torch.isfinite(out.float()).all() and err <= lim, f"M={M} I={I} K={K} bias={bias}: {err:.3e} > {lim:.3e}"
     assert ops.pack_gate_up(wg[:100], wu[:100]) is None, "I must be a multiple of 64"
+
+
+@pytest.mark.parametrize("Hq,Hkv,hd,K,bs", [(32, 8, 128, 4096, 16), (14, 2, 64, 896, 8), (3, 1, 64, 128, 5), (5, 5, 32, 200, 16),
+                                            (2, 1, 128, 64, 3)])
+@pytest.mark.parametrize("M", [1, 8, 19, 128])
+def test_qkv_product_with_rotation_and_cache_write(Hq, Hkv, hd, K, bs, M):
+    """The q/k/v product that ends in the rotation and the cache write gives the bits of the product followed by the
+    rotation kernel: q, and every slot of the key and value pools (written ones and untouched ones); with a bias, a
+    padding row, rows of several requests at scattered positions, whole heads that straddle nothing (hd divides 128)
+    and a last tile that is not full; and it leaves the pool alone when the layer does not write its cache."""
+    from types import SimpleNamespace
+    from fusezap_core_b200.kernels import cuda_ops
+    from test_kernels_gpu import Meta, make_cache
+    ops = cuda_ops("bfloat16")
+    g = torch.Generator().manual_seed(Hq * 7 + hd + M)
+    N = (Hq + 2 * Hkv) * hd
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(N, K, generator=g) * K ** -0.5).to(torch.bfloat16).cuda()
+    b = torch.randn(N, generator=g).cuda()
+    max_len = 700
+    ang = torch.rand(max_len, hd // 2, generator=g) * 6.28
+    cos, sin = torch.cos(ang).cuda(), torch.sin(ang).cuda()
+    n_req = 3
+    mb = -(-max_len // bs)
+    perm = torch.randperm(n_req * mb + 2, generator=g).tolist()
+    table = [perm[r * mb:(r + 1) * mb] for r in range(n_req)]
+    pos, seq = [], []
+    used = set()
+    for i in range(M):
+        r = i % n_req
+        p = int(torch.randint(0, max_len, (1,), generator=g))
+        while (r, p) in used:
+            p = (p + 1) % max_len
+        used.add((r, p)); pos.append(p); seq.append(r)
+    if M > 2:
+        seq[M // 2] = -1
+    meta = Meta(pos, seq, table, "cuda")
+    for write in (True, False):
+        res = []
+        for fused in (True, False):
+            cache = make_cache(n_req * mb + 2, Hkv, bs, hd, torch.bfloat16, "cuda", write=write)
+            cache.pool.copy_(torch.randn(cache.pool.shape, generator=torch.Generator().manual_seed(5)).to(torch.bfloat16))
+            q = torch.full((M, Hq * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+            if fused:
+                assert ops.linear_rope_kv_write(a, w, b, cos, sin, meta, cache, q, Hq, Hkv, hd)
+            else:
+                qkv = torch.empty(M, N, device="cuda")
+                ops.linear(a, w, b, qkv)
+                ops.rope_kv_write(qkv, cos, sin, meta, cache, q, Hq, Hkv, hd)
+            ops.check_errors()
+            res.append((q.clone(), cache.pool.clone()))
+        assert torch.isfinite(res[0][0].float()).all()
+        assert torch.equal(res[0][0], res[1][0]), f"write={write}: q differs"
+        assert torch.equal(res[0][1], res[1][1]), f"write={write}: the pools differ"
+    # sizes the fused kernel does not take are refused, not computed
+    q = torch.empty(200, Hq * hd, dtype=torch.bfloat16, device="cuda")
+    big = torch.randn(200, K, generator=g).to(torch.bfloat16).cuda()
+    assert ops.linear_rope_kv_write(big, w, b, cos, sin, meta, cache, q, Hq, Hkv, hd) is False
