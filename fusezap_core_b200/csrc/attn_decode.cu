@@ -288,6 +288,19 @@ __host__ __device__ __forceinline__ int unit_start(int u) {
 }
 __host__ __device__ __forceinline__ int unit_len(int u) { return u < SMALL_UNITS ? UNIT_SMALL : UNIT_BIG; }
 
+// Merging the partial result (m2, l2, o2) of a unit into the running (m, l, o) of its block. The unit kernel and the
+// combine kernel both merge with exactly these operations, so the bits do not depend on which of them did it.
+__device__ __forceinline__ void merge_unit_scalars(float& m, float& l, float m2, float l2, float& fa, float& fb) {
+  const float mn = fmaxf(m, m2);
+  fa = exp2f(m - mn);
+  fb = exp2f(m2 - mn);
+  l = __fmaf_rn(l2, fb, __fmul_rn(l, fa));
+  m = mn;
+}
+__device__ __forceinline__ float merge_unit_value(float o, float o2, float fa, float fb) {
+  return __fmaf_rn(o2, fb, __fmul_rn(o, fa));
+}
+
 // Where a warp stands in its list of units: the unit's row, kv head and key range, and the next 16-key group.
 struct UnitCursor {
   int u;            // number of the unit among the step's units
@@ -452,6 +465,7 @@ attn_decode_units_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_
   uint32_t qf[KSTEPS][QW];
   float o[OB][4];
   float m_run[2], l_run[2];
+  float blk_o[OB][4], blk_m[2], blk_l[2];       // the block that is being merged from this warp's own units
   bool fresh = true;
   while (cc.valid) {
     while (ci.valid && issued - consumed < NSTAGE) {
@@ -503,38 +517,78 @@ attn_decode_units_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_
     __syncwarp();        // every lane has read the stage: it may be refilled
     ++consumed;
     if (cc.g + 1 >= cc.g_end) {
-      // the unit is complete: its unnormalised O and (max, sum), straight from the MMA fragments
-      const size_t head0 = (size_t)cc.n * Hq + (size_t)cc.kvh * G;
-      if constexpr (SMALLG) {
+      // The unit is complete. Its sum of weights over all lanes that hold keys of a head:
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
+      for (int j = 0; j < 2; ++j) {
+        if constexpr (SMALLG) {
           l_run[j] += __shfl_xor_sync(0xffffffffu, l_run[j], 4);
           l_run[j] += __shfl_xor_sync(0xffffffffu, l_run[j], 8);
           l_run[j] += __shfl_xor_sync(0xffffffffu, l_run[j], 16);
-          const int g = 2 * (lane & 3) + j;
-          if (g < G) {
-            const size_t slot = (head0 + g) * NPU + cc.unit;
-            float* dst = part_o + slot * HD + (lane >> 2);
+        } else {
+          l_run[j] += __shfl_xor_sync(0xffffffffu, l_run[j], 1);
+          l_run[j] += __shfl_xor_sync(0xffffffffu, l_run[j], 2);
+        }
+      }
+      // The 64-key units of one 256-key block that this warp computes all by itself are merged here, in rising order
+      // and with the arithmetic of `merge_unit` (the combine kernel merges a block's units the same way when they
+      // come from different warps, so the result does not depend on who computed what); the block then leaves one
+      // partial result, marked by a negative sum, in the slot of its first unit.
+      int write_unit = cc.unit;
+      bool write = true;
+      if (cc.unit < SMALL_UNITS) {
+        const int bu0 = max(unit_of(cc.lo), cc.unit & ~3), bu1 = min(unit_of(cc.p), cc.unit | 3);
+        if (bu1 > bu0 && cc.u - (cc.unit - bu0) >= u_begin && cc.u + (bu1 - cc.unit) < u_end) {
+          if (cc.unit == bu0) {
 #pragma unroll
-            for (int i = 0; i < OB; ++i) { dst[16 * i] = o[i][j]; dst[16 * i + 8] = o[i][2 + j]; }
-            if ((lane >> 2) == 0) *(float2*)(part_ml + slot * 2) = make_float2(m_run[j], l_run[j]);
+            for (int i = 0; i < OB; ++i) { blk_o[i][0] = o[i][0]; blk_o[i][1] = o[i][1]; blk_o[i][2] = o[i][2]; blk_o[i][3] = o[i][3]; }
+            blk_m[0] = m_run[0]; blk_m[1] = m_run[1]; blk_l[0] = l_run[0]; blk_l[1] = l_run[1];
+          } else {
+            float fa[2], fb[2];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) merge_unit_scalars(blk_m[j], blk_l[j], m_run[j], l_run[j], fa[j], fb[j]);
+#pragma unroll
+            for (int i = 0; i < OB; ++i)
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int j = SMALLG ? (e & 1) : (e >> 1);
+                blk_o[i][e] = merge_unit_value(blk_o[i][e], o[i][e], fa[j], fb[j]);
+              }
+          }
+          write = cc.unit == bu1;
+          if (write) {
+            write_unit = bu0;
+#pragma unroll
+            for (int i = 0; i < OB; ++i) { o[i][0] = blk_o[i][0]; o[i][1] = blk_o[i][1]; o[i][2] = blk_o[i][2]; o[i][3] = blk_o[i][3]; }
+            m_run[0] = blk_m[0]; m_run[1] = blk_m[1]; l_run[0] = -blk_l[0]; l_run[1] = -blk_l[1];
           }
         }
-      } else {
+      }
+      if (write) {
+        // unnormalised O and (max, sum), straight from the MMA fragments
+        const size_t head0 = (size_t)cc.n * Hq + (size_t)cc.kvh * G;
+        if constexpr (SMALLG) {
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
-          l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
-        }
+          for (int j = 0; j < 2; ++j) {
+            const int g = 2 * (lane & 3) + j;
+            if (g < G) {
+              const size_t slot = (head0 + g) * NPU + write_unit;
+              float* dst = part_o + slot * HD + (lane >> 2);
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int g = (lane >> 2) + 8 * h;
-          if (g < G) {
-            const size_t slot = (head0 + g) * NPU + cc.unit;
-            float* dst = part_o + slot * HD + 2 * (lane & 3);
+              for (int i = 0; i < OB; ++i) { dst[16 * i] = o[i][j]; dst[16 * i + 8] = o[i][2 + j]; }
+              if ((lane >> 2) == 0) *(float2*)(part_ml + slot * 2) = make_float2(m_run[j], l_run[j]);
+            }
+          }
+        } else {
 #pragma unroll
-            for (int i = 0; i < OB; ++i) *(float2*)(dst + 8 * i) = make_float2(o[i][2 * h], o[i][2 * h + 1]);
-            if ((lane & 3) == 0) *(float2*)(part_ml + slot * 2) = make_float2(m_run[h], l_run[h]);
+          for (int h = 0; h < 2; ++h) {
+            const int g = (lane >> 2) + 8 * h;
+            if (g < G) {
+              const size_t slot = (head0 + g) * NPU + write_unit;
+              float* dst = part_o + slot * HD + 2 * (lane & 3);
+#pragma unroll
+              for (int i = 0; i < OB; ++i) *(float2*)(dst + 8 * i) = make_float2(o[i][2 * h], o[i][2 * h + 1]);
+              if ((lane & 3) == 0) *(float2*)(part_ml + slot * 2) = make_float2(m_run[h], l_run[h]);
+            }
           }
         }
       }
@@ -544,48 +598,72 @@ attn_decode_units_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_
   }
 }
 
-// One block per (token row, query head): merges the row's units in rising order, normalises, rounds to bf16. The
-// units a row has follow from its position and the window alone, as in the kernel above.
+// One block per (token row, query head), COMBINE_SPLIT x HD threads: thread (s, d) merges, for dimension d, the blocks
+// s, s + COMBINE_SPLIT, ... of the row's key axis (a block: the up to four 64-key units of 256 keys below key 4096,
+// either already merged by the unit kernel or merged here in rising order with the same arithmetic; a 256-key unit
+// above); the COMBINE_SPLIT results are merged in order, normalised and rounded to bf16. Which units a row has follows
+// from its position and the window alone, as in the kernel above.
+constexpr int COMBINE_SPLIT = 4;
 __global__ void attn_combine_units_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                           const int* __restrict__ pos, const int* __restrict__ seq_row,
                                           const int* __restrict__ seg, __nv_bfloat16* __restrict__ out, int Hq, int HD,
                                           int NPU, int window, int long_from) {
-  extern __shared__ float s_f[];      // [units of the row]: exp2(max_i - max), then 2 floats of scratch per warp
+  __shared__ float s_m[COMBINE_SPLIT], s_l[COMBINE_SPLIT], s_o[COMBINE_SPLIT][128];
   fz_grid_launch_dependents();
-  fz_grid_wait();
-  const int n = blockIdx.y, h = blockIdx.x, tid = threadIdx.x, nthreads = blockDim.x;
-  __nv_bfloat16* orow = out + ((size_t)n * Hq + h) * HD;
+  const int n = blockIdx.y, h = blockIdx.x, d = threadIdx.x % HD, sub = threadIdx.x / HD;
   const int row = seq_row[n];
+  const bool skip = row >= 0 && seg[row * 4 + 1] >= long_from;
+  const int p = pos[n];
+  fz_grid_wait();
+  __nv_bfloat16* orow = out + ((size_t)n * Hq + h) * HD;
   if (row < 0) {
-    for (int d = tid; d < HD; d += nthreads) orow[d] = __float2bfloat16_rn(0.f);
+    if (sub == 0) orow[d] = __float2bfloat16_rn(0.f);
     return;
   }
-  if (seg[row * 4 + 1] >= long_from) return;
-  const int p = pos[n];
+  if (skip) return;
   const int lo = window > 0 ? max(0, p - window + 1) : 0;
-  const int u0 = unit_of(lo), cnt = unit_of(p) - u0 + 1;
-  const float* ml = part_ml + (((size_t)n * Hq + h) * NPU + u0) * 2;
-  const float* po = part_o + (((size_t)n * Hq + h) * NPU + u0) * HD;
-  float* s_red = s_f + NPU;
-  float M = -INFINITY;
-  for (int i = tid; i < cnt; i += nthreads) M = fmaxf(M, ml[2 * i]);
-#pragma unroll
-  for (int d = 16; d > 0; d >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, d));
-  if ((tid & 31) == 0) s_red[tid >> 5] = M;
-  __syncthreads();
-  M = s_red[0];
-  for (int w = 1; w < (nthreads >> 5); ++w) M = fmaxf(M, s_red[w]);
-  for (int i = tid; i < cnt; i += nthreads) s_f[i] = exp2f(ml[2 * i] - M);
-  __syncthreads();
-  // the sum of the weights: every thread adds the same terms in the same (rising) order
-  float L = 0.f;
-  for (int i = 0; i < cnt; ++i) L += ml[2 * i + 1] * s_f[i];
-  const float inv = 1.0f / L;
-  for (int d = tid; d < HD; d += nthreads) {
-    float acc = 0.f;
-    for (int i = 0; i < cnt; ++i) acc += po[(size_t)i * HD + d] * s_f[i];
-    orow[d] = __float2bfloat16_rn(acc * inv);
+  const int u0 = unit_of(lo), u1 = unit_of(p);
+  const float2* ml = (const float2*)part_ml + ((size_t)n * Hq + h) * NPU;
+  const float* po = part_o + ((size_t)n * Hq + h) * NPU * HD + d;
+  const int n_small = u0 < SMALL_UNITS ? (min(u1, SMALL_UNITS - 1) >> 2) - (u0 >> 2) + 1 : 0;
+  const int big0 = max(u0, SMALL_UNITS);
+  const int n_items = n_small + (u1 >= SMALL_UNITS ? u1 - big0 + 1 : 0);
+  float M = -INFINITY, L = 0.f, O = 0.f;
+  for (int k = sub; k < n_items; k += COMBINE_SPLIT) {
+    float Mb, Lb, Ob;
+    if (k < n_small) {
+      const int b = (u0 >> 2) + k;
+      const int bu0 = max(u0, 4 * b), bu1 = min(u1, 4 * b + 3);
+      const float2 first = ml[bu0];
+      Mb = first.x; Lb = fabsf(first.y); Ob = po[(size_t)bu0 * HD];
+      if (first.y >= 0.f) {           // not merged by the unit kernel: the block's units one by one
+        for (int u = bu0 + 1; u <= bu1; ++u) {
+          const float2 next = ml[u];
+          float fa, fb;
+          merge_unit_scalars(Mb, Lb, next.x, next.y, fa, fb);
+          Ob = merge_unit_value(Ob, po[(size_t)u * HD], fa, fb);
+        }
+      }
+    } else {
+      const int u = big0 + (k - n_small);
+      const float2 v = ml[u];
+      Mb = v.x; Lb = v.y; Ob = po[(size_t)u * HD];
+    }
+    float fa, fb;
+    merge_unit_scalars(M, L, Mb, Lb, fa, fb);
+    O = merge_unit_value(O, Ob, fa, fb);
   }
+  if (d == 0) { s_m[sub] = M; s_l[sub] = L; }
+  s_o[sub][d] = O;
+  __syncthreads();
+  if (sub != 0) return;
+  for (int k = 1; k < COMBINE_SPLIT; ++k) {
+    if (s_m[k] == -INFINITY) continue;        // that share of the blocks was empty
+    float fa, fb;
+    merge_unit_scalars(M, L, s_m[k], s_l[k], fa, fb);
+    O = merge_unit_value(O, s_o[k][d], fa, fb);
+  }
+  orow[d] = __float2bfloat16_rn(O / L);
 }
 
 // One block per (token row, query head): merges the partitions in rising order, normalises, rounds to bf16.
@@ -651,7 +729,7 @@ int launch_units(const void* q, const void* k_pool, long long pool_rows, const i
             scale * 1.4426950408889634f, window, long_from, err);
   FZ_LAUNCH_CHECK();
   dim3 cgrid(Hq, N);
-  fz_launch(attn_combine_units_kernel, cgrid, dim3(HD < 128 ? 64 : 128), (size_t)(NPU + 8) * 4, stream, (const float*)part_o,
+  fz_launch(attn_combine_units_kernel, cgrid, dim3(COMBINE_SPLIT * HD), 0, stream, (const float*)part_o,
             (const float*)part_ml, pos, seq_row, seg, (__nv_bfloat16*)out, Hq, HD, NPU, window, long_from);
   FZ_LAUNCH_CHECK();
   return FZ_OK;
@@ -661,10 +739,9 @@ template <int HD, int BOX>
 int launch_tma(const void* q, const void* k_pool, long long pool_rows, const int* pos, const int* seq_row, const int* seg,
                const int* table, int mb, int page_size, void* out, float* part_o, float* part_ml, int N, int Hq, int Hkv,
                float scale, int window, int NPU, int long_from, int* err, cudaStream_t stream) {
-  static const int cfg = getenv("FZB200_ATTN_CFG") ? atoi(getenv("FZB200_ATTN_CFG")) : 0;
 #define FZ_U(NS_, MB_, SG_) return launch_units<HD, BOX, NS_, MB_, SG_>(q, k_pool, pool_rows, pos, seq_row, seg, table, mb, page_size, out, part_o, part_ml, N, Hq, Hkv, scale, window, NPU, long_from, err, stream)
-  if (Hq / Hkv > 8 || cfg == 3) FZ_U(3, 2, false);
-  if (cfg == 1) FZ_U(2, 3, true);
+  // three stages of 16 keys per warp and two CTAs per SM (eight warps with 24 KB in flight each) measured best
+  if (Hq / Hkv > 8) FZ_U(3, 2, false);
   FZ_U(3, 2, true);
 #undef FZ_U
 }

@@ -47,7 +47,9 @@ __device__ __forceinline__ float ld_dsmem(uint32_t addr, uint32_t rank) {
   uint32_t remote;
   float v;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  // (volatile keeps it behind the cluster barrier, itself a volatile asm; no memory clobber, so that the loads of the
+  // next column may be issued before this column's result is stored)
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote));
   return v;
 }
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + __expf(-g)) * u; }
@@ -255,11 +257,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const int n_my = cols > (int)rank ? (cols - (int)rank + p.splits - 1) / p.splits : 0;   // columns rank, rank + S, ...
       for (int i0 = 0; i0 < n_my; i0 += 16) {
         const int ni = min(16, n_my - i0);
+#pragma unroll 2
         for (int i = 0; i < ni; ++i) {
           const int c = (int)rank + (i0 + i) * p.splits;
           float acc = 0.f;
           if (p.splits > 1) {
-            for (int sp = 0; sp < p.splits; ++sp) acc += ld_dsmem(base + (uint32_t)(c * BM) * 4u, (uint32_t)sp);   // split order
+            // all splits' partials are asked for before the first is used (a cluster holds at most 8 CTAs); the sum
+            // runs in split order
+            float v[8];
+#pragma unroll
+            for (int sp = 0; sp < 8; ++sp) v[sp] = sp < p.splits ? ld_dsmem(base + (uint32_t)(c * BM) * 4u, (uint32_t)sp) : 0.f;
+#pragma unroll
+            for (int sp = 0; sp < 8; ++sp) acc += v[sp];
           } else {
             acc = ((const float*)smem)[c * BM + r];
           }
@@ -609,9 +618,10 @@ FZ_API int fz_gemm_tc(const void* x, const void* w, const float* bias, void* c, 
 }
 
 // Can the query/key/value product of M token rows with heads of size hd end in the rotation and the cache write?
-// (the few-token mode only, and a 128-feature tile must hold whole heads)
+// (a 128-feature tile must hold whole heads; up to 32 rows, where the separate rotation kernel costs more than its work:
+// with more rows the epilogue's per-token lookups outweigh the launch they save)
 FZ_API int fz_gemm_tc_qkv_rope_check(int M, int hd) {
-  return (M >= 1 && M <= 128 && hd >= 2 && hd % 2 == 0 && 128 % hd == 0) ? FZ_OK : FZ_BAD_SHAPE;
+  return (M >= 1 && M <= 32 && hd >= 2 && hd % 2 == 0 && 128 % hd == 0) ? FZ_OK : FZ_BAD_SHAPE;
 }
 
 // x: [M, K] bf16; w: [(Hq + 2 Hkv) hd, K] bf16, rows [q heads | k heads | v heads]; bias float32 or null. Rotates the q
@@ -648,7 +658,7 @@ static int gemm_tc_impl(const void* x, const void* w, const float* bias, void* c
   int st = fz_gemm_tc_check(x, w, M, N, K);
   if (st != FZ_OK) return st;
   if (out_dtype != FZ_F32 && out_dtype != FZ_BF16) return FZ_BAD_DTYPE;
-  if (fused.rope && M > 128) return FZ_BAD_SHAPE;
+  if (fused.rope && M > 32) return FZ_BAD_SHAPE;
   Params p = fused;
   p.c_f32 = out_dtype == FZ_F32 ? (float*)c : nullptr;
   p.c_bf16 = out_dtype == FZ_BF16 ? (__nv_bfloat16*)c : nullptr;

@@ -102,3 +102,35 @@ def test_padding_rows_and_row_independence():
     part = torch.empty(40, Hq * hd, dtype=BF, device="cuda")
     cu.paged_attention(q[1:41].contiguous(), cc, Meta(list(range(100, 140)), [1] * 40, table, "cuda"), part, Hq, Hkv, hd, hd ** -0.5, 0)
     assert torch.equal(part, full[1:41])
+
+
+@pytest.mark.parametrize("Hq,Hkv,hd", [(8, 2, 128), (12, 1, 64)])
+def test_a_row_alone_and_among_hundreds(Hq, Hkv, hd):
+    """With few rows every 64-key unit of a row is computed by another warp and the combine kernel merges them; with
+    hundreds of rows a warp computes whole 256-key blocks and merges their units itself. Both give the same bits."""
+    from fusezap_core_b200.kernels import cuda_ops
+    cu = cuda_ops("bfloat16")
+    g = torch.Generator().manual_seed(11)
+    lengths = [1500, 900, 333]
+    bs = 16
+    mb = -(-max(lengths) // bs)
+    table = [list(range(r * mb, (r + 1) * mb)) for r in range(3)]
+    cp = make_cache(3 * mb, Hkv, bs, hd, BF, "cpu")
+    fill_cache(cp, table, lengths, g)
+    cc = make_cache(3 * mb, Hkv, bs, hd, BF, "cuda")
+    cc.pool.copy_(cp.pool)
+    pos = [1499, 899, 332] + [int(x) for x in torch.randint(200, 1500, (400,), generator=g)]
+    seq = [0, 1, 2] + [0] * 400
+    q = torch.randn(len(pos), Hq * hd, generator=g).to(BF).cuda()
+    q[3:] = q[0]          # the crowd asks request 0 at other positions
+    many = torch.empty(len(pos), Hq * hd, dtype=BF, device="cuda")
+    # short portions only (no run of 8 consecutive positions): every row goes through the split kernel
+    cu.paged_attention(q, cc, Meta(pos, seq, table, "cuda"), many, Hq, Hkv, hd, hd ** -0.5, 0)
+    for i in range(3):
+        one = torch.empty(1, Hq * hd, dtype=BF, device="cuda")
+        cu.paged_attention(q[i:i + 1].contiguous(), cc, Meta([pos[i]], [seq[i]], table, "cuda"), one, Hq, Hkv, hd, hd ** -0.5, 0)
+        assert torch.equal(one[0], many[i]), f"row {i}"
+    few = torch.empty(3, Hq * hd, dtype=BF, device="cuda")
+    cu.paged_attention(q[:3].contiguous(), cc, Meta(pos[:3], seq[:3], table, "cuda"), few, Hq, Hkv, hd, hd ** -0.5, 0)
+    assert torch.equal(few, many[:3])
+    cu.check_errors()

@@ -113,7 +113,7 @@ def test_fused_gate_up_swiglu(M, I, K):
 
 @pytest.mark.parametrize("Hq,Hkv,hd,K,bs", [(32, 8, 128, 4096, 16), (14, 2, 64, 896, 8), (3, 1, 64, 128, 5), (5, 5, 32, 200, 16),
                                             (2, 1, 128, 64, 3)])
-@pytest.mark.parametrize("M", [1, 8, 19, 128])
+@pytest.mark.parametrize("M", [1, 8, 19, 32])
 def test_qkv_product_with_rotation_and_cache_write(Hq, Hkv, hd, K, bs, M):
     """The q/k/v product that ends in the rotation and the cache write gives the bits of the product followed by the
     rotation kernel: q, and every slot of the key and value pools (written ones and untouched ones); with a bias, a
