@@ -602,7 +602,10 @@ FZ_API int fz_gemm_tc_check(const void* x, const void* w, int M, int N, int K) {
 // order never depends on how many rows share the step.
 FZ_API int fz_gemm_tc_splits(int N, int K) {
   const int tiles = (N + BM - 1) / BM, kblocks = (K + BK - 1) / BK;
-  int s = 296 / tiles;               // two CTAs on each of the 148 SMs
+  // Two CTAs fit each of the 148 SMs, but clusters do not pack the GPCs perfectly: measured on B200, 48 clusters of 6
+  // (288 CTAs) need a second wave (19 us for the 6144 x 4096 product) where 48 of 5 (13 us) and 32 of 8 do not. So the
+  // CTA count stays at or below 256.
+  int s = 256 / tiles;
   if (s > kblocks / 4) s = kblocks / 4;
   if (s > 8) s = 8;                  // a portable cluster holds at most 8 CTAs
   return s < 1 ? 1 : s;
