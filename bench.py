@@ -104,6 +104,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--preset", default="llama-3.1-8b")
     ap.add_argument("--prefill-tokens", type=int, default=2048)
+    ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page (the engine's block_size)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
     ap.add_argument("--no-e2e", action="store_true")
     a = ap.parse_args()
@@ -128,7 +129,7 @@ def main() -> int:
     L = cfg["num_hidden_layers"]
     pk = peaks()
     dev = torch.device("cuda:0")
-    page = 16
+    page = a.page_size
     t0 = time.time()
     model = random_model(cfg, "bfloat16", dev, seed=0, max_len=a.context)
     torch.cuda.synchronize()
