@@ -138,22 +138,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         load_weights(i, i);
       }
       fz_grid_wait();
-      for (int i = 0; i < nkb; ++i) {
-        const int s = i % p.stages, round = i / p.stages;
+      for (int i = 0, s = 0, round = 0; i < nkb; ++i) {
         if (round > 0) {
           if (!mbar_wait(&empty[s], (round - 1) & 1)) { flag[1] = 1; break; }
           mbar_expect_tx(&full[s], STAGE_BYTES);
           load_weights(i, s);
         }
         load_activations(i, s);
+        if (++s == p.stages) { s = 0; ++round; }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc(BM, BN);
       bool ok = true;
-      for (int i = 0; i < nkb && ok; ++i) {
-        const int s = i % p.stages, round = i / p.stages;
+      for (int i = 0, s = 0, round = 0; i < nkb && ok; ++i) {
         if (!mbar_wait(&full[s], round & 1)) { flag[1] = 1; ok = false; break; }
         tc_fence_after();
         const uint8_t* sa = smem + (size_t)s * STAGE_BYTES;
@@ -163,6 +162,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           umma_bf16(tmem_d, da + (uint64_t)(k * UMMA_K * 2 / 16), db + (uint64_t)(k * UMMA_K * 2 / 16), idesc,
                     (i > 0 || k > 0) ? 1u : 0u);
         umma_commit(&empty[s]);
+        if (++s == p.stages) { s = 0; ++round; }
       }
       umma_commit(acc_ready);   // arrives when every MMA issued so far has finished (at once if none was issued)
     }
@@ -390,13 +390,14 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         tma_load_2d(smem + (size_t)i * STAGE_BYTES + A_BYTES, &map_w, &full[i], i * BK, (first / tiles_m) * BN);
       }
       fz_grid_wait();
-      int it = 0;
+      // (the stage and its round are kept by counting: this one lane feeds the whole pipeline, and a division per
+      // k-block would make it the slowest part)
+      int it = 0, s = 0, round = 0;
       bool ok = true;
       for (int j = 0; j < my_tiles && ok; ++j) {
         const int tile = (int)blockIdx.x + j * (int)gridDim.x;
         const int tm = tile % tiles_m, tn = tile / tiles_m;
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          const int s = it % p.stages, round = it / p.stages;
           uint8_t* sa = smem + (size_t)s * STAGE_BYTES;
           if (it >= early) {
             if (round > 0 && !mbar_wait(&empty[s], (round - 1) & 1)) { flag[0] = 1; ok = false; break; }
@@ -404,21 +405,21 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             tma_load_2d(sa + A_BYTES, &map_w, &full[s], kb * BK, tn * BN);
           }
           tma_load_2d(sa, &map_x, &full[s], kb * BK, tm * BM);
+          if (++s == p.stages) { s = 0; ++round; }
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc(BM, BN);
-      int it = 0;
+      int s = 0, round = 0;
       bool ok = true;
       for (int j = 0; j < my_tiles && ok; ++j) {
         const int acc = j & 1;
         if (j >= 2 && !mbar_wait(&acc_empty[acc], ((j >> 1) - 1) & 1)) { flag[0] = 1; break; }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
-        for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          const int s = it % p.stages, round = it / p.stages;
+        for (int kb = 0; kb < kblocks; ++kb) {
           if (!mbar_wait(&full[s], round & 1)) { flag[0] = 1; ok = false; break; }
           tc_fence_after();
           const uint8_t* sa = smem + (size_t)s * STAGE_BYTES;
@@ -427,6 +428,7 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
           for (int k = 0; k < BK / UMMA_K; ++k)
             umma_bf16(tmem_d, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (kb > 0 || k > 0) ? 1u : 0u);
           umma_commit(&empty[s]);
+          if (++s == p.stages) { s = 0; ++round; }
         }
         umma_commit(&acc_full[acc]);
       }
