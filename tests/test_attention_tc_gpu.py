@@ -47,7 +47,7 @@ def close(o, op, what):
 
 
 @pytest.mark.parametrize("Hq,Hkv,hd", [(4, 1, 128), (14, 2, 64), (8, 8, 64), (16, 1, 128), (10, 2, 128), (3, 3, 64)])
-@pytest.mark.parametrize("bs,window", [(16, 0), (8, 300), (5, 0)])
+@pytest.mark.parametrize("bs,window", [(16, 0), (8, 300), (5, 0), (64, 0), (48, 200)])
 def test_decode_rows_at_long_contexts(Hq, Hkv, hd, bs, window):
     lengths = [1100, 257, 1, 640]
     # single tokens at the ends of partitions and tiles, the first token, and short portions (below 8 rows)
@@ -68,7 +68,7 @@ def test_decode_rows_past_4096_keys(Hq, Hkv, hd, bs, window):
 
 
 @pytest.mark.parametrize("Hq,Hkv,hd", [(4, 1, 128), (14, 2, 64), (8, 8, 64), (2, 1, 128)])
-@pytest.mark.parametrize("bs,window", [(16, 0), (8, 100), (3, 0)])
+@pytest.mark.parametrize("bs,window", [(16, 0), (8, 100), (3, 0), (64, 0), (128, 90), (48, 0)])
 def test_prefill_portions(Hq, Hkv, hd, bs, window):
     lengths = [400, 70, 200]
     # a first portion from position 0 (three tiles), a later portion that continues a request (ragged last tile),
