@@ -71,6 +71,9 @@ def build_parser() -> argparse.ArgumentParser:
     r.add_argument("--norm-noise", action="store_true", help="norm weights 1 + N(0, 0.02) instead of 1")
     r.add_argument("--num-layers", type=int, default=None, help="override the layer count")
     sub.add_parser("build", help="compile the CUDA kernels")
+    sub.add_parser("replay", add_help=False, help="trace replay: token ids from standard input, logits to files "
+                                                   "(the options of bin/trace_run)")
+    sub.add_parser("bench", add_help=False, help="the benchmark of the source tree (bench.py beside the package)")
     return ap
 
 
@@ -142,6 +145,18 @@ def cmd_random_weights(a: argparse.Namespace) -> int:
 
 
 def main(argv: list[str] | None = None) -> int:
+    argv = sys.argv[1:] if argv is None else list(argv)
+    if argv and argv[0] == "replay":          # its options are its own: hand the rest over
+        from .replay import main as replay_main
+        return replay_main(argv[1:])
+    if argv and argv[0] == "bench":
+        import runpy
+        path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bench.py")
+        if not os.path.exists(path):
+            raise SystemExit(f"bench.py is not beside the package (looked for {path})")
+        sys.argv = [path] + argv[1:]
+        runpy.run_path(path, run_name="__main__")
+        return 0
     a = build_parser().parse_args(argv)
     if a.cmd == "generate":
         return cmd_generate(a)

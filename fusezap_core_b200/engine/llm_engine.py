@@ -94,6 +94,28 @@ class LLMEngine:
         self.stats = {"steps": 0, "decode_steps": 0, "prefill_steps": 0, "mixed_steps": 0, "tokens": 0,
                       "preemptions": 0, "graph_replays": 0, "lookahead_steps": 0, "h2d_bytes": 0, "d2h_bytes": 0}
 
+    # ---- a model and its engine in one call
+    @classmethod
+    def from_pretrained(cls, path: str, dtype: str = "bfloat16", device: str = "cuda:0", max_model_len: int = 2048,
+                        ops=None, **engine_options) -> "LLMEngine":
+        """`load_model(path, dtype, device, max_len=max_model_len)` and an engine over it; `engine_options` are the
+        constructor's (num_blocks, block_size, max_num_seqs, ...)."""
+        from .model import load_model
+        model = load_model(path, dtype, device, max_len=max_model_len, ops=ops)
+        return cls(model, max_model_len=max_model_len, **engine_options)
+
+    @classmethod
+    def from_random(cls, config: dict | str, seed: int = 0, dtype: str = "bfloat16", device: str = "cuda:0",
+                    max_model_len: int = 2048, ops=None, **engine_options) -> "LLMEngine":
+        """An engine over a model with seeded random weights drawn on the device. `config`: a config.json dictionary, or
+        the name of a preset of this package (`tiny-llama`, `llama-3.1-8b`, ...)."""
+        from .model import random_model
+        if isinstance(config, str):
+            from ..cli import load_preset
+            config = load_preset(config)
+        model = random_model(config, dtype, device, seed=seed, max_len=max_model_len, ops=ops)
+        return cls(model, max_model_len=max_model_len, **engine_options)
+
     # ---- requests
     def add_request(self, prompt_ids: Seq[int], params: SamplingParams | None = None, request_id: int | None = None) -> int:
         params = params or SamplingParams()

@@ -196,3 +196,16 @@ def test_launching_ahead_changes_no_token(models):
     assert eng.stats["lookahead_steps"] > 5
     assert a[3][-1][1:] == (True, "stop") and len(a[3]) <= 13
     assert a[1][-1] == ((), True, "abort") and a[0][-1][1:] == (True, "length") and len(a[2]) == 17
+
+
+def test_engine_in_one_call(tmp_path):
+    """`LLMEngine.from_pretrained` and `from_random` build the model and the engine together."""
+    d, cfg, opts = make_model_dir("tiny_llama", tmp_path)
+    w = read_weights(d)
+    eng = LLMEngine.from_pretrained(d, "float32", "cpu", max_model_len=64, ops=PlainOps(), num_blocks=16, block_size=8,
+                                    max_num_seqs=2)
+    P = prompts(cfg, (5,), seed=3)
+    assert eng.generate(P, SamplingParams(max_tokens=4, ignore_eos=True)) == [greedy_reference(cfg, w, P[0], 4)]
+    rnd = LLMEngine.from_random("tiny-llama", seed=1, dtype="float32", device="cpu", max_model_len=64, ops=PlainOps(),
+                                num_blocks=16, block_size=8, max_num_seqs=2)
+    assert len(rnd.generate([[1, 2, 3]], SamplingParams(max_tokens=3, ignore_eos=True))[0]) == 3
