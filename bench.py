@@ -167,10 +167,12 @@ def main() -> int:
         runner, meta = eng.runner, eng.runner.meta
         seqs = [eng.seqs[r] for r in rids]
         bucket = next(b for b in eng._buckets if b >= batch)
+        def graph_key():      # the captured step of this bucket (greedy rows, ids picked on the device)
+            return next(k for k in eng._graphs if k[0] == bucket)
         def one_step(i: int):
             portions = [Portion(s.seq_id, [s.token_at(s.num_computed)], [0]) for s in seqs]
             starts = runner.prepare(portions, pad_rows=bucket, pad_wanted=bucket)
-            eng._graphs[(bucket, True)].replay()
+            eng._graphs[graph_key()].replay()
             runner.commit(portions, starts)
             for s, st in zip(seqs, starts):   # the next token is fixed beforehand: nothing is read back in this loop
                 s.num_computed = st + 1
@@ -190,7 +192,7 @@ def main() -> int:
         ms = start.elapsed_time(end) / steps
         ctx_mean = ctx0 + steps / 2
         out.update(ms=ms, tok_s=batch * 1000.0 / ms, context=ctx_mean,
-                   launches=steps * eng.launches_per_graph.get((bucket, True), 0) + (model.ops.launches - launches0),
+                   launches=steps * eng.launches_per_graph.get(graph_key(), 0) + (model.ops.launches - launches0),
                    bytes=model.weight_bytes() + batch * ctx_mean * kv_bytes_per_token)
         if e2e:
             eng.lookahead = True        # the entry point's default; off above, where the steps are driven by hand

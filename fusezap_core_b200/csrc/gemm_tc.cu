@@ -53,6 +53,16 @@ __device__ __forceinline__ float ld_dsmem(uint32_t addr, uint32_t rank) {
   return v;
 }
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + __expf(-g)) * u; }
+// (value, index) order of numpy.argmax: a NaN is the maximum, among equals the lower index wins; index 0x7fffffff: none
+__device__ __forceinline__ bool am_better(float v, int i, float bv, int bi) {
+  if (i == 0x7fffffff) return false;
+  if (bi == 0x7fffffff) return true;
+  const bool vn = isnan(v), bn = isnan(bv);
+  if (vn != bn) return vn;
+  if (vn) return i < bi;
+  if (v != bv) return v > bv;
+  return i < bi;
+}
 
 struct Params {
   float* c_f32;            // exactly one of c_f32 / c_bf16 is set
@@ -80,6 +90,11 @@ struct Params {
   __nv_bfloat16* v_pool;
   long long page_stride;
   int page_size, write, Hq, Hkv, hd, max_len;
+  // argmax != 0 (few tokens, no split): nothing is stored but, per token row and 128-feature tile, the largest value
+  // and its feature index (numpy's order: a NaN is the maximum, the lower index wins among equals)
+  int argmax;
+  float* am_val;           // [rows][tiles]
+  int* am_idx;
 };
 
 template <int BN>
@@ -233,10 +248,43 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
           for (int j = 0; j < 16; ++j) v[j] = 0.f;
         }
-        if (direct) store16(v, c);
+        if (p.argmax) {
+          // the tile's best (value, feature) per token row: over the warp by shuffles, over the four warps through the
+          // (idle) stage buffers
+          const float bv = (p.bias && a_row < a_limit) ? p.bias[a_row] : 0.f;
+          float* am_v = (float*)smem;                 // [4 warps][BN]
+          int* am_i = (int*)smem + 4 * BN;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            float x = v[j] + bv;
+            int ix = a_row < a_limit ? a_row : 0x7fffffff;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+              const float ox = __shfl_xor_sync(0xffffffffu, x, o);
+              const int oi = __shfl_xor_sync(0xffffffffu, ix, o);
+              if (am_better(ox, oi, x, ix)) { x = ox; ix = oi; }
+            }
+            if (lane == 0) { am_v[quad * BN + c + j] = x; am_i[quad * BN + c + j] = ix; }
+          }
+        } else if (direct) store16(v, c);
         else {
 #pragma unroll
           for (int j = 0; j < 16; ++j) part[(c + j) * BM] = v[j];
+        }
+      }
+      if (p.argmax) {
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const int m = b0 + r;                        // thread r merges column r of the four warps
+        if (r < BN && m < b_limit) {
+          const float* am_v = (const float*)smem;
+          const int* am_i = (const int*)smem + 4 * BN;
+          float x = am_v[r];
+          int ix = am_i[r];
+#pragma unroll
+          for (int w = 1; w < 4; ++w)
+            if (am_better(am_v[w * BN + r], am_i[w * BN + r], x, ix)) { x = am_v[w * BN + r]; ix = am_i[w * BN + r]; }
+          p.am_val[(size_t)m * gridDim.x + tile_a] = x;
+          p.am_idx[(size_t)m * gridDim.x + tile_a] = ix;
         }
       }
     }
@@ -644,6 +692,64 @@ FZ_API int fz_gemm_tc_qkv_rope(const void* x, const void* w, const float* bias, 
   f.k_pool = (__nv_bfloat16*)k_pool; f.v_pool = (__nv_bfloat16*)v_pool; f.page_stride = page_stride;
   f.page_size = page_size; f.write = write; f.Hq = Hq; f.Hkv = Hkv; f.hd = hd; f.max_len = max_len;
   return gemm_tc_impl(x, w, bias, q_out, FZ_BF16, M, (Hq + 2 * Hkv) * hd, K, f, err, stream);
+}
+
+// The best (value, index) of a row over its tiles' partial results, in tile order; out[r] = the index (0 if none).
+__global__ void argmax_tiles_kernel(const float* __restrict__ val, const int* __restrict__ idx, int tiles, int* __restrict__ out) {
+  fz_grid_launch_dependents();
+  fz_grid_wait();
+  __shared__ float s_v[32];
+  __shared__ int s_i[32];
+  const int r = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float x = 0.f;
+  int ix = 0x7fffffff;
+  for (int t = threadIdx.x; t < tiles; t += blockDim.x) {
+    const float v = val[(size_t)r * tiles + t];
+    const int i = idx[(size_t)r * tiles + t];
+    if (am_better(v, i, x, ix)) { x = v; ix = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ox = __shfl_xor_sync(0xffffffffu, x, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, ix, o);
+    if (am_better(ox, oi, x, ix)) { x = ox; ix = oi; }
+  }
+  if (lane == 0) { s_v[warp] = x; s_i[warp] = ix; }
+  __syncthreads();
+  if (warp == 0) {
+    const int nw = blockDim.x >> 5;
+    x = lane < nw ? s_v[lane] : 0.f;
+    ix = lane < nw ? s_i[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ox = __shfl_xor_sync(0xffffffffu, x, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, ix, o);
+      if (am_better(ox, oi, x, ix)) { x = ox; ix = oi; }
+    }
+    if (lane == 0) out[r] = ix == 0x7fffffff ? 0 : ix;
+  }
+}
+
+// Can `fz_gemm_tc_argmax` take the product? Few token rows, and so many output tiles that K is not split.
+FZ_API int fz_gemm_tc_argmax_check(int M, int N, int K) {
+  return (M >= 1 && M <= 128 && N >= 1 && K >= 8 && K % 8 == 0 && fz_gemm_tc_splits(N, K) == 1) ? FZ_OK : FZ_BAD_SHAPE;
+}
+
+// ids[m] = argmax_n (x[m] . w[n] + bias[n]), numpy's order, without writing the products out. scratch_val / scratch_idx:
+// M * ceil(N / 128) elements each.
+FZ_API int fz_gemm_tc_argmax(const void* x, const void* w, const float* bias, int M, int N, int K, float* scratch_val,
+                             int* scratch_idx, int* ids, int* err, cudaStream_t stream) {
+  if (fz_gemm_tc_argmax_check(M, N, K) != FZ_OK) return FZ_BAD_SHAPE;
+  Params f{};
+  f.argmax = 1;
+  f.am_val = scratch_val;
+  f.am_idx = scratch_idx;
+  int st = gemm_tc_impl(x, w, bias, scratch_val, FZ_F32, M, N, K, f, err, stream);
+  if (st != FZ_OK) return st;
+  fz_launch(argmax_tiles_kernel, dim3(M), dim3(256), 0, stream, (const float*)scratch_val, (const int*)scratch_idx,
+            (N + BM - 1) / BM, ids);
+  FZ_LAUNCH_CHECK();
+  return FZ_OK;
 }
 
 // Fused gate/up product and SwiGLU: w is [2 I, K] with rows in blocks of 128 = [64 gate rows | 64 up rows] of the same 64

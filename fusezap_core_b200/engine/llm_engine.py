@@ -90,6 +90,7 @@ class LLMEngine:
         self._graphs: dict[tuple, torch.cuda.CUDAGraph] = {}     # (bucket, all rows greedy) -> captured step
         self.launches_per_graph: dict[tuple, int] = {}           # kernels of this package in one replay of it
         self._greedy_step = True
+        self._ids_only = False
         self._buckets = sorted({min(1 << i, R) for i in range(R.bit_length() + 1)})
         self.stats = {"steps": 0, "decode_steps": 0, "prefill_steps": 0, "mixed_steps": 0, "tokens": 0,
                       "preemptions": 0, "graph_replays": 0, "lookahead_steps": 0, "h2d_bytes": 0, "d2h_bytes": 0}
@@ -254,6 +255,7 @@ class LLMEngine:
             unif_h[i] = seq.sampler.next_uniform() if device_row else 0.0
         # all rows greedy: the row-split argmax kernel picks the tokens; else the sampling kernel (argmax for its greedy rows)
         self._greedy_step = all(s.params.greedy or not s.params.on_device for s, _ in rows)
+        self._ids_only = all(s.params.greedy and s.params.on_device for s, _ in rows)
         bucket = next((b for b in self._buckets if b >= len(portions)), None) if decode_only and self.cuda_graphs else None
         pad = bucket or 0
         starts = runner.prepare(portions, pad_rows=pad, pad_wanted=pad)
@@ -267,7 +269,7 @@ class LLMEngine:
             self._unif_d[:n_w].copy_(unif_h[:n_w], non_blocking=True)
         st["h2d_bytes"] += runner.meta.size * 4 + n_w * 12
         if bucket is not None:
-            key = (bucket, self._greedy_step)
+            key = (bucket, self._greedy_step, self._ids_only)
             g = self._graphs.get(key)
             if g is None:
                 # warm-up (builds, sets kernel attributes, sizes the buffers) on a copy of the ids the step may read
@@ -284,7 +286,7 @@ class LLMEngine:
             g.replay()
             ops.launches += self.launches_per_graph[key]
             st["graph_replays"] += 1
-            logits = runner.ws.get("logits", (n_w, self.model.spec.vocab_size), torch.float32)
+            logits = None if self._ids_only else runner.ws.get("logits", (n_w, self.model.spec.vocab_size), torch.float32)
         else:
             logits = self._eager(n_w)
         runner.commit(portions, starts)
@@ -305,8 +307,13 @@ class LLMEngine:
         st[kind] += 1
         return _Launched(rows, slot, logits, event, all_produce)
 
-    def _eager(self, n_wanted: int) -> torch.Tensor:
-        logits = self.runner.forward()
+    def _eager(self, n_wanted: int) -> torch.Tensor | None:
+        # a step whose rows are all greedy and picked on the device needs no logits: the lm_head product may then keep
+        # only the largest value of every row
+        ids_only = n_wanted > 0 and self._ids_only
+        logits = self.runner.forward(self._ids_d[:n_wanted] if ids_only else None)
+        if logits is None:
+            return None
         if n_wanted and self._greedy_step:
             self.ops.argmax(logits, self._ids_d[:n_wanted])
         elif n_wanted:

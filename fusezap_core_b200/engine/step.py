@@ -220,8 +220,10 @@ class StepRunner:
             lc.state = {name: t for (entry, name), t in cache.states.tensors.items() if entry == n}
             self.layer_caches.append(lc)
 
-    def forward(self) -> torch.Tensor:
-        """Runs the model over the metadata already filled; returns logits (n_wanted, vocab) float32."""
+    def forward(self, ids_out: torch.Tensor | None = None) -> torch.Tensor | None:
+        """Runs the model over the metadata already filled; returns logits (n_wanted, vocab) float32. With `ids_out`
+        (int32, n_wanted): if the kernel table can pick the largest logit of every wanted row without writing the logits
+        out, it does, `ids_out` receives the token ids and None is returned; otherwise logits as usual."""
         model, ctx, meta = self.model, self.ctx, self.meta
         spec = model.spec
         x = self.ws.get("x", (meta.n_rows, spec.hidden_size), torch.float32)
@@ -232,6 +234,9 @@ class StepRunner:
         logits = self.ws.get("logits", (meta.n_wanted, spec.vocab_size), torch.float32)
         if meta.n_wanted:
             h = model.final_norm.forward(ctx, x, delta, rows=meta.sel, n_rows=meta.n_wanted)
+            fused = getattr(self.ops, "linear_argmax", None) if ids_out is not None else None
+            if fused is not None and fused(h, model.lm_head, None, ids_out):
+                return None
             self.ops.linear(h, model.lm_head, None, logits)
         return logits
 

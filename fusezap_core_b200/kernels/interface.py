@@ -76,6 +76,11 @@ class Ops:
         """gate_up: (N, 2 I) T = [gate | up]; out[n, i] = T(silu(gate[n, i]) * up[n, i]), silu in float32."""
         raise NotImplementedError
 
+    def linear_argmax(self, a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor) -> bool:
+        """out[m] = argmax_n (a[m] . w[n] + bias[n]) (the order of `argmax` below) without writing the products out.
+        Optional: returns False, having done nothing, if this table has no such kernel for these sizes."""
+        return False
+
     def argmax(self, logits: torch.Tensor, out: torch.Tensor) -> None:
         """out[r] = first index of the row's maximum (a NaN counts as the maximum, the first one wins); int32."""
         raise NotImplementedError

@@ -52,6 +52,8 @@ class CudaOps(Ops):
         self.use_tensor_cores = self.tc is not None
         self.prefill_tcgen05 = True        # False: long portions on the mma.sync flash-attention kernel
         self.fuse_swiglu = True            # gate/up product and SwiGLU in one kernel where the sizes allow it
+        self.fuse_argmax = True            # lm_head product and argmax in one pass where no logits are asked for
+        self._lm_scratch = None
         self.fuse_rope = True              # q/k/v product, rotation and cache write in one kernel (few-token steps)
         self._attn_scratch: torch.Tensor | None = None      # float32 partial outputs of the split decode attention
 
@@ -227,6 +229,30 @@ class CudaOps(Ops):
             c_int(table.shape[1]), _p(kp), _p(vp), c_longlong(page_stride), c_int(cache.page_size),
             c_int(1 if cache.write else 0), _p(q_out), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
             c_int(cos.shape[0]), _p(self.err), self._stream()), "linear_rope_kv_write (tensor cores)")
+        return True
+
+    def linear_argmax(self, a, w, bias, out) -> bool:
+        m, k = a.shape
+        n = w.shape[0]
+        if not (self.use_tensor_cores and self.fuse_argmax and self.dtype == torch.bfloat16) or \
+                self.tc.fz_gemm_tc_argmax_check(c_int(m), c_int(n), c_int(k)) != 0 or \
+                self.tc.fz_gemm_tc_check(_p(a), _p(w), c_int(m), c_int(n), c_int(k)) != 0:
+            return False
+        self._want(a, "linear input", (torch.bfloat16,), 2)
+        self._want(w, "linear weight", (torch.bfloat16,), 2)
+        self._want(out, "argmax output", (torch.int32,), 1)
+        if bias is not None:
+            self._want(bias, "linear bias", (torch.float32,), 1)
+        if w.shape[1] != k or out.shape[0] != m or (bias is not None and bias.shape[0] != n):
+            raise KernelError(f"linear_argmax: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+        need = m * ((n + 127) // 128)
+        if self._lm_scratch is None or self._lm_scratch[0].numel() < need:
+            self._lm_scratch = (torch.empty(need, dtype=torch.float32, device=self.device),
+                                torch.empty(need, dtype=torch.int32, device=self.device))
+        self._check(self.tc.fz_gemm_tc_argmax(_p(a), _p(w), _p(bias), c_int(m), c_int(n), c_int(k), _p(self._lm_scratch[0]),
+                                              _p(self._lm_scratch[1]), _p(out), _p(self.err), self._stream()),
+                    "linear_argmax (tensor cores)")
+        self.launches += 1     # the reduction over the tiles
         return True
 
     def paged_attention(self, q, cache, meta, out, num_heads, num_kv_heads, head_dim, scale, window) -> None:

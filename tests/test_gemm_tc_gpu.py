@@ -167,3 +167,37 @@ def test_qkv_product_with_rotation_and_cache_write(Hq, Hkv, hd, K, bs, M):
     q = torch.empty(200, Hq * hd, dtype=torch.bfloat16, device="cuda")
     big = torch.randn(200, K, generator=g).to(torch.bfloat16).cuda()
     assert ops.linear_rope_kv_write(big, w, b, cos, sin, meta, cache, q, Hq, Hkv, hd) is False
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 20000, 256), (8, 33333, 128), (37, 17000, 64), (128, 16512, 72)])
+def test_product_that_keeps_only_the_largest_of_each_row(M, N, K):
+    """`linear_argmax` gives the ids that `argmax` finds in the logits `linear` writes, with the numpy rule for ties (the
+    lower index) and NaN (a NaN wins), a bias, a ragged last tile; sizes whose K is split are refused."""
+    from fusezap_core_b200.kernels import cuda_ops
+    ops = cuda_ops("bfloat16")
+    g = torch.Generator().manual_seed(M + N)
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    w = torch.randn(N, K, generator=g).to(torch.bfloat16).cuda()
+    w[N - 1] = w[5]                      # equal logits at 5 and N - 1 in every row: the lower index must win where they are the maximum
+    w[N // 2] = w[5]
+    a[0] = 0                             # a row of all-equal logits
+    b = (torch.randn(N, generator=g) * 0.01).cuda()
+    b[N - 1] = b[5]; b[N // 2] = b[5]
+    for bias in (None, b):
+        logits = torch.empty(M, N, device="cuda")
+        ops.linear(a, w, bias, logits)
+        want = torch.empty(M, dtype=torch.int32, device="cuda")
+        ops.argmax(logits, want)
+        got = torch.full((M,), -1, dtype=torch.int32, device="cuda")
+        assert ops.linear_argmax(a, w, bias, got)
+        ops.check_errors()
+        assert torch.equal(got, want), (got.tolist(), want.tolist())
+        assert bias is not None or int(got[0]) == 0
+    if M > 1:
+        a2 = a.clone(); a2[1, 3] = float("nan")            # a NaN activation makes the whole row NaN: index 0
+        got = torch.full((M,), -1, dtype=torch.int32, device="cuda")
+        assert ops.linear_argmax(a2, w, None, got) and int(got[1]) == 0
+    # few tiles and a long K: the product would be split along K; refused, the caller writes logits and uses `argmax`
+    a3 = torch.randn(M, 4096, generator=g).to(torch.bfloat16).cuda()
+    w3 = torch.randn(1024, 4096, generator=g).to(torch.bfloat16).cuda()
+    assert ops.linear_argmax(a3, w3, None, got) is False
