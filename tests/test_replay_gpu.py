@@ -100,3 +100,37 @@ def test_replay_default_pages_bf16_file(tmp_path):
         assert sorted(got["a"]) == list(range(29, 50))
         assert_close(g, ref[0][29:], dtype, f"a {dtype}")
         assert_close(np.stack([got["b"][p] for p in range(19)]), ref[1], dtype, f"b {dtype}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,page", [("tiny_hd128", 64), ("tiny_hd64", 16)])
+def test_replay_beyond_4096_positions(name, page, dtype, tmp_path):
+    """A 4,400-token request: portions of 1,500, then the last 32 tokens one by one, beside a short second request. Past
+    key 4096 the decode kernel cuts the key axis in larger units, the prompt kernel walks 35 key tiles, and pages of 64 are
+    fetched as one TMA box."""
+    model_dir, cfg, opts = make_model_dir(name, tmp_path, "float32")
+    weights = read_weights(model_dir)
+    P = prompts(cfg, (4400, 70), seed=5)
+    ref = [plain_logits(cfg, weights, ids, dtype) for ids in P]
+    tb = TraceBuilder()
+    long_ids, short = P
+    at = 0
+    for n in (1500, 1500, 1368):
+        tb.step([("L", long_ids[at:at + n], [n - 1])])
+        at += n
+    tb.step([("L", long_ids[at:at + 1], [0]), ("S", short[:60], [59])])
+    at += 1
+    k = 60
+    while at < len(long_ids):
+        entries = [("L", long_ids[at:at + 1], [0])]
+        if k < len(short):
+            entries.append(("S", short[k:k + 2], "all")); k += 2
+        tb.step(entries, end=(["S"] if k >= len(short) and len(entries) == 2 else []))
+        at += 1
+    outs = run_trace(model_dir, dtype, str(tmp_path / "out"), max_tokens=4608, steps=tb.steps, page_size=page, timeout=900)
+    got = tb.collect(outs, cfg["vocab_size"])
+    for rid, i in (("L", 0), ("S", 1)):
+        pos = sorted(got[rid])
+        g = np.stack([got[rid][p] for p in pos])
+        assert_close(g, ref[i][pos], dtype, f"{name} {dtype} request {rid}")
+    assert max(got["L"]) == 4399 and len(got["L"]) >= 35
