@@ -598,72 +598,99 @@ attn_decode_units_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_
   }
 }
 
-// One block per (token row, query head), COMBINE_SPLIT x HD threads: thread (s, d) merges, for dimension d, the blocks
-// s, s + COMBINE_SPLIT, ... of the row's key axis (a block: the up to four 64-key units of 256 keys below key 4096,
-// either already merged by the unit kernel or merged here in rising order with the same arithmetic; a 256-key unit
-// above); the COMBINE_SPLIT results are merged in order, normalised and rounded to bf16. Which units a row has follows
+// One block of 128 threads per (token row, query head). A thread owns four neighbouring output dimensions (one float4 per
+// partial result); the HD / 4 threads that cover a row form a group, and the 128 / (HD / 4) groups share the row's blocks
+// of the key axis out among themselves (a block: the up to four 64-key units of 256 keys below key 4096, either already
+// merged by the unit kernel or merged here in rising order with the same arithmetic; a 256-key unit above). The groups'
+// results are merged in group order, normalised and rounded to bf16. All (max, sum) pairs of the row are brought into
+// shared memory first, so that what a thread loads next never waits on a load before it. Which units a row has follows
 // from its position and the window alone, as in the kernel above.
-constexpr int COMBINE_SPLIT = 4;
-__global__ void attn_combine_units_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                          const int* __restrict__ pos, const int* __restrict__ seq_row,
-                                          const int* __restrict__ seg, __nv_bfloat16* __restrict__ out, int Hq, int HD,
-                                          int NPU, int window, int long_from) {
-  __shared__ float s_m[COMBINE_SPLIT], s_l[COMBINE_SPLIT], s_o[COMBINE_SPLIT][128];
+__global__ void __launch_bounds__(128)
+attn_combine_units_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                          const int* __restrict__ pos, const int* __restrict__ seq_row, const int* __restrict__ seg,
+                          __nv_bfloat16* __restrict__ out, int Hq, int HD, int NPU, int window, int long_from) {
+  extern __shared__ float2 s_ml[];             // [units of the row], then the groups' results
   fz_grid_launch_dependents();
-  const int n = blockIdx.y, h = blockIdx.x, d = threadIdx.x % HD, sub = threadIdx.x / HD;
+  const int n = blockIdx.y, h = blockIdx.x, tid = threadIdx.x;
+  const int per_row = HD >> 2, groups = 128 / per_row;          // threads per row, groups per block
+  const int grp = tid / per_row, d4 = (tid - grp * per_row) * 4;
   const int row = seq_row[n];
   const bool skip = row >= 0 && seg[row * 4 + 1] >= long_from;
   const int p = pos[n];
   fz_grid_wait();
   __nv_bfloat16* orow = out + ((size_t)n * Hq + h) * HD;
   if (row < 0) {
-    if (sub == 0) orow[d] = __float2bfloat16_rn(0.f);
+    if (grp == 0) *(uint2*)(orow + d4) = make_uint2(0u, 0u);
     return;
   }
   if (skip) return;
   const int lo = window > 0 ? max(0, p - window + 1) : 0;
-  const int u0 = unit_of(lo), u1 = unit_of(p);
-  const float2* ml = (const float2*)part_ml + ((size_t)n * Hq + h) * NPU;
-  const float* po = part_o + ((size_t)n * Hq + h) * NPU * HD + d;
+  const int u0 = unit_of(lo), u1 = unit_of(p), cnt = u1 - u0 + 1;
+  const float2* ml = (const float2*)part_ml + ((size_t)n * Hq + h) * NPU + u0;
+  const float* po = part_o + (((size_t)n * Hq + h) * NPU + u0) * HD + d4;
+  for (int i = tid; i < cnt; i += 128) s_ml[i] = ml[i];
+  __syncthreads();
+  float4* s_o = (float4*)(s_ml + cnt + (cnt & 1));              // [groups][per_row]
+  float2* s_g = (float2*)(s_o + groups * per_row);              // [groups]: (max, sum)
   const int n_small = u0 < SMALL_UNITS ? (min(u1, SMALL_UNITS - 1) >> 2) - (u0 >> 2) + 1 : 0;
   const int big0 = max(u0, SMALL_UNITS);
   const int n_items = n_small + (u1 >= SMALL_UNITS ? u1 - big0 + 1 : 0);
-  float M = -INFINITY, L = 0.f, O = 0.f;
-  for (int k = sub; k < n_items; k += COMBINE_SPLIT) {
-    float Mb, Lb, Ob;
+  float M = -INFINITY, L = 0.f;
+  float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
+  auto merge4 = [](float4& o, const float4& o2, float fa, float fb) {
+    o.x = merge_unit_value(o.x, o2.x, fa, fb); o.y = merge_unit_value(o.y, o2.y, fa, fb);
+    o.z = merge_unit_value(o.z, o2.z, fa, fb); o.w = merge_unit_value(o.w, o2.w, fa, fb);
+  };
+  for (int k = grp; k < n_items; k += groups) {
+    float Mb, Lb;
+    float4 Ob;
     if (k < n_small) {
       const int b = (u0 >> 2) + k;
-      const int bu0 = max(u0, 4 * b), bu1 = min(u1, 4 * b + 3);
-      const float2 first = ml[bu0];
-      Mb = first.x; Lb = fabsf(first.y); Ob = po[(size_t)bu0 * HD];
-      if (first.y >= 0.f) {           // not merged by the unit kernel: the block's units one by one
-        for (int u = bu0 + 1; u <= bu1; ++u) {
-          const float2 next = ml[u];
-          float fa, fb;
-          merge_unit_scalars(Mb, Lb, next.x, next.y, fa, fb);
-          Ob = merge_unit_value(Ob, po[(size_t)u * HD], fa, fb);
+      const int i0 = max(u0, 4 * b) - u0, i1 = min(u1, 4 * b + 3) - u0;       // the block's units, relative to u0
+      const float2 first = s_ml[i0];
+      Mb = first.x; Lb = fabsf(first.y);
+      if (first.y < 0.f || i1 == i0) {
+        Ob = *(const float4*)(po + (size_t)i0 * HD);
+      } else {                        // not merged by the unit kernel: the block's units one by one, loads first
+        float4 v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (i0 + j <= i1) v[j] = *(const float4*)(po + (size_t)(i0 + j) * HD);
+        Ob = v[0];
+#pragma unroll
+        for (int j = 1; j < 4; ++j) {
+          if (i0 + j <= i1) {
+            const float2 next = s_ml[i0 + j];
+            float fa, fb;
+            merge_unit_scalars(Mb, Lb, next.x, next.y, fa, fb);
+            merge4(Ob, v[j], fa, fb);
+          }
         }
       }
     } else {
-      const int u = big0 + (k - n_small);
-      const float2 v = ml[u];
-      Mb = v.x; Lb = v.y; Ob = po[(size_t)u * HD];
+      const int i = big0 + (k - n_small) - u0;
+      const float2 v = s_ml[i];
+      Mb = v.x; Lb = v.y;
+      Ob = *(const float4*)(po + (size_t)i * HD);
     }
     float fa, fb;
     merge_unit_scalars(M, L, Mb, Lb, fa, fb);
-    O = merge_unit_value(O, Ob, fa, fb);
+    merge4(O, Ob, fa, fb);
   }
-  if (d == 0) { s_m[sub] = M; s_l[sub] = L; }
-  s_o[sub][d] = O;
+  s_o[grp * per_row + (tid - grp * per_row)] = O;
+  if (tid - grp * per_row == 0) s_g[grp] = make_float2(M, L);
   __syncthreads();
-  if (sub != 0) return;
-  for (int k = 1; k < COMBINE_SPLIT; ++k) {
-    if (s_m[k] == -INFINITY) continue;        // that share of the blocks was empty
+  if (grp != 0) return;
+  for (int k = 1; k < groups; ++k) {
+    const float2 g = s_g[k];
+    if (g.x == -INFINITY) continue;        // that group had no block
     float fa, fb;
-    merge_unit_scalars(M, L, s_m[k], s_l[k], fa, fb);
-    O = merge_unit_value(O, s_o[k][d], fa, fb);
+    merge_unit_scalars(M, L, g.x, g.y, fa, fb);
+    merge4(O, s_o[k * per_row + tid], fa, fb);
   }
-  orow[d] = __float2bfloat16_rn(O / L);
+  const float inv = 1.0f / L;
+  const __nv_bfloat162 a = __floats2bfloat162_rn(O.x * inv, O.y * inv), c = __floats2bfloat162_rn(O.z * inv, O.w * inv);
+  *(uint2*)(orow + d4) = make_uint2(*(const uint32_t*)&a, *(const uint32_t*)&c);
 }
 
 // One block per (token row, query head): merges the partitions in rising order, normalises, rounds to bf16.
@@ -729,7 +756,8 @@ int launch_units(const void* q, const void* k_pool, long long pool_rows, const i
             scale * 1.4426950408889634f, window, long_from, err);
   FZ_LAUNCH_CHECK();
   dim3 cgrid(Hq, N);
-  fz_launch(attn_combine_units_kernel, cgrid, dim3(COMBINE_SPLIT * HD), 0, stream, (const float*)part_o,
+  // shared memory: the row's (max, sum) pairs, then 128 float4 and up to 8 float2 of the groups' results
+  fz_launch(attn_combine_units_kernel, cgrid, dim3(128), (size_t)(NPU + 2) * 8 + 128 * 16 + 8 * 8, stream, (const float*)part_o,
             (const float*)part_ml, pos, seq_row, seg, (__nv_bfloat16*)out, Hq, HD, NPU, window, long_from);
   FZ_LAUNCH_CHECK();
   return FZ_OK;
@@ -800,7 +828,7 @@ FZ_API int fz_attn_decode(const void* q, const void* k_pool, const void* v_pool,
                            (const __nv_bfloat16*)v_pool == (const __nv_bfloat16*)k_pool + (long long)Hkv * page_size * hd;
   const bool tma_ok = num_pages > 0 && interleaved && (((uintptr_t)k_pool) & 15) == 0 &&
                       (page_size == 8 || page_size % 16 == 0) && N <= MAX_UNIT_ROWS &&
-                      (long long)N * Hkv * NPU < (1LL << 30) && (size_t)NPU * 4 < 40 * 1024 && !getenv("FZB200_NO_TMA_ATTN");
+                      (long long)N * Hkv * NPU < (1LL << 30) && (size_t)NPU * 8 < 40 * 1024 && !getenv("FZB200_NO_TMA_ATTN");
   if (tma_ok) {
     const long long pool_rows = (long long)num_pages * 2 * Hkv * page_size;
 #define FZ_T(HD_, BOX_) return launch_tma<HD_, BOX_>(q, k_pool, pool_rows, pos, seq_row, seg, table, mb, page_size, out, part_o, part_ml, N, Hq, Hkv, scale, window, NPU, long_from, err, stream)
