@@ -249,23 +249,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           for (int j = 0; j < 16; ++j) v[j] = 0.f;
         }
         if (p.argmax) {
-          // the tile's best (value, feature) per token row: over the warp by shuffles, over the four warps through the
-          // (idle) stage buffers
+          // the tile's logits go to the (idle) stage buffers as [token][feature], rows one float apart from a multiple of
+          // the bank count, and are searched below
           const float bv = (p.bias && a_row < a_limit) ? p.bias[a_row] : 0.f;
-          float* am_v = (float*)smem;                 // [4 warps][BN]
-          int* am_i = (int*)smem + 4 * BN;
+          float* am = (float*)smem;                   // [BN][BM + 1]
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            float x = v[j] + bv;
-            int ix = a_row < a_limit ? a_row : 0x7fffffff;
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-              const float ox = __shfl_xor_sync(0xffffffffu, x, o);
-              const int oi = __shfl_xor_sync(0xffffffffu, ix, o);
-              if (am_better(ox, oi, x, ix)) { x = ox; ix = oi; }
-            }
-            if (lane == 0) { am_v[quad * BN + c + j] = x; am_i[quad * BN + c + j] = ix; }
-          }
+          for (int j = 0; j < 16; ++j) am[(c + j) * (BM + 1) + r] = v[j] + bv;
         } else if (direct) store16(v, c);
         else {
 #pragma unroll
@@ -273,16 +262,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
       }
       if (p.argmax) {
+        // 128 / BN threads share a token: each scans its part of the tile's 128 features in rising order (so the lower
+        // index wins among equals), then the parts are merged in rising order
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        const int m = b0 + r;                        // thread r merges column r of the four warps
-        if (r < BN && m < b_limit) {
-          const float* am_v = (const float*)smem;
-          const int* am_i = (const int*)smem + 4 * BN;
-          float x = am_v[r];
-          int ix = am_i[r];
-#pragma unroll
-          for (int w = 1; w < 4; ++w)
-            if (am_better(am_v[w * BN + r], am_i[w * BN + r], x, ix)) { x = am_v[w * BN + r]; ix = am_i[w * BN + r]; }
+        constexpr int TPC = BM / BN < 1 ? 1 : BM / BN;          // threads per token
+        constexpr int SEG = BM / TPC;                            // features per thread
+        const float* am = (const float*)smem;
+        float* best_v = (float*)smem + BN * (BM + 1);            // [BN][TPC]
+        int* best_i = (int*)(best_v + BN * TPC);
+        const int col = r % BN, seg = r / BN;                    // (for BN = 128 every thread has a token of its own)
+        float x = 0.f;
+        int ix = 0x7fffffff;
+        if (seg < TPC) {
+          for (int i = 0; i < SEG; ++i) {
+            const int f = seg * SEG + i, feat = tile_a * BM + f;
+            if (feat < a_limit && am_better(am[col * (BM + 1) + f], feat, x, ix)) { x = am[col * (BM + 1) + f]; ix = feat; }
+          }
+          best_v[col * TPC + seg] = x;
+          best_i[col * TPC + seg] = ix;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const int m = b0 + col;
+        if (seg == 0 && m < b_limit) {
+          for (int sgm = 1; sgm < TPC; ++sgm)
+            if (am_better(best_v[col * TPC + sgm], best_i[col * TPC + sgm], x, ix)) { x = best_v[col * TPC + sgm]; ix = best_i[col * TPC + sgm]; }
           p.am_val[(size_t)m * gridDim.x + tile_a] = x;
           p.am_idx[(size_t)m * gridDim.x + tile_a] = ix;
         }
