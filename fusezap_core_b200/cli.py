@@ -48,7 +48,10 @@ def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="fusezap_core_b200", description="B200-native engine for the dense Llama / Qwen2.5 decoder")
     sub = ap.add_subparsers(dest="cmd", required=True)
     g = sub.add_parser("generate", help="generate tokens for prompts given as token ids")
-    g.add_argument("model", help="model folder (config.json + safetensors)")
+    g.add_argument("model", nargs="?", default=None, help="model folder (config.json + safetensors)")
+    g.add_argument("--random", default=None, metavar="PRESET",
+                   help=f"instead of a model folder: the sizes of a preset ({', '.join(presets())}) with random weights")
+    g.add_argument("--random-seed", type=int, default=0, help="seed of the random weights")
     add_engine_options(g)
     g.add_argument("--prompt-ids", action="append", default=[], help="comma-separated token ids; repeat for more prompts")
     g.add_argument("--prompt-file", default=None, help="JSON lines, each a list of token ids")
@@ -83,8 +86,15 @@ def resolve_dtype(name: str) -> str:
 
 def build_engine(a: argparse.Namespace):
     from .engine.llm_engine import LLMEngine
-    from .engine.model import load_model
-    model = load_model(a.model, resolve_dtype(a.dtype), a.device, max_len=a.max_model_len)
+    from .engine.model import load_model, random_model
+    if (a.model is None) == (a.random is None):
+        raise SystemExit("give a model folder or --random PRESET (one of them)")
+    if a.random is not None:
+        model = random_model(load_preset(a.random), resolve_dtype(a.dtype), a.device, seed=a.random_seed,
+                             max_len=a.max_model_len)
+        a.model = f"random {a.random} (seed {a.random_seed})"
+    else:
+        model = load_model(a.model, resolve_dtype(a.dtype), a.device, max_len=a.max_model_len)
     return LLMEngine(model, num_blocks=a.num_blocks, block_size=a.block_size, max_num_seqs=a.max_num_seqs,
                      max_prefill_tokens=a.max_prefill_tokens, max_model_len=a.max_model_len,
                      cuda_graphs=not a.no_cuda_graphs, lookahead=not a.no_lookahead)

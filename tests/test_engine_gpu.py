@@ -136,6 +136,19 @@ def test_command_line(folders, tmp_path):
     p = subprocess.run([sys.executable, "-m", "fusezap_core_b200", "random-weights", "--preset", "tiny-qwen2", "--out", out,
                         "--seed", "3", "--dtype", "bfloat16"], capture_output=True, text=True, cwd=ROOT, timeout=120)
     assert p.returncode == 0 and os.path.isfile(os.path.join(out, "model.safetensors")) and os.path.isfile(os.path.join(out, "config.json"))
+    # a preset with random weights instead of a folder; the same seed gives the same tokens, and the replay subcommand runs
+    runs = []
+    for _ in range(2):
+        p = subprocess.run([sys.executable, "-m", "fusezap_core_b200", "generate", "--random", "tiny-qwen2", "--random-seed", "5",
+                            "--prompt-ids", "1,2,3", "--max-tokens", "4", "--ignore-eos", "--max-model-len", "64",
+                            "--num-blocks", "16", "--max-num-seqs", "2"], capture_output=True, text=True, cwd=ROOT, timeout=300)
+        assert p.returncode == 0, p.stderr[-2000:]
+        runs.append([json.loads(l)["token_ids"] for l in p.stdout.splitlines() if l.startswith("{")])
+    assert runs[0] == runs[1] and len(runs[0][0]) == 4
+    p = subprocess.run([sys.executable, "-m", "fusezap_core_b200", "replay", "--model", out, "--dtype", "bfloat16", "--out",
+                        str(tmp_path / "lg"), "--max-tokens", "64"], input='{"step": 0, "entries": [{"id": "a", "tokens": [5, 6, 7], "want": [2]}], "end": ["a"]}\n',
+                       capture_output=True, text=True, cwd=ROOT, timeout=300)
+    assert p.returncode == 0 and "done 0" in p.stdout and os.path.getsize(str(tmp_path / "lg" / "0.f32")) == 4 * 384, p.stderr[-2000:]
 
 
 def test_no_gpu_tensor_no_run(folders):
