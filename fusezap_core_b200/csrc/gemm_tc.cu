@@ -638,7 +638,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, dim3 g
 int pick_stages(int bn) {
   const int stage = (BM + bn) * BK * 2;
   int s = (200 * 1024) / stage;
-  if (bn <= 64) s = (100 * 1024) / stage;   // leaves room for two CTAs per SM when the tile is small
+  if (bn <= 128) s = (100 * 1024) / stage;  // few-token mode: leaves room for two CTAs per SM
   return s < 2 ? 2 : (s > 8 ? 8 : s);
 }
 }  // namespace
