@@ -45,7 +45,11 @@ def test_few_rows(M, N, K):
 
 
 @pytest.mark.parametrize("M,N,K", [(129, 256, 128), (300, 777, 200), (2048, 1024, 512), (257, 64, 4096), (1000, 136, 72),
-                                   (384, 96, 96)])
+                                   (384, 96, 96),
+                                   # fewer tiles than SMs, or a partial last round, with a long K
+                                   (256, 4096, 4096), (512, 6144, 4096), (200, 1000, 8192), (2048, 4096, 4096), (640, 4096, 1024),
+                                   # many rounds and a short K
+                                   (150, 151936, 896)])
 def test_many_rows(M, N, K):
     for out_dtype, bias in ((torch.float32, True), (torch.bfloat16, False)):
         out, ref = run(M, N, K, out_dtype, bias)
