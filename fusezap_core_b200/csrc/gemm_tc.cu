@@ -21,6 +21,9 @@
 // stores the result. The sum has one fixed order (as the reference's split-K has: wgmma.py:209-239) and no partial ever
 // goes to global memory. Waits on this CTA's own mbarriers are bounded by a time limit after which the kernel sets an
 // error bit and leaves; the cluster barriers are hardware barriers, not spins.
+// Epilogues besides bias + store: SwiGLU over weight rows packed as [64 gate | 64 up] blocks (both modes); for few
+// tokens the rotation of the q and k heads with the write of k and v into the paged cache, and a per-tile argmax that
+// stores no products at all (the lm_head of a greedy step).
 #include "umma.cuh"
 
 namespace {
