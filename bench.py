@@ -218,7 +218,7 @@ def main() -> int:
         eng = make_engine(1)
         ids = rng.integers(0, V, tokens).tolist()
         times = []
-        for i in range(4):
+        for i in range(7):      # one warm-up, then the best of six (the clock under the power cap wanders between runs)
             rid = eng.add_request(ids, SamplingParams(max_tokens=1, ignore_eos=True))
             torch.cuda.synchronize()
             start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

@@ -226,6 +226,16 @@ class StepRunner:
         out, it does, `ids_out` receives the token ids and None is returned; otherwise logits as usual."""
         model, ctx, meta = self.model, self.ctx, self.meta
         spec = model.spec
+        begin, end = getattr(self.ops, "begin_step", None), getattr(self.ops, "end_step", None)
+        if begin is not None:
+            begin()
+        try:
+            return self._forward(model, ctx, meta, spec, ids_out)
+        finally:
+            if end is not None:
+                end()
+
+    def _forward(self, model, ctx, meta, spec, ids_out):
         x = self.ws.get("x", (meta.n_rows, spec.hidden_size), torch.float32)
         self.ops.embed(model.embed, meta.tokens, x, meta.src if self.prev_ids is not None else None, self.prev_ids)
         delta = None

@@ -45,6 +45,7 @@ class CudaOps(Ops):
         self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._err_host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
         self.launches = 0
+        self._stream_handle = None
         self._argmax_scratch = None
         self.tc = None
         if self.dtype == torch.bfloat16:
@@ -58,7 +59,17 @@ class CudaOps(Ops):
         self._attn_scratch: torch.Tensor | None = None      # float32 partial outputs of the split decode attention
 
     # ---- plumbing
+    def begin_step(self) -> None:
+        """Called by the step function before it launches anything: the kernels of the step all go to the stream that
+        is current now (asked for once; it changes when a graph is captured or a caller switches streams)."""
+        self._stream_handle = c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def end_step(self) -> None:
+        self._stream_handle = None
+
     def _stream(self) -> c_void_p:
+        if self._stream_handle is not None:
+            return self._stream_handle
         return c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
 
     def _check(self, status: int, what: str) -> None:
