@@ -407,7 +407,7 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-  constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;      // two accumulators
+  constexpr int TMEM_COLS = 2 * BN <= 32 ? 32 : 2 * BN <= 64 ? 64 : 2 * BN <= 128 ? 128 : 2 * BN <= 256 ? 256 : 512;   // two accumulators (a power of two)
   uint64_t* full = (uint64_t*)(smem + (size_t)p.stages * STAGE_BYTES);
   uint64_t* empty = full + p.stages;
   uint64_t* acc_full = empty + p.stages;     // [2]
@@ -802,13 +802,39 @@ static int gemm_tc_impl(const void* x, const void* w, const float* bias, void* c
   }
   // rows mode: token rows are the 128 lanes; persistent CTAs with two accumulators
   p.swap = 0;
-  const int bn = N >= 256 ? 256 : N >= 128 ? 128 : 64;     // with the fused SwiGLU N = 2 I >= 128, so a tile holds whole blocks
-  p.stages = pick_stages(bn);
+  int bn = N >= 256 ? 256 : N >= 128 ? 128 : 64;     // with the fused SwiGLU N = 2 I >= 128, so a tile holds whole blocks
+  if (bn == 256 && !p.swiglu) {
+    // Few token rows: when the 256-wide tiles do not fill the SMs even once, the narrowest width that still fits one
+    // round is the fastest (256 x 4096 x 4096 is 32 tiles of 256 columns for 148 SMs, but 52 of 160). Not below 160:
+    // a 128-wide instruction reads its operands from shared memory at the rate the tensor core consumes them and runs
+    // at about half speed. With more than one round the widest tile stays: measured at 2,048 rows, 160-wide tiles in
+    // three rounds (60 -> 72 us) lose against 256-wide ones in two, whatever the count of rounds says.
+    static int sms = 0;
+    if (sms == 0) {
+      int dev = 0;
+      cudaGetDevice(&dev);
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+      if (sms <= 0) sms = 148;
+    }
+    const long long tm = (M + BM - 1) / BM;
+    if (tm * ((N + 255) / 256) < sms) {
+      for (int cand : {224, 192, 160})
+        if (tm * ((N + cand - 1) / cand) <= sms) bn = cand;
+    }
+  }
+  {
+    const int stage = (BM + bn) * BK * 2;
+    const int st_n = (200 * 1024) / stage;
+    p.stages = st_n < 2 ? 2 : (st_n > 8 ? 8 : st_n);
+  }
   if ((st = get_map_bf16(x, M, K, BM, &ma)) != FZ_OK) return st;
   if ((st = get_map_bf16(w, N, K, bn, &mb)) != FZ_OK) return st;
   const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + bn - 1) / bn;
   switch (bn) {
     case 256: return launch_rows<256>(ma, mb, p, tiles_m, tiles_n, stream);
+    case 224: return launch_rows<224>(ma, mb, p, tiles_m, tiles_n, stream);
+    case 192: return launch_rows<192>(ma, mb, p, tiles_m, tiles_n, stream);
+    case 160: return launch_rows<160>(ma, mb, p, tiles_m, tiles_n, stream);
     case 128: return launch_rows<128>(ma, mb, p, tiles_m, tiles_n, stream);
     default: return launch_rows<64>(ma, mb, p, tiles_m, tiles_n, stream);
   }

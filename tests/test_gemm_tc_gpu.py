@@ -48,6 +48,7 @@ def test_few_rows(M, N, K):
                                    (384, 96, 96),
                                    # fewer tiles than SMs, or a partial last round, with a long K
                                    (256, 4096, 4096), (512, 6144, 4096), (200, 1000, 8192), (2048, 4096, 4096), (640, 4096, 1024),
+                                   (512, 8192, 512),      # tiles 160, 192, 160, 256, 160 and 224 columns wide
                                    # many rounds and a short K
                                    (150, 151936, 896)])
 def test_many_rows(M, N, K):
