@@ -209,3 +209,47 @@ def test_engine_in_one_call(tmp_path):
     rnd = LLMEngine.from_random("tiny-llama", seed=1, dtype="float32", device="cpu", max_model_len=64, ops=PlainOps(),
                                 num_blocks=16, block_size=8, max_num_seqs=2)
     assert len(rnd.generate([[1, 2, 3]], SamplingParams(max_tokens=3, ignore_eos=True))[0]) == 3
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2, 3])
+def test_launching_ahead_under_random_traffic(models, seed):
+    """Random arrivals, lengths, limits, stop tokens, sampled and greedy requests, aborts and few pages (so that requests
+    lose theirs): with and without launching decode steps ahead, every request gets the same tokens and the same end,
+    and the cache manager's books are right after every step."""
+    model, cfg, opts, w = models["tiny_qwen2"]
+    rng = np.random.default_rng(seed)
+    n_req = 9
+    lens = rng.integers(1, 40, n_req)
+    P = prompts(cfg, tuple(int(x) for x in lens), seed=100 + seed)
+    arrive = np.sort(rng.integers(0, 25, n_req))
+    params = []
+    for i in range(n_req):
+        kind = rng.integers(0, 3)
+        params.append(SamplingParams(max_tokens=int(rng.integers(1, 30)), ignore_eos=True,
+                                     temperature=0.8 if kind == 1 else 0.0, seed=int(rng.integers(0, 1000)),
+                                     top_k=5 if kind == 2 and rng.random() < 0.5 else 0,
+                                     stop_token_ids=[int(t) for t in rng.integers(0, cfg["vocab_size"], 12)]))
+    abort_at = {int(rng.integers(5, 40)): int(rng.integers(0, n_req))}
+    res = {}
+    for ahead in (False, True):
+        eng = LLMEngine(model, num_blocks=14, block_size=8, max_num_seqs=4, max_prefill_tokens=16, max_model_len=96,
+                        lookahead=ahead)
+        rec, rids, step, nxt = {}, {}, 0, 0
+        while nxt < n_req or eng.has_unfinished():
+            while nxt < n_req and arrive[nxt] <= step:
+                rids[nxt] = eng.add_request(P[nxt], params[nxt]); rec[rids[nxt]] = []; nxt += 1
+            for o in eng.step():
+                rec[o.request_id].append((tuple(o.new_token_ids), o.finished, o.finish_reason))
+            eng.cache.check()
+            step += 1
+            if step in abort_at and abort_at[step] in rids:
+                o = eng.abort(rids[abort_at[step]])
+                if o is not None:
+                    rec[o.request_id].append(((), True, "abort"))
+            assert step < 2000
+        assert eng.cache.num_free_pages == 14
+        res[ahead] = (rec, eng.stats["lookahead_steps"], eng.stats["preemptions"])
+    assert res[False][0] == res[True][0]
+    assert res[True][1] > 0 and res[False][1] == 0
+    if seed == 0:
+        assert res[True][2] > 0 and res[False][2] > 0, "this seed is meant to run out of pages"
