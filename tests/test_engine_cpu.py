@@ -9,7 +9,7 @@ from fusezap_core_b200 import LLMEngine, SamplingParams, load_model
 from fusezap_core_b200.cache import CacheManager, OutOfPages
 from fusezap_core_b200.engine import Portion, StepRunner
 from plain_ops import PlainOps
-from util import lookahead_scenario, make_model_dir, prompts, read_weights
+from util import lookahead_scenario, make_model_dir, prompts, random_traffic, read_weights
 
 
 @pytest.fixture(scope="module")
@@ -217,38 +217,7 @@ def test_launching_ahead_under_random_traffic(models, seed):
     lose theirs): with and without launching decode steps ahead, every request gets the same tokens and the same end,
     and the cache manager's books are right after every step."""
     model, cfg, opts, w = models["tiny_qwen2"]
-    rng = np.random.default_rng(seed)
-    n_req = 9
-    lens = rng.integers(1, 40, n_req)
-    P = prompts(cfg, tuple(int(x) for x in lens), seed=100 + seed)
-    arrive = np.sort(rng.integers(0, 25, n_req))
-    params = []
-    for i in range(n_req):
-        kind = rng.integers(0, 3)
-        params.append(SamplingParams(max_tokens=int(rng.integers(1, 30)), ignore_eos=True,
-                                     temperature=0.8 if kind == 1 else 0.0, seed=int(rng.integers(0, 1000)),
-                                     top_k=5 if kind == 2 and rng.random() < 0.5 else 0,
-                                     stop_token_ids=[int(t) for t in rng.integers(0, cfg["vocab_size"], 12)]))
-    abort_at = {int(rng.integers(5, 40)): int(rng.integers(0, n_req))}
-    res = {}
-    for ahead in (False, True):
-        eng = LLMEngine(model, num_blocks=14, block_size=8, max_num_seqs=4, max_prefill_tokens=16, max_model_len=96,
-                        lookahead=ahead)
-        rec, rids, step, nxt = {}, {}, 0, 0
-        while nxt < n_req or eng.has_unfinished():
-            while nxt < n_req and arrive[nxt] <= step:
-                rids[nxt] = eng.add_request(P[nxt], params[nxt]); rec[rids[nxt]] = []; nxt += 1
-            for o in eng.step():
-                rec[o.request_id].append((tuple(o.new_token_ids), o.finished, o.finish_reason))
-            eng.cache.check()
-            step += 1
-            if step in abort_at and abort_at[step] in rids:
-                o = eng.abort(rids[abort_at[step]])
-                if o is not None:
-                    rec[o.request_id].append(((), True, "abort"))
-            assert step < 2000
-        assert eng.cache.num_free_pages == 14
-        res[ahead] = (rec, eng.stats["lookahead_steps"], eng.stats["preemptions"])
+    res = random_traffic(model, cfg, seed)
     assert res[False][0] == res[True][0]
     assert res[True][1] > 0 and res[False][1] == 0
     if seed == 0:

@@ -10,7 +10,7 @@ import pytest
 import torch
 
 import plain_model
-from util import ROOT, lookahead_scenario, make_model_dir, plain_logits, prompts, read_weights
+from util import ROOT, lookahead_scenario, make_model_dir, plain_logits, prompts, random_traffic, read_weights
 
 pytestmark = pytest.mark.gpu
 
@@ -95,6 +95,18 @@ def test_launching_ahead_changes_no_token(folders, dtype, graphs):
     if stop is not None:
         assert a[3][-1][1:] == (True, "stop")
     assert a[1][-1] == ((), True, "abort") and a[0][-1][1:] == (True, "length") and len(a[2]) == 17
+
+
+@pytest.mark.parametrize("seed,graphs", [(0, True), (5, True), (6, False)])
+def test_launching_ahead_under_random_traffic(folders, seed, graphs):
+    """The random story of `util.random_traffic` on the GPU in float32 (a row's bits do not depend on the batch, so the
+    tokens must be equal): tokens fed on the device, captured steps, requests that lose their pages."""
+    from fusezap_core_b200 import load_model
+    d, cfg, opts = folders["tiny_qwen2"]
+    model = load_model(d, "float32", "cuda:0", max_len=128)
+    res = random_traffic(model, cfg, seed, graphs)
+    assert res[False][0] == res[True][0]
+    assert res[True][1] > 0 and res[False][1] == 0
 
 
 def test_seeded_sampling_on_the_device(folders):

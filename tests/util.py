@@ -162,3 +162,43 @@ def lookahead_scenario(model, page_size, cfg, graphs=True, stop_from=None):
         eng.cache.check()
         res[ahead] = (rec, eng)
     return res[False][0], res[True][0], res[True][1]
+
+
+def random_traffic(model, cfg, seed, graphs=True):
+    """Runs one random story of requests (arrivals, lengths, limits, stop tokens, sampled and greedy ones, an abort, few
+    pages) with and without launching decode steps ahead. Returns {ahead: (records per request, steps launched ahead,
+    preemptions)}; the cache manager's books are checked after every step."""
+    from fusezap_core_b200 import LLMEngine, SamplingParams
+    rng = np.random.default_rng(seed)
+    n_req = 9
+    lens = rng.integers(1, 40, n_req)
+    P = prompts(cfg, tuple(int(x) for x in lens), seed=100 + seed)
+    arrive = np.sort(rng.integers(0, 25, n_req))
+    params = []
+    for i in range(n_req):
+        kind = rng.integers(0, 3)
+        params.append(SamplingParams(max_tokens=int(rng.integers(1, 30)), ignore_eos=True,
+                                     temperature=0.8 if kind == 1 else 0.0, seed=int(rng.integers(0, 1000)),
+                                     top_k=5 if kind == 2 and rng.random() < 0.5 else 0,
+                                     stop_token_ids=[int(t) for t in rng.integers(0, cfg["vocab_size"], 12)]))
+    abort_at = {int(rng.integers(5, 40)): int(rng.integers(0, n_req))}
+    res = {}
+    for ahead in (False, True):
+        eng = LLMEngine(model, num_blocks=14, block_size=8, max_num_seqs=4, max_prefill_tokens=16, max_model_len=96,
+                        lookahead=ahead, cuda_graphs=graphs)
+        rec, rids, step, nxt = {}, {}, 0, 0
+        while nxt < n_req or eng.has_unfinished():
+            while nxt < n_req and arrive[nxt] <= step:
+                rids[nxt] = eng.add_request(P[nxt], params[nxt]); rec[rids[nxt]] = []; nxt += 1
+            for o in eng.step():
+                rec[o.request_id].append((tuple(o.new_token_ids), o.finished, o.finish_reason))
+            eng.cache.check()
+            step += 1
+            if step in abort_at and abort_at[step] in rids:
+                o = eng.abort(rids[abort_at[step]])
+                if o is not None:
+                    rec[o.request_id].append(((), True, "abort"))
+            assert step < 2000
+        assert eng.cache.num_free_pages == 14
+        res[ahead] = (rec, eng.stats["lookahead_steps"], eng.stats["preemptions"])
+    return res
