@@ -134,3 +134,16 @@ def test_a_row_alone_and_among_hundreds(Hq, Hkv, hd):
     cu.paged_attention(q[:3].contiguous(), cc, Meta(pos[:3], seq[:3], table, "cuda"), few, Hq, Hkv, hd, hd ** -0.5, 0)
     assert torch.equal(few, many[:3])
     cu.check_errors()
+
+
+@pytest.mark.parametrize("Hq,Hkv,hd,bs", [(8, 2, 128, 16), (14, 2, 64, 8)])
+def test_decode_rows_without_tma(Hq, Hkv, hd, bs, monkeypatch):
+    """The cp.async variant of the decode kernel (the one page sizes without a TMA box get) on sizes the TMA variant
+    normally takes: FZB200_NO_TMA_ATTN selects it."""
+    monkeypatch.setenv("FZB200_NO_TMA_ATTN", "1")
+    lengths = [1100, 257, 1, 640]
+    rows = [(0, 1099, 1), (1, 255, 2), (2, 0, 1), (3, 511, 1), (3, 512, 1), (0, 62, 3), (3, 633, 7)]
+    o, op, _ = run_both(Hq, Hkv, hd, bs, 0, lengths, rows)
+    close(o, op, "decode without TMA")
+    o, op, _ = run_both(Hq, Hkv, hd, bs, 300, lengths, rows)
+    close(o, op, "decode without TMA, window")
