@@ -109,6 +109,23 @@ class DecoderModel:
             p.prepare(max_len, self.device)
         return self
 
+    def generate(self, prompt_ids: list[int], max_tokens: int = 16, params: Any = None, stop_token_ids: list[int] | None = None,
+                 block_size: int = 16) -> list[int]:
+        """One prompt in, its new tokens out: the batch-1 convenience of the reference's model class
+        (fusezap/serve/models/llama.py:916-929). Builds a one-request engine with just enough pages; `params` (a
+        SamplingParams) overrides max_tokens / stop_token_ids; greedy by default."""
+        from ..sampling import SamplingParams
+        from .llm_engine import LLMEngine
+        if params is None:
+            params = SamplingParams(max_tokens=max_tokens, stop_token_ids=list(stop_token_ids or []))
+        need = len(prompt_ids) + params.max_tokens
+        if need > self.max_len:
+            raise ValueError(f"prompt ({len(prompt_ids)}) + max_tokens ({params.max_tokens}) exceeds the length the model "
+                             f"was loaded for ({self.max_len})")
+        eng = LLMEngine(self, num_blocks=-(-need // block_size) + 1, block_size=block_size, max_num_seqs=1,
+                        max_prefill_tokens=min(2048, self.max_len), max_model_len=self.max_len)
+        return eng.generate([prompt_ids], params)[0]
+
     def weight_bytes(self) -> int:
         """Bytes of every distinct tensor a step reads once (the decode roofline's weight term)."""
         seen: dict[int, int] = {}

@@ -206,6 +206,7 @@ def test_engine_in_one_call(tmp_path):
                                     max_num_seqs=2)
     P = prompts(cfg, (5,), seed=3)
     assert eng.generate(P, SamplingParams(max_tokens=4, ignore_eos=True)) == [greedy_reference(cfg, w, P[0], 4)]
+    assert eng.model.generate(P[0], params=SamplingParams(max_tokens=4, ignore_eos=True)) == greedy_reference(cfg, w, P[0], 4)
     rnd = LLMEngine.from_random("tiny-llama", seed=1, dtype="float32", device="cpu", max_model_len=64, ops=PlainOps(),
                                 num_blocks=16, block_size=8, max_num_seqs=2)
     assert len(rnd.generate([[1, 2, 3]], SamplingParams(max_tokens=3, ignore_eos=True))[0]) == 3
