@@ -38,7 +38,18 @@ def read_config_json(model_dir: str) -> dict:
     if not os.path.isfile(path):
         raise FileNotFoundError(f"{model_dir!r} has no config.json")
     with open(path) as f:
-        return json.load(f)
+        config = json.load(f)
+    # chat models stop on more ids than config.json lists: the ids of generation_config.json are merged in, as the
+    # reference does (fusezap/serve/models/llama.py:443-451)
+    gen = os.path.join(model_dir, "generation_config.json")
+    if os.path.isfile(gen):
+        with open(gen) as f:
+            more = json.load(f).get("eos_token_id")
+        have = config.get("eos_token_id")
+        ids = {*([have] if isinstance(have, int) else (have or [])), *([more] if isinstance(more, int) else (more or []))}
+        if ids:
+            config["eos_token_id"] = sorted(int(i) for i in ids)
+    return config
 
 
 def describe(config: dict) -> tuple[Any, ModelSpec]:

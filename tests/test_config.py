@@ -105,3 +105,19 @@ def test_engine_config():
     for bad in (dict(dtype="float16"), dict(block_size=0), dict(num_blocks=-1), dict(prefill_first=-1)):
         with pytest.raises(ValueError):
             EngineConfig(**bad)
+
+
+def test_generation_config_adds_stop_ids(tmp_path):
+    """The end-of-sequence ids of generation_config.json are merged with config.json's (fusezap/serve/models/llama.py:443-451)."""
+    import json
+    from fusezap_core_b200.config import describe, read_config_json
+    from tiny_configs import TINY_QWEN2
+    cfg = dict(TINY_QWEN2, eos_token_id=7)
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    assert describe(read_config_json(str(tmp_path)))[1].eos_token_ids == (7,)
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": [9, 7, 3]}))
+    assert describe(read_config_json(str(tmp_path)))[1].eos_token_ids == (3, 7, 9)
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": 11}))
+    assert describe(read_config_json(str(tmp_path)))[1].eos_token_ids == (7, 11)
+    (tmp_path / "generation_config.json").write_text(json.dumps({"temperature": 0.7}))
+    assert describe(read_config_json(str(tmp_path)))[1].eos_token_ids == (7,)
