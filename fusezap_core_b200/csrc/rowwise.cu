@@ -589,6 +589,281 @@ FZ_API int fz_sample(const float* logits, const float* temperature, const double
   return FZ_OK;
 }
 
+// ------------------------------------------------------------------------------------------------ top-k / top-p sampling
+// The reference's host sampler on the device (fusezap/serve/sampling.py:25-45, 61-73): logits / T in float64; top-k keeps
+// everything not below the k-th largest value (ties stay); top-p keeps, in falling order of value (ties by rising
+// index), every token before which less than p of the probability lies; then one draw from the softmax of what is left:
+// the first index whose running sum in index order exceeds u times the total. One block of 1024 threads per row.
+// Nothing is sorted: the thresholds are found by radix selection over an order-preserving 32-bit key of the logit,
+// eight passes of 4 bits, with a histogram of counts for top-k and of probability mass (float64) for top-p. Each thread
+// fills 16 bins of its own in shared memory and the bins are then summed over the threads in a fixed order, so there
+// are no atomics and the result is the same from run to run. exp(x / T - max) of every token is computed once, in
+// float64, into `scratch` (V doubles per row); dropped tokens are zeroed there.
+constexpr int SF_THREADS = 1024;
+constexpr int SF_BINS = 16;
+constexpr size_t SF_SMEM = (size_t)SF_BINS * SF_THREADS * sizeof(double);
+
+__device__ __forceinline__ uint32_t falling_key(float x) {      // smaller key = larger value; -0 counts as +0
+  const uint32_t u = __float_as_uint(x + 0.f);
+  return ~((u & 0x80000000u) ? ~u : (u | 0x80000000u));
+}
+
+// Sum of v over the block in a fixed order; every thread gets it. s_part: 32 doubles.
+__device__ __forceinline__ double block_sum_fixed(double v, double* s_part) {
+  for (int o = 16; o; o >>= 1) v += __shfl_down_sync(0xffffffffu, v, o);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = v;
+  __syncthreads();
+  double run = 0.0;
+  for (int w = 0; w < SF_THREADS / 32; ++w) run += s_part[w];
+  return run;
+}
+
+// bins[b * SF_THREADS + t]: thread t's share of bin b. Leaves the sums over the threads in total[0..15].
+template <typename T>
+__device__ __forceinline__ void sum_bins(const T* bins, T* s_part, T* total) {
+  __syncthreads();
+  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31, b = w & (SF_BINS - 1), half = w >> 4;
+  T acc = 0;
+  for (int j = 0; j < SF_THREADS / 64; ++j) acc += bins[b * SF_THREADS + half * (SF_THREADS / 2) + j * 32 + lane];
+  for (int o = 16; o; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
+  if (lane == 0) s_part[w] = acc;
+  __syncthreads();
+  if (threadIdx.x < SF_BINS) total[threadIdx.x] = s_part[threadIdx.x] + s_part[threadIdx.x + SF_BINS];
+  __syncthreads();
+}
+
+// f(i, key of row[i]) for every i this thread owns (i = tid, tid + 1024, ...), eight loads in flight at a time.
+template <typename F>
+__device__ __forceinline__ void for_each_key(const float* __restrict__ row, int V, F f) {
+  constexpr int U = 8;
+  for (int base = threadIdx.x; base < V; base += SF_THREADS * U) {
+    float x[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int i = base + u * SF_THREADS;
+      x[u] = i < V ? row[i] : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int i = base + u * SF_THREADS;
+      if (i < V) f(i, x[u], falling_key(x[u]));
+    }
+  }
+}
+
+// Inclusive sum over the lanes below and this one, always in the same order.
+__device__ __forceinline__ double warp_scan_fixed(double v, int lane) {
+  for (int o = 1; o < 32; o <<= 1) {
+    const double up = __shfl_up_sync(0xffffffffu, v, o);
+    if (lane >= o) v += up;
+  }
+  return v;
+}
+
+__global__ void __launch_bounds__(SF_THREADS, 1)
+sample_filtered_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
+                       const int* __restrict__ top_k, const float* __restrict__ top_p,
+                       const double* __restrict__ uniform, double* __restrict__ scratch, int* __restrict__ out, int V) {
+  fz_grid_launch_dependents();
+  fz_grid_wait();
+  extern __shared__ __align__(16) unsigned char sf_smem[];
+  double* bins_d = reinterpret_cast<double*>(sf_smem);
+  unsigned int* bins_u = reinterpret_cast<unsigned int*>(sf_smem);
+  __shared__ float s_val[32];
+  __shared__ int s_idx[32];
+  __shared__ double s_part[32], s_mass[SF_BINS], s_wsum[32];
+  __shared__ unsigned int s_partu[32], s_count[SF_BINS];
+  __shared__ int s_wties[32];
+  __shared__ uint32_t s_prefix;
+  __shared__ unsigned int s_rank;
+  __shared__ double s_need, s_target;
+  __shared__ int s_res, s_warp;
+  const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const float* row = logits + (size_t)r * V;
+  double* e = scratch + (size_t)r * V;
+  const float T = temperature[r];
+  const int k = top_k[r];
+  const int amax = block_argmax(row, V, s_val, s_idx);
+  if (!(T > 0.f) || k == 1) {
+    if (tid == 0) out[r] = amax;
+    return;
+  }
+  const double mx = (double)row[amax] / (double)T;
+  const uint32_t top_key = falling_key(row[amax]);
+  // ---- top-k: the key of the k-th largest logit (x / T rises with x, so the selection runs on the logits themselves)
+  uint32_t k_key = 0xffffffffu;                 // tokens with a key <= k_key stay
+  if (k > 0 && k < V) {
+    if (tid == 0) { s_prefix = 0u; s_rank = (unsigned int)(k - 1); }
+    for (int pass = 0; pass < 8; ++pass) {
+      const int shift = 28 - 4 * pass;
+      __syncthreads();
+      const uint32_t prefix = s_prefix;
+      for (int b = 0; b < SF_BINS; ++b) bins_u[b * SF_THREADS + tid] = 0u;
+      for_each_key(row, V, [&](int, float, uint32_t key) {
+        if (pass == 0 || (key >> (shift + 4)) == prefix) bins_u[((key >> shift) & 15u) * SF_THREADS + tid] += 1u;
+      });
+      sum_bins(bins_u, s_partu, s_count);
+      if (tid == 0) {
+        unsigned int rank = s_rank, cum = 0;
+        int b = 0;
+        for (; b < SF_BINS - 1; ++b) {
+          if (cum + s_count[b] > rank) break;
+          cum += s_count[b];
+        }
+        s_prefix = (prefix << 4) | (uint32_t)b;
+        s_rank = rank - cum;
+      }
+    }
+    __syncthreads();
+    k_key = s_prefix;
+  }
+  // ---- top-p: the key of the last value of which something stays, and the mass that is still missing where it begins.
+  // All keys that stay lie between top_key and k_key: the digits these two share are not searched. The first pass that
+  // is searched also computes exp(x / T - max) of what top-k keeps, and the sum.
+  const float pp = top_p[r];
+  const bool nucleus = pp < 1.0f;
+  const int first = nucleus ? __clz((int)(top_key ^ k_key)) / 4 : 8;       // 8: all digits shared, or no top-p
+  uint32_t t_key = nucleus ? top_key : 0xffffffffu;                         // (first == 8: one value stays)
+  double need_at_t = 0.0, total = 0.0;
+  if (first == 8) {
+    double local = 0.0;
+    for_each_key(row, V, [&](int i, float x, uint32_t key) {
+      const double v = key <= k_key ? exp((double)x / (double)T - mx) : 0.0;
+      e[i] = v;
+      local += v;
+    });
+    total = block_sum_fixed(local, s_part);
+    need_at_t = (double)pp * total;
+  } else {
+    if (tid == 0) s_prefix = first == 0 ? 0u : top_key >> (32 - 4 * first);
+    for (int pass = first; pass < 8; ++pass) {
+      const int shift = 28 - 4 * pass;
+      __syncthreads();
+      const uint32_t prefix = s_prefix;
+      for (int b = 0; b < SF_BINS; ++b) bins_d[b * SF_THREADS + tid] = 0.0;
+      if (pass == first) {
+        double local = 0.0;
+        for_each_key(row, V, [&](int i, float x, uint32_t key) {
+          const double v = key <= k_key ? exp((double)x / (double)T - mx) : 0.0;
+          e[i] = v;
+          local += v;
+          if (key <= k_key) bins_d[((key >> shift) & 15u) * SF_THREADS + tid] += v;
+        });
+        total = block_sum_fixed(local, s_part);
+        if (tid == 0) s_need = (double)pp * total;
+      } else {
+        for_each_key(row, V, [&](int i, float, uint32_t key) {
+          if (key <= k_key && (key >> (shift + 4)) == prefix) bins_d[((key >> shift) & 15u) * SF_THREADS + tid] += e[i];
+        });
+      }
+      sum_bins(bins_d, s_part, s_mass);
+      if (tid == 0) {
+        // bins run from the largest values down: the first one at whose end the mass reaches what is needed holds the
+        // threshold; if rounding leaves the sum a hair short, the last bin with any mass does
+        const double need = s_need;
+        double cum = 0.0, cum_last = 0.0;
+        int b = 0, last = 0;
+        for (; b < SF_BINS; ++b) {
+          if (s_mass[b] > 0.0) { last = b; cum_last = cum; }
+          if (cum + s_mass[b] >= need) break;
+          cum += s_mass[b];
+        }
+        if (b == SF_BINS) { b = last; cum = cum_last; }
+        s_prefix = (prefix << 4) | (uint32_t)b;
+        s_need = need - cum;
+      }
+    }
+    __syncthreads();
+    t_key = s_prefix;
+    need_at_t = s_need;
+  }
+  // ---- the draw. Warp w owns the contiguous range [w * span, (w + 1) * span) and walks it 32 tokens at a time, so that
+  // sums run in index order. Equal values at the threshold: the j-th of them in index order (j = 0, 1, ...) stays while
+  // j * e < need_at_t.
+  const int span = ((V + 1023) / 1024) * 32;
+  const int w_lo = min(V, warp * span), w_hi = min(V, w_lo + span);
+  if (nucleus) {
+    int ties = 0;
+    for (int i = w_lo + lane; i < w_hi; i += 32) ties += falling_key(row[i]) == t_key ? 1 : 0;
+    for (int o = 16; o; o >>= 1) ties += __shfl_xor_sync(0xffffffffu, ties, o);
+    if (lane == 0) s_wties[warp] = ties;
+  }
+  __syncthreads();
+  int j0 = 0;
+  if (nucleus)
+    for (int w = 0; w < warp; ++w) j0 += s_wties[w];
+  double run = 0.0;
+  for (int base = w_lo; base < w_hi; base += 32) {
+    const int i = base + lane;
+    const bool in = i < w_hi;
+    double v = in ? e[i] : 0.0;
+    if (nucleus) {
+      const uint32_t key = in ? falling_key(row[i]) : 0u;
+      const bool tie = in && key == t_key;
+      const unsigned int tie_mask = __ballot_sync(0xffffffffu, tie);
+      bool drop = in && key > t_key;
+      if (tie) drop = !((double)(j0 + __popc(tie_mask & ((1u << lane) - 1u))) * v < need_at_t);
+      j0 += __popc(tie_mask);
+      if (drop && v != 0.0) e[i] = 0.0;
+      if (drop) v = 0.0;
+    }
+    run += __shfl_sync(0xffffffffu, warp_scan_fixed(v, lane), 31);
+  }
+  if (lane == 0) s_wsum[warp] = run;
+  __syncthreads();
+  if (tid == 0) {
+    double before = 0.0;
+    for (int w = 0; w < 32; ++w) before += s_wsum[w];
+    const double target = uniform[r] * before;
+    before = 0.0;
+    int w = 0;
+    for (; w < 31; ++w) {
+      if (before + s_wsum[w] > target) break;
+      before += s_wsum[w];
+    }
+    s_warp = w;
+    s_need = before;
+    s_target = target;
+    s_res = amax;   // stays only if rounding leaves every running sum at or below the target
+  }
+  __syncthreads();
+  if (warp == s_warp) {
+    const double target = s_target;
+    run = s_need;
+    for (int base = w_lo; base < w_hi; base += 32) {
+      const int i = base + lane;
+      const double sc = warp_scan_fixed(i < w_hi ? e[i] : 0.0, lane);
+      const unsigned int hit = __ballot_sync(0xffffffffu, run + sc > target);
+      if (hit) {
+        if (lane == 0) s_res = base + __ffs(hit) - 1;
+        break;
+      }
+      run += __shfl_sync(0xffffffffu, sc, 31);
+    }
+  }
+  __syncthreads();
+  if (tid == 0) out[r] = s_res;
+}
+
+// scratch: R * V doubles. top_k[r] <= 0 or >= V: no top-k; top_p[r] >= 1: no top-p; temperature[r] <= 0 or top_k[r]
+// == 1: argmax.
+FZ_API int fz_sample_filtered(const float* logits, const float* temperature, const int* top_k, const float* top_p,
+                              const double* uniform, double* scratch, int* out, int R, int V, cudaStream_t stream) {
+  if (R <= 0) return FZ_OK;
+  if (V <= 0) return FZ_BAD_SHAPE;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(sample_filtered_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SF_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  fz_launch(sample_filtered_kernel, dim3(R), dim3(SF_THREADS), SF_SMEM, stream, logits, temperature, top_k, top_p, uniform,
+            scratch, out, V);
+  FZ_LAUNCH_CHECK();
+  return FZ_OK;
+}
+
 // ------------------------------------------------------------------------------------------------ error word
 // The error word is a device int the caller owns; this clears it on a stream.
 FZ_API int fz_clear_error(int* err, cudaStream_t stream) {

@@ -77,6 +77,8 @@ class LLMEngine:
         # (two of each host buffer: a step may be launched while the one before it is still in flight)
         self._temp_h = torch.zeros(2, R, dtype=torch.float32, pin_memory=pin)
         self._unif_h = torch.zeros(2, R, dtype=torch.float64, pin_memory=pin)
+        self._topk_h = torch.zeros(2, R, dtype=torch.int32, pin_memory=pin)
+        self._topp_h = torch.ones(2, R, dtype=torch.float32, pin_memory=pin)
         self._ids_h = torch.zeros(2, R, dtype=torch.int32, pin_memory=pin)
         self._events = [torch.cuda.Event() for _ in range(2)] if pin else None
         self._slot = 0
@@ -84,6 +86,8 @@ class LLMEngine:
         self.lookahead = bool(lookahead)
         self._temp_d = torch.zeros(R, dtype=torch.float32, device=dev)
         self._unif_d = torch.zeros(R, dtype=torch.float64, device=dev)
+        self._topk_d = torch.zeros(R, dtype=torch.int32, device=dev)
+        self._topp_d = torch.ones(R, dtype=torch.float32, device=dev)
         self._ids_d = torch.zeros(R, dtype=torch.int32, device=dev)
         self.runner.prev_ids = self._ids_d
         self.cuda_graphs = bool(cuda_graphs) and pin and model.graph_safe()
@@ -91,6 +95,7 @@ class LLMEngine:
         self.launches_per_graph: dict[tuple, int] = {}           # kernels of this package in one replay of it
         self._greedy_step = True
         self._ids_only = False
+        self._filtered_step = False
         self._buckets = sorted({min(1 << i, R) for i in range(R.bit_length() + 1)})
         self.stats = {"steps": 0, "decode_steps": 0, "prefill_steps": 0, "mixed_steps": 0, "tokens": 0,
                       "preemptions": 0, "graph_replays": 0, "lookahead_steps": 0, "h2d_bytes": 0, "d2h_bytes": 0}
@@ -246,16 +251,22 @@ class LLMEngine:
         ids and the error word down. Does not wait for it."""
         runner, ops, st = self.runner, self.ops, self.stats
         slot = self._slot = (self._slot + 1) % 2
-        temp_h, unif_h = self._temp_h[slot], self._unif_h[slot]
+        temp_h, unif_h, topk_h, topp_h = self._temp_h[slot], self._unif_h[slot], self._topk_h[slot], self._topp_h[slot]
         R = len(rows)
+        filtered = False
         for seq, i in rows:
             p = seq.params
             device_row = p.on_device and not p.greedy
             temp_h[i] = p.temperature if device_row else 0.0
             unif_h[i] = seq.sampler.next_uniform() if device_row else 0.0
-        # all rows greedy: the row-split argmax kernel picks the tokens; else the sampling kernel (argmax for its greedy rows)
+            topk_h[i] = p.top_k if device_row else 0
+            topp_h[i] = p.top_p if device_row else 1.0
+            filtered = filtered or (device_row and p.filtered)
+        # all rows greedy: the row-split argmax kernel picks the tokens; else a sampling kernel (argmax for its greedy
+        # rows): the plain one, or the one with the top-k and top-p filters if some row has them
         self._greedy_step = all(s.params.greedy or not s.params.on_device for s, _ in rows)
         self._ids_only = all(s.params.greedy and s.params.on_device for s, _ in rows)
+        self._filtered_step = filtered
         bucket = next((b for b in self._buckets if b >= len(portions)), None) if decode_only and self.cuda_graphs else None
         pad = bucket or 0
         starts = runner.prepare(portions, pad_rows=pad, pad_wanted=pad)
@@ -267,9 +278,14 @@ class LLMEngine:
             temp_h[R:n_w] = 0.0
             self._temp_d[:n_w].copy_(temp_h[:n_w], non_blocking=True)
             self._unif_d[:n_w].copy_(unif_h[:n_w], non_blocking=True)
-        st["h2d_bytes"] += runner.meta.size * 4 + n_w * 12
+            if filtered:
+                topk_h[R:n_w] = 0
+                topp_h[R:n_w] = 1.0
+                self._topk_d[:n_w].copy_(topk_h[:n_w], non_blocking=True)
+                self._topp_d[:n_w].copy_(topp_h[:n_w], non_blocking=True)
+        st["h2d_bytes"] += runner.meta.size * 4 + n_w * (20 if filtered else 12)
         if bucket is not None:
-            key = (bucket, self._greedy_step, self._ids_only)
+            key = (bucket, self._greedy_step, self._ids_only, self._filtered_step)
             g = self._graphs.get(key)
             if g is None:
                 # warm-up (builds, sets kernel attributes, sizes the buffers) on a copy of the ids the step may read
@@ -316,6 +332,9 @@ class LLMEngine:
             return None
         if n_wanted and self._greedy_step:
             self.ops.argmax(logits, self._ids_d[:n_wanted])
+        elif n_wanted and self._filtered_step:
+            self.ops.sample_filtered(logits, self._temp_d[:n_wanted], self._topk_d[:n_wanted], self._topp_d[:n_wanted],
+                                     self._unif_d[:n_wanted], self._ids_d[:n_wanted])
         elif n_wanted:
             self.ops.sample(logits, self._temp_d[:n_wanted], self._unif_d[:n_wanted], self._ids_d[:n_wanted])
         return logits

@@ -53,11 +53,14 @@ class Workspace:
     def __init__(self, device: torch.device, row_capacity: int):
         self.device, self.row_capacity = device, row_capacity
         self._bufs: dict[tuple, torch.Tensor] = {}
+        self._retired: list[torch.Tensor] = []      # outgrown buffers: a captured step may still point at them
 
     def get(self, tag: str, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
         key = (tag, tuple(shape[1:]), dtype)
         buf = self._bufs.get(key)
         if buf is None or buf.shape[0] < shape[0]:
+            if buf is not None:
+                self._retired.append(buf)
             buf = torch.empty((max(self.row_capacity, shape[0]), *shape[1:]), dtype=dtype, device=self.device)
             self._bufs[key] = buf
         return buf[:shape[0]]

@@ -89,3 +89,11 @@ class Ops:
         """out[r] = the token at which the running sum of softmax(logits[r] / temperature[r]) (float64, in index
         order) first exceeds uniform[r] * total; temperature[r] <= 0 means argmax. uniform: float64 in [0, 1)."""
         raise NotImplementedError
+
+    def sample_filtered(self, logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+                        uniform: torch.Tensor, out: torch.Tensor) -> None:
+        """`sample` after the reference's filters on logits[r] / temperature[r] (fusezap/serve/sampling.py:25-45):
+        top_k[r] (int32; <= 0 or >= V: off, 1: argmax) keeps what is not below the k-th largest value, ties included;
+        top_p[r] (float32; >= 1: off) then keeps, in falling order of value and rising index among equals, every token
+        before which less than top_p[r] of the probability lies."""
+        raise NotImplementedError

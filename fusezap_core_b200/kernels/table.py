@@ -46,7 +46,8 @@ class CudaOps(Ops):
         self._err_host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
         self.launches = 0
         self._stream_handle = None
-        self._argmax_scratch = None
+        self._scratch_bufs: dict[str, torch.Tensor] = {}
+        self._retired: list[torch.Tensor] = []      # outgrown scratch: a captured step may still point at it
         self.tc = None
         if self.dtype == torch.bfloat16:
             self.tc = load("fzb200_tc")      # tcgen05 / TMA kernels
@@ -54,9 +55,7 @@ class CudaOps(Ops):
         self.prefill_tcgen05 = True        # False: long portions on the mma.sync flash-attention kernel
         self.fuse_swiglu = True            # gate/up product and SwiGLU in one kernel where the sizes allow it
         self.fuse_argmax = True            # lm_head product and argmax in one pass where no logits are asked for
-        self._lm_scratch = None
         self.fuse_rope = True              # q/k/v product, rotation and cache write in one kernel (few-token steps)
-        self._attn_scratch: torch.Tensor | None = None      # float32 partial outputs of the split decode attention
 
     # ---- plumbing
     def begin_step(self) -> None:
@@ -71,6 +70,17 @@ class CudaOps(Ops):
         if self._stream_handle is not None:
             return self._stream_handle
         return c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def _scratch(self, name: str, numel: int, dtype: torch.dtype, zero: bool = False) -> torch.Tensor:
+        """A scratch buffer of at least `numel` elements. It only ever grows, and a buffer that was outgrown is kept
+        alive, since a captured step that was recorded with it still writes there."""
+        buf = self._scratch_bufs.get(name)
+        if buf is None or buf.numel() < numel:
+            if buf is not None:
+                self._retired.append(buf)
+            buf = (torch.zeros if zero else torch.empty)(numel, dtype=dtype, device=self.device)
+            self._scratch_bufs[name] = buf
+        return buf
 
     def _check(self, status: int, what: str) -> None:
         self.launches += 1
@@ -257,11 +267,10 @@ class CudaOps(Ops):
         if w.shape[1] != k or out.shape[0] != m or (bias is not None and bias.shape[0] != n):
             raise KernelError(f"linear_argmax: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
         need = m * ((n + 127) // 128)
-        if self._lm_scratch is None or self._lm_scratch[0].numel() < need:
-            self._lm_scratch = (torch.empty(need, dtype=torch.float32, device=self.device),
-                                torch.empty(need, dtype=torch.int32, device=self.device))
-        self._check(self.tc.fz_gemm_tc_argmax(_p(a), _p(w), _p(bias), c_int(m), c_int(n), c_int(k), _p(self._lm_scratch[0]),
-                                              _p(self._lm_scratch[1]), _p(out), _p(self.err), self._stream()),
+        tile_val = self._scratch("lm_head tile maxima", need, torch.float32)
+        tile_idx = self._scratch("lm_head tile indices", need, torch.int32)
+        self._check(self.tc.fz_gemm_tc_argmax(_p(a), _p(w), _p(bias), c_int(m), c_int(n), c_int(k), _p(tile_val),
+                                              _p(tile_idx), _p(out), _p(self.err), self._stream()),
                     "linear_argmax (tensor cores)")
         self.launches += 1     # the reduction over the tiles
         return True
@@ -283,10 +292,8 @@ class CudaOps(Ops):
                 # rows of short portions and decoded tokens: split over key partitions, partials in float32 scratch
                 parts = self.tc.fz_attn_partitions(c_int(meta.max_context))
                 need = n * hq * parts * (hd + 2)
-                if self._attn_scratch is None or self._attn_scratch.numel() < need:
-                    self._attn_scratch = torch.empty(need, dtype=torch.float32, device=self.device)
-                part_o = self._attn_scratch
-                part_ml = self._attn_scratch[n * hq * parts * hd:]
+                part_o = self._scratch("attention partials", need, torch.float32)
+                part_ml = part_o[n * hq * parts * hd:]
                 self._check(self.tc.fz_attn_decode(
                     _p(q), _p(k), _p(v), _p(meta.pos), _p(meta.seq_row), _p(meta.seg), _p(table), c_int(table.shape[1]),
                     c_longlong(page_stride), c_int(cache.page_size), _p(out), _p(part_o), _p(part_ml), c_int(n),
@@ -328,12 +335,10 @@ class CudaOps(Ops):
         if out.shape[0] != r:
             raise KernelError(f"argmax: logits {tuple(logits.shape)}, out {tuple(out.shape)}")
         # scratch of the row-split argmax: per row up to 64 partial (value, index) pairs and one counter (kept zero)
-        if self._argmax_scratch is None or self._argmax_scratch[2].numel() < r:
-            cap = max(r, 64)
-            self._argmax_scratch = (torch.empty(cap * 64, dtype=torch.float32, device=self.device),
-                                    torch.empty(cap * 64, dtype=torch.int32, device=self.device),
-                                    torch.zeros(cap, dtype=torch.int32, device=self.device))
-        pv, pi, cnt = self._argmax_scratch
+        cap = max(r, 64)
+        pv = self._scratch("argmax partial values", cap * 64, torch.float32)
+        pi = self._scratch("argmax partial indices", cap * 64, torch.int32)
+        cnt = self._scratch("argmax counters", cap, torch.int32, zero=True)
         self._check(self.core.fz_argmax(_p(logits), _p(out), c_int(r), c_int(v), _p(pv), _p(pi), _p(cnt), self._stream()),
                     "argmax")
 
@@ -347,3 +352,17 @@ class CudaOps(Ops):
             raise KernelError("sample: row counts differ")
         self._check(self.core.fz_sample(_p(logits), _p(temperature), _p(uniform), _p(out), c_int(r), c_int(v),
                                         self._stream()), "sample")
+
+    def sample_filtered(self, logits, temperature, top_k, top_p, uniform, out) -> None:
+        self._want(logits, "logits", (torch.float32,), 2)
+        self._want(temperature, "temperature", (torch.float32,), 1)
+        self._want(top_k, "top_k", (torch.int32,), 1)
+        self._want(top_p, "top_p", (torch.float32,), 1)
+        self._want(uniform, "uniform", (torch.float64,), 1)
+        self._want(out, "sample output", (torch.int32,), 1)
+        r, v = logits.shape
+        if any(t.shape[0] != r for t in (out, temperature, top_k, top_p, uniform)):
+            raise KernelError("sample_filtered: row counts differ")
+        weights = self._scratch("sampling weights", r * v, torch.float64)       # exp(x / T - max) of every token
+        self._check(self.core.fz_sample_filtered(_p(logits), _p(temperature), _p(top_k), _p(top_p), _p(uniform), _p(weights),
+                                                 _p(out), c_int(r), c_int(v), self._stream()), "sample_filtered")

@@ -26,5 +26,11 @@ class SamplingParams:
 
     @property
     def on_device(self) -> bool:
-        """Greedy or plain temperature sampling: the device kernels pick the token; anything else goes to the host."""
-        return self.repetition_penalty == 1.0 and (self.greedy or (self.top_k == 0 and self.top_p >= 1.0))
+        """The device kernels pick the token (greedy, temperature, top-k, top-p); a repetition penalty, which needs the
+        request's history, goes to the host."""
+        return self.repetition_penalty == 1.0
+
+    @property
+    def filtered(self) -> bool:
+        """Sampled after a top-k or top-p filter."""
+        return not self.greedy and (self.top_k > 0 or self.top_p < 1.0)

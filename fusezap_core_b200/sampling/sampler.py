@@ -1,10 +1,11 @@
 """Token choice. Order of the filters as in the reference (fusezap/serve/sampling.py:6-10, 61-73): repetition penalty,
 temperature, top-k, top-p, softmax in float64, one seeded uniform draw per token.
 
-Greedy rows and plain temperature rows are picked by the device kernels (`Ops.argmax`, `Ops.sample`): the host only
-supplies the request's next uniform number, so the draw is `searchsorted(cumsum(p), u * sum(p), side="right")` as in
-sampling.py:73. Rows with top-k, top-p or a repetition penalty copy their logits row to the host and go through
-`host_choice` below, which restates the reference's filters.
+Greedy rows, temperature rows and rows with top-k or top-p are picked by the device kernels (`Ops.argmax`, `Ops.sample`,
+`Ops.sample_filtered`): the host only supplies the request's next uniform number, so the draw is
+`searchsorted(cumsum(p), u * sum(p), side="right")` as in sampling.py:73. Rows with a repetition penalty, which needs the
+request's history, copy their logits row to the host and go through `host_choice` below, which restates the reference's
+filters.
 """
 from __future__ import annotations
 from typing import Sequence

@@ -8,6 +8,8 @@ from __future__ import annotations
 import numpy as np
 import torch
 
+import plain_model
+
 
 class PlainOps:
     def __init__(self, dtype: torch.dtype = torch.float32):
@@ -115,6 +117,19 @@ class PlainOps:
             x = a[r].astype(np.float64) / t
             e = np.exp(x - x.max())
             c = np.cumsum(e)
+            res[r] = int(np.searchsorted(c, float(uniform[r]) * c[-1], side="right").clip(0, len(c) - 1))
+        out.copy_(torch.from_numpy(res))
+
+    def sample_filtered(self, logits, temperature, top_k, top_p, uniform, out) -> None:
+        a = logits.detach().cpu().numpy()
+        res = np.zeros(a.shape[0], np.int32)
+        for r in range(a.shape[0]):
+            t, k, p = float(temperature[r]), int(top_k[r]), float(top_p[r])
+            if t <= 0 or k == 1:
+                res[r] = int(np.argmax(a[r]))
+                continue
+            x = plain_model.top_p_filter(plain_model.top_k_filter(a[r].astype(np.float64) / t, k), p)
+            c = np.cumsum(np.exp(x - x.max()))
             res[r] = int(np.searchsorted(c, float(uniform[r]) * c[-1], side="right").clip(0, len(c) - 1))
         out.copy_(torch.from_numpy(res))
 

@@ -106,11 +106,17 @@ def test_seeded_sampling_does_not_depend_on_the_batch(models):
     P = prompts(cfg, (1, 7, 23, 40), seed=2)
     ps = [SamplingParams(max_tokens=12, temperature=0.8, seed=10 + i, ignore_eos=True) for i in range(4)]
     ps[2] = SamplingParams(max_tokens=12, temperature=0.8, top_k=20, top_p=0.9, repetition_penalty=1.2, seed=5, ignore_eos=True)
+    ps[3] = SamplingParams(max_tokens=12, temperature=1.3, top_k=12, top_p=0.8, seed=6, ignore_eos=True)   # filters in the kernel table
     mk = lambda: LLMEngine(model, num_blocks=64, block_size=8, max_num_seqs=4, max_prefill_tokens=8, max_model_len=128)
     together = mk().generate(P, ps)
     alone = [mk().generate([p], [q])[0] for p, q in zip(P, ps)]
     assert together == alone
     assert len({tuple(t) for t in together}) == 4 and together != mk().generate(P, SamplingParams(max_tokens=12, ignore_eos=True))
+    rng, ids, out = np.random.default_rng(6), list(P[3]), []
+    for _ in range(12):
+        t = plain_model.sample(plain_model.forward(cfg, w, ids)[-1].numpy(), ids, float(np.float32(1.3)), 12, float(np.float32(0.8)), 1.0, rng)
+        out.append(t); ids.append(t)
+    assert out == together[3]
     # the sampled tokens follow the plain sampler fed with the plain model's logits
     rng, ids, out = np.random.default_rng(5), list(P[2]), []
     for _ in range(12):

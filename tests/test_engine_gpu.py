@@ -117,10 +117,18 @@ def test_seeded_sampling_on_the_device(folders):
     model = load_model(d, "float32", "cuda:0", max_len=128)
     ps = [SamplingParams(max_tokens=12, temperature=0.8, seed=10 + i, ignore_eos=True) for i in range(4)]
     ps[2] = SamplingParams(max_tokens=12, temperature=0.8, top_k=20, top_p=0.9, repetition_penalty=1.2, seed=5, ignore_eos=True)
+    ps[3] = SamplingParams(max_tokens=12, temperature=1.3, top_k=12, top_p=0.8, seed=6, ignore_eos=True)   # filters on the device
     mk = lambda: LLMEngine(model, num_blocks=64, block_size=8, max_num_seqs=4, max_prefill_tokens=8, max_model_len=128)
     together = mk().generate(P, ps)
     alone = [mk().generate([p], [q])[0] for p, q in zip(P, ps)]
     assert together == alone, "a request's draws do not depend on the batch"
+    # request 3 (top-k and top-p, picked on the device): every token lies in the set the plain filters keep
+    ids = list(P[3])
+    for t in together[3]:
+        lg = plain_model.forward(cfg, w, ids)[-1].numpy().astype(np.float64) / float(np.float32(1.3))
+        kept = plain_model.top_p_filter(plain_model.top_k_filter(lg, 12), float(np.float32(0.8)))
+        assert np.isfinite(kept[t]) and np.isfinite(kept).sum() <= 12
+        ids.append(t)
     # request 0 (temperature only, picked on the device) against the plain sampler on the plain model's logits
     rng, ids = np.random.default_rng(10), list(P[0])
     for t in together[0]:

@@ -289,6 +289,41 @@ def test_sample_matches_the_host_rule():
     assert int(out[5]) == int(lg[5].argmax())
 
 
+@pytest.mark.parametrize("V", [1511, 50257])
+def test_sample_filtered_matches_the_host_rule(V):
+    """Top-k and top-p on the device against the plain filters: every mix of the two, rows that are greedy, logits on a
+    coarse grid (so that equal values sit at both thresholds), masked tokens, and draws at both ends."""
+    cu, pl = ops_pair("float32")
+    g = torch.Generator().manual_seed(9)
+    R = 40
+    lg = torch.randn(R, V, generator=g) * 3
+    lg[8:16] = (lg[8:16] * 2).round() / 2              # many equal values
+    lg[16:20] = (lg[16:20] / 4).round()                # a handful of distinct values: long runs of equals at a threshold
+    lg[20, ::3] = -float("inf")
+    lg[21] = 0.0                                       # all equal
+    lg[22, 100] = 60.0                                 # one token holds all the mass
+    temp = torch.full((R,), 0.8); temp[5] = 0.0; temp[6] = 2.5; temp[24:32] = 1.7
+    top_k = torch.zeros(R, dtype=torch.int32); top_p = torch.ones(R)
+    ks = [0, 1, 2, 7, 50, 300, V - 1, V, V + 5]
+    ps = [1.0, 0.999, 0.9, 0.5, 0.1, 1e-6]
+    for r in range(R):
+        top_k[r] = ks[r % len(ks)]
+        top_p[r] = ps[(r // 2) % len(ps)]
+    u = torch.rand(R, generator=g, dtype=torch.float64); u[7] = 0.0; u[9] = 1.0 - 2.0 ** -53; u[17] = 0.0; u[18] = 1.0 - 2.0 ** -53
+    out, outp = torch.empty(R, dtype=torch.int32, device="cuda"), torch.empty(R, dtype=torch.int32)
+    cu.sample_filtered(lg.cuda(), temp.cuda(), top_k.cuda(), top_p.cuda(), u.cuda(), out)
+    pl.sample_filtered(lg, temp, top_k, top_p, u, outp)
+    assert out.cpu().tolist() == outp.tolist()
+    again = torch.empty_like(out)
+    cu.sample_filtered(lg.cuda(), temp.cuda(), top_k.cuda(), top_p.cuda(), u.cuda(), again)
+    assert torch.equal(out, again)
+    # without filters it is the plain sampling kernel
+    plain = torch.empty_like(out)
+    cu.sample(lg.cuda(), temp.cuda(), u.cuda(), plain)
+    cu.sample_filtered(lg.cuda(), temp.cuda(), torch.zeros_like(top_k).cuda(), torch.ones(R).cuda(), u.cuda(), again)
+    assert torch.equal(plain, again)
+
+
 def test_refusals():
     cu, _ = ops_pair("float32")
     from fusezap_core_b200.kernels.table import KernelError
