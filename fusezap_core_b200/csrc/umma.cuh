@@ -27,6 +27,15 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
 }
+// The same with A in tensor memory: lane = row, two bf16 per 32-bit column (k even in the low half), so 16 k are 8
+// columns; B from shared memory as above.
+__device__ __forceinline__ void umma_bf16_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -35,6 +44,30 @@ __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+// 2^x for two finite x <= 0 on the FMA pipe, which takes two float32 per instruction here, so that the special-function
+// unit (4 results per clock and scheduler) is not the only place exponentials come from: n = round(x) by the magic-number
+// addition, f = x - n in [-0.5, 0.5], 2^f by a polynomial of degree 5 (relative error 2.1e-7, about what ex2.approx has),
+// and n added to the exponent field as an integer. x is clamped at -125, so the result is never below 2^-125.5.
+__device__ __forceinline__ float2 exp2_fma2(float2 x) {
+  x.x = fmaxf(x.x, -125.f);
+  x.y = fmaxf(x.y, -125.f);
+  const float2 t = __fadd2_rn(x, make_float2(12582912.f, 12582912.f));          // 1.5 * 2^23: the low bits of t are n
+  const float2 n = __fadd2_rn(t, make_float2(-12582912.f, -12582912.f));
+  const float2 f = __fadd2_rn(x, make_float2(-n.x, -n.y));
+  float2 p = make_float2(0.00132764654699713f, 0.00132764654699713f);
+  p = __ffma2_rn(p, f, make_float2(0.009675540961325169f, 0.009675540961325169f));
+  p = __ffma2_rn(p, f, make_float2(0.05550713464617729f, 0.05550713464617729f));
+  p = __ffma2_rn(p, f, make_float2(0.24022120237350464f, 0.24022120237350464f));
+  p = __ffma2_rn(p, f, make_float2(0.6931469440460205f, 0.6931469440460205f));
+  p = __ffma2_rn(p, f, make_float2(1.0000001192092896f, 1.0000001192092896f));
+  return make_float2(__int_as_float(__float_as_int(t.x) * (1 << 23) + __float_as_int(p.x)),
+                     __int_as_float(__float_as_int(t.y) * (1 << 23) + __float_as_int(p.y)));
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
 }
 // 16 consecutive float32 columns of this thread's TMEM lane
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
@@ -62,6 +95,19 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// 32 consecutive 32-bit columns of this thread's TMEM lane, written; complete when the call returns
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
 // Shared-memory operand descriptors (64 bits): [0,14) address >> 4, [16,30) leading offset >> 4, [32,46) stride offset
