@@ -1,23 +1,26 @@
 // Causal flash attention for prompt portions over the paged bf16 cache on the 5th-generation tensor cores.
 //
-// grid (tiles, query heads), 352 threads, one CTA per SM. A tile is 128 consecutive token rows of one portion (the host
-// lists the tiles, the ones with the most keys first); the 128 rows are the 128 TMEM lanes. Keys come in tiles of 128:
-//   warps 0, 10 TMA producers: warp 0 the Q tile once and the key tiles, warp 10 the value tiles (a page's rows of one kv
-//               head are one box of the pool seen as a 2-D array of rows; 128-byte swizzle), each into a ring of its own
-//               and as far ahead as the ring allows (a key stage is free again as soon as its score product is done);
+// One block per SM (352 threads), each walking its share of the work items: an item is a tile of 128 consecutive token
+// rows of one portion (the host lists the tiles, the ones with the most keys first) and one query head; items are dealt
+// out in rows of gridDim.x, every other row backwards, which evens out the causal tile sizes. The 128 rows are the 128
+// TMEM lanes. Keys come in tiles of 128; every role counts the key tiles it has gone through, so rings, buffers and
+// barrier phases carry over from item to item and the producers fetch the next item's tiles while this one finishes:
+//   warps 0, 10 TMA producers: warp 0 the Q tile (once the last score product of the item before has freed it) and the
+//               key tiles, warp 10 the value tiles (a page's rows of one kv head are one box of the pool seen as a 2-D
+//               array of rows; 128-byte swizzle), each into a ring of its own and as far ahead as the ring allows (a
+//               key stage is free again as soon as its score product is done);
 //   warp 1      one lane issues tcgen05.mma: S = Q K^T (128 x 128 x hd, both operands K-major) into one of two TMEM
-//               buffers, one key tile ahead of the softmax warps, and, once they have written P, PV = P V (128 x hd x
-//               128; P is the A operand in tensor memory, V the MN-major B operand as TMA delivers it) into one of two
-//               more;
+//               buffers, one key tile ahead of the softmax warps, and, once they have written P, O += P V (128 x hd x
+//               128; P is the A operand in tensor memory, V the MN-major B operand as TMA delivers it), accumulated in
+//               tensor memory over the item's key tiles;
 //   warps 2..9  two threads per row, each with 64 of the tile's 128 score columns and half of the output dimensions (the
 //               two warps of a row pair sit on one scheduler, so one computes while the other waits): read the
 //               scores from TMEM once, scale, mask (causal by position, window), exchange the row maximum through
-//               shared memory, online softmax in the exp2 domain with float32 max and sum, write P as bf16 pairs back
-//               into tensor memory over the scores they came from (P never passes through shared memory, whose
-//               bandwidth the operand reads of the two products and the TMA fills already use up); then fold the PV
-//               product of the tile
-//               *before* into the float32 output registers, so that the tensor core computes a tile's PV while
-//               these warps already work on the next tile's scores. At the end normalise and store the row.
+//               shared memory, online softmax in the exp2 domain with float32 max and sum (packed float32 x 2
+//               arithmetic; three pairs of exponentials in eight by a polynomial on the FMA pipe, the rest on the
+//               special-function unit), write P as bf16 pairs back into tensor memory over the scores they came from.
+//               O stays in tensor memory and is rescaled there only when a row's maximum has grown by more than 2^8
+//               over the maximum in use, so it costs no registers; at the item's end normalise and store the rows.
 // Key tiles start at multiples of 128 in absolute position, so a row's sums do not depend on how the prompt was cut.
 // Waits on the CTA's own mbarriers are bounded; a wait that gives up sets the error bit. No multicast.
 // (The reference's paged prefill kernel is an mma.sync kernel with 64-row tiles: fusezap/device/cuda_kernels/
@@ -324,8 +327,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         const float mu = m_run == -INFINITY ? 0.f : m_run;
         // P goes back into tensor memory as the A operand of the PV product: bf16 pairs, over the first 64 columns of
         // the score buffer (both threads of the row have read their scores: the pair barrier above lies between).
-        // Where every key of this thread's half is visible (no -inf), every other pair of exponentials runs on the FMA
-        // pipe.
+        // Where every key of this thread's half is visible (no -inf), three pairs of exponentials in eight run on the
+        // FMA pipe: that balances it with the special-function unit.
         const float2 sc2 = make_float2(scale_log2, scale_log2), nmu2 = make_float2(-mu, -mu);
         float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};      // two packed chains; added up in a fixed order below
         uint32_t w[32];
@@ -333,7 +336,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             const float2 x = __ffma2_rn(make_float2(v[2 * j], v[2 * j + 1]), sc2, nmu2);
-            const float2 e = (j & 1) ? exp2_fma2(x) : make_float2(fast_exp2(x.x), fast_exp2(x.y));
+            const float2 e = ((0x52u >> (j & 7)) & 1u) ? exp2_fma2(x) : make_float2(fast_exp2(x.x), fast_exp2(x.y));      // 3 pairs in 8
             sum2[j & 1] = __fadd2_rn(sum2[j & 1], e);
             const __nv_bfloat162 pk = __floats2bfloat162_rn(e.x, e.y);
             w[j] = *(const uint32_t*)&pk;

@@ -45,24 +45,24 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-// 2^x for two finite x <= 0 on the FMA pipe, which takes two float32 per instruction here, so that the special-function
-// unit (4 results per clock and scheduler) is not the only place exponentials come from: n = round(x) by the magic-number
-// addition, f = x - n in [-0.5, 0.5], 2^f by a polynomial of degree 5 (relative error 2.1e-7, about what ex2.approx has),
-// and n added to the exponent field as an integer. x is clamped at -125, so the result is never below 2^-125.5.
+// 2^x for two finite x on the FMA pipe, which takes two float32 per instruction here, so that the special-function unit
+// (4 results per clock and scheduler) is not the only place exponentials come from: n = round(x) by the magic-number
+// addition, f = x - n in [-0.5, 0.5], 2^f by a polynomial of degree 4 (relative error 2.7e-6), and n added to the
+// exponent field with integer instructions (they run on the ALU pipe). x is clamped at -125, so the result is never
+// below 2^-125.5; x must stay below 127.
 __device__ __forceinline__ float2 exp2_fma2(float2 x) {
   x.x = fmaxf(x.x, -125.f);
   x.y = fmaxf(x.y, -125.f);
   const float2 t = __fadd2_rn(x, make_float2(12582912.f, 12582912.f));          // 1.5 * 2^23: the low bits of t are n
   const float2 n = __fadd2_rn(t, make_float2(-12582912.f, -12582912.f));
   const float2 f = __fadd2_rn(x, make_float2(-n.x, -n.y));
-  float2 p = make_float2(0.00132764654699713f, 0.00132764654699713f);
-  p = __ffma2_rn(p, f, make_float2(0.009675540961325169f, 0.009675540961325169f));
-  p = __ffma2_rn(p, f, make_float2(0.05550713464617729f, 0.05550713464617729f));
-  p = __ffma2_rn(p, f, make_float2(0.24022120237350464f, 0.24022120237350464f));
-  p = __ffma2_rn(p, f, make_float2(0.6931469440460205f, 0.6931469440460205f));
-  p = __ffma2_rn(p, f, make_float2(1.0000001192092896f, 1.0000001192092896f));
-  return make_float2(__int_as_float(__float_as_int(t.x) * (1 << 23) + __float_as_int(p.x)),
-                     __int_as_float(__float_as_int(t.y) * (1 << 23) + __float_as_int(p.y)));
+  float2 p = make_float2(0.009570094756782055f, 0.009570094756782055f);
+  p = __ffma2_rn(p, f, make_float2(0.05591785907745361f, 0.05591785907745361f));
+  p = __ffma2_rn(p, f, make_float2(0.240247443318367f, 0.240247443318367f));
+  p = __ffma2_rn(p, f, make_float2(0.6931217908859253f, 0.6931217908859253f));
+  p = __ffma2_rn(p, f, make_float2(0.9999992847442627f, 0.9999992847442627f));
+  return make_float2(__uint_as_float((__float_as_uint(t.x) << 23) + __float_as_uint(p.x)),
+                     __uint_as_float((__float_as_uint(t.y) << 23) + __float_as_uint(p.y)));
 }
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float r;
