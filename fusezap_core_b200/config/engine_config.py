@@ -19,6 +19,7 @@ class EngineConfig:
     prefill_first: int = 0                       # up to this many consecutive steps of prompt portions alone while
                                                  # others decode (0: portions and decoded tokens share every step)
     cuda_graphs: bool = True                     # replay decode steps from captured CUDA graphs
+    graph_rows: int = 256                        # other steps of at most this many rows are captured too, by their sizes
     lookahead: bool = True                       # launch the next decode step before reading the last one's tokens
     seed: int = 0
 

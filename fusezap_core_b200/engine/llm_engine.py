@@ -54,7 +54,8 @@ class _Launched:
 class LLMEngine:
     def __init__(self, model: DecoderModel, num_blocks: int = 1024, block_size: int = 16, max_num_seqs: int = 32,
                  max_prefill_tokens: int | None = None, max_model_len: int | None = None,
-                 max_num_batched_tokens: int | None = None, prefill_first: int = 0, cuda_graphs: bool = True, lookahead: bool = True):
+                 max_num_batched_tokens: int | None = None, prefill_first: int = 0, cuda_graphs: bool = True, lookahead: bool = True,
+                 graph_rows: int = 256):
         self.model = model
         self.max_model_len = int(max_model_len or model.max_len)
         if self.max_model_len > model.max_len:
@@ -91,14 +92,21 @@ class LLMEngine:
         self._ids_d = torch.zeros(R, dtype=torch.int32, device=dev)
         self.runner.prev_ids = self._ids_d
         self.cuda_graphs = bool(cuda_graphs) and pin and model.graph_safe()
-        self._graphs: dict[tuple, torch.cuda.CUDAGraph] = {}     # (bucket, all rows greedy) -> captured step
+        # Captured steps. Decode steps: by (padded row count, how the tokens are chosen). Other steps of at most
+        # `graph_rows` rows (portions of prompts, with or without decoded tokens beside them) are bound by the host's
+        # launches, not by the GPU: they are captured too, by the sizes that fix their launches, the second time such
+        # a step comes up (all else a step depends on lies in device memory at fixed addresses).
+        self.graph_rows = int(graph_rows)
+        self._step_seen: dict[tuple, int] = {}
+        self._step_keys: list[tuple] = []                        # captured non-decode steps, oldest first
+        self._graphs: dict[tuple, torch.cuda.CUDAGraph] = {}     # key -> captured step
         self.launches_per_graph: dict[tuple, int] = {}           # kernels of this package in one replay of it
         self._greedy_step = True
         self._ids_only = False
         self._filtered_step = False
         self._buckets = sorted({min(1 << i, R) for i in range(R.bit_length() + 1)})
         self.stats = {"steps": 0, "decode_steps": 0, "prefill_steps": 0, "mixed_steps": 0, "tokens": 0,
-                      "preemptions": 0, "graph_replays": 0, "lookahead_steps": 0, "h2d_bytes": 0, "d2h_bytes": 0}
+                      "preemptions": 0, "graph_replays": 0, "step_graph_replays": 0, "lookahead_steps": 0, "h2d_bytes": 0, "d2h_bytes": 0}
 
     # ---- a model and its engine in one call
     @classmethod
@@ -270,7 +278,19 @@ class LLMEngine:
         bucket = next((b for b in self._buckets if b >= len(portions)), None) if decode_only and self.cuda_graphs else None
         pad = bucket or 0
         starts = runner.prepare(portions, pad_rows=pad, pad_wanted=pad)
+        key = None
         if bucket is not None:
+            key = (bucket, self._greedy_step, self._ids_only, self._filtered_step)
+        elif self.cuda_graphs and runner.meta.n_rows <= self.graph_rows:
+            m = runner.meta
+            sig = ("step", m.n_rows, m.n_wanted, m.n_tiles, m.n_short_rows > 0, self._greedy_step, self._ids_only,
+                   self._filtered_step)
+            if len(self._step_seen) > 4096:
+                self._step_seen.clear()
+            self._step_seen[sig] = self._step_seen.get(sig, 0) + 1
+            if sig in self._graphs or self._step_seen[sig] >= 2:
+                key = sig
+        if key is not None:
             # a captured step must cover every context it may be replayed with (its launch sizes are fixed)
             runner.meta.max_context = self.max_model_len
         n_w = runner.meta.n_wanted
@@ -284,8 +304,7 @@ class LLMEngine:
                 self._topk_d[:n_w].copy_(topk_h[:n_w], non_blocking=True)
                 self._topp_d[:n_w].copy_(topp_h[:n_w], non_blocking=True)
         st["h2d_bytes"] += runner.meta.size * 4 + n_w * (20 if filtered else 12)
-        if bucket is not None:
-            key = (bucket, self._greedy_step, self._ids_only, self._filtered_step)
+        if key is not None:
             g = self._graphs.get(key)
             if g is None:
                 # warm-up (builds, sets kernel attributes, sizes the buffers) on a copy of the ids the step may read
@@ -299,9 +318,17 @@ class LLMEngine:
                     self._eager(n_w)
                 self.launches_per_graph[key] = ops.launches - before
                 self._graphs[key] = g
+                if key[0] == "step":
+                    self._step_keys.append(key)
+                    if len(self._step_keys) > 64:      # the oldest goes, once nothing of it is in flight
+                        torch.cuda.synchronize()
+                        old = self._step_keys.pop(0)
+                        del self._graphs[old], self.launches_per_graph[old]
             g.replay()
             ops.launches += self.launches_per_graph[key]
             st["graph_replays"] += 1
+            if key[0] == "step":
+                st["step_graph_replays"] += 1
             logits = None if self._ids_only else runner.ws.get("logits", (n_w, self.model.spec.vocab_size), torch.float32)
         else:
             logits = self._eager(n_w)

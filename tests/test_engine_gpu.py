@@ -109,6 +109,27 @@ def test_launching_ahead_under_random_traffic(folders, seed, graphs):
     assert res[True][1] > 0 and res[False][1] == 0
 
 
+def test_small_steps_replay_captured_graphs(folders):
+    """Portions of 8 prompt tokens with decoded tokens of other requests beside them: the second step of a shape is
+    captured and later ones replay it. In float32 a row's bits do not depend on the batch, so the tokens must be those
+    of an engine that launches every kernel itself."""
+    from fusezap_core_b200 import LLMEngine, SamplingParams, load_model
+    d, cfg, opts = folders["tiny_qwen2"]
+    model = load_model(d, "float32", "cuda:0", max_len=128)
+    P = prompts(cfg, (41, 33, 38, 29, 44, 35), seed=4)
+    ps = [SamplingParams(max_tokens=9 + i, ignore_eos=True) for i in range(len(P))]
+    ps[1] = SamplingParams(max_tokens=10, temperature=0.9, top_k=15, top_p=0.85, seed=3, ignore_eos=True)
+    mk = lambda graphs: LLMEngine(model, num_blocks=96, block_size=8, max_num_seqs=4, max_prefill_tokens=8,
+                                  max_model_len=128, cuda_graphs=graphs)
+    with_graphs, without = mk(True), mk(False)
+    assert with_graphs.generate(P, ps) == without.generate(P, ps)
+    assert with_graphs.stats["step_graph_replays"] > 4 and without.stats["graph_replays"] == 0
+    assert with_graphs.cache.num_free_pages == with_graphs.cache.num_pages
+    # an engine told not to capture such steps replays decode steps only
+    only_decode = LLMEngine(model, num_blocks=96, block_size=8, max_num_seqs=4, max_prefill_tokens=8, max_model_len=128, graph_rows=0)
+    assert only_decode.generate(P, ps) == without.generate(P, ps) and only_decode.stats["step_graph_replays"] == 0
+
+
 def test_seeded_sampling_on_the_device(folders):
     from fusezap_core_b200 import LLMEngine, SamplingParams, load_model
     d, cfg, opts = folders["tiny_qwen2"]
