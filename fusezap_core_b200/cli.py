@@ -40,7 +40,13 @@ def add_engine_options(s: argparse.ArgumentParser) -> None:
     s.add_argument("--max-prefill-tokens", type=int, default=None, help="prompt tokens per step (default 2048, at most max-model-len)")
     s.add_argument("--num-blocks", type=int, default=1024, help="cache pages (shared by all requests)")
     s.add_argument("--block-size", type=int, default=16, help="tokens per page")
-    s.add_argument("--no-cuda-graphs", action="store_true", help="launch decode steps kernel by kernel")
+    s.add_argument("--max-num-batched-tokens", type=int, default=None,
+                   help="all tokens per step (default max-num-seqs + max-prefill-tokens)")
+    s.add_argument("--prefill-first", type=int, default=0,
+                   help="up to this many consecutive steps of prompt portions alone while others decode (default 0)")
+    s.add_argument("--no-cuda-graphs", action="store_true", help="launch every step kernel by kernel")
+    s.add_argument("--graph-rows", type=int, default=256,
+                   help="steps of at most this many rows that are not pure decode steps replay graphs captured by shape")
     s.add_argument("--no-lookahead", action="store_true", help="read each decode step's tokens before launching the next")
 
 
@@ -97,7 +103,8 @@ def build_engine(a: argparse.Namespace):
         model = load_model(a.model, resolve_dtype(a.dtype), a.device, max_len=a.max_model_len)
     return LLMEngine(model, num_blocks=a.num_blocks, block_size=a.block_size, max_num_seqs=a.max_num_seqs,
                      max_prefill_tokens=a.max_prefill_tokens, max_model_len=a.max_model_len,
-                     cuda_graphs=not a.no_cuda_graphs, lookahead=not a.no_lookahead)
+                     max_num_batched_tokens=a.max_num_batched_tokens, prefill_first=a.prefill_first,
+                     cuda_graphs=not a.no_cuda_graphs, lookahead=not a.no_lookahead, graph_rows=a.graph_rows)
 
 
 def cmd_generate(a: argparse.Namespace) -> int:
