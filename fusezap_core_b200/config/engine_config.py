@@ -34,6 +34,8 @@ class EngineConfig:
             raise ValueError(f"max_num_batched_tokens must be positive, got {self.max_num_batched_tokens}")
         if self.prefill_first < 0:
             raise ValueError("prefill_first must be >= 0")
+        if not isinstance(self.graph_rows, int) or self.graph_rows < 0:
+            raise ValueError(f"graph_rows must be an integer >= 0, got {self.graph_rows!r}")
 
     @property
     def token_budget(self) -> int:

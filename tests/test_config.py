@@ -102,9 +102,27 @@ def test_schedule_validation():
 def test_engine_config():
     e = EngineConfig(max_num_seqs=8, max_prefill_tokens=64)
     assert e.token_budget == 72 and EngineConfig(max_num_batched_tokens=100).token_budget == 100
-    for bad in (dict(dtype="float16"), dict(block_size=0), dict(num_blocks=-1), dict(prefill_first=-1)):
+    for bad in (dict(dtype="float16"), dict(block_size=0), dict(num_blocks=-1), dict(prefill_first=-1), dict(graph_rows=-1)):
         with pytest.raises(ValueError):
             EngineConfig(**bad)
+    assert EngineConfig().graph_rows == 256 and EngineConfig(graph_rows=0).graph_rows == 0
+
+
+def test_sampling_params_say_who_picks_the_token():
+    """Greedy, temperature, top-k and top-p rows are picked by the device kernels; a repetition penalty needs the
+    request's history and goes to the host (fusezap/serve/sampling.py:6-10 gives the order of the filters)."""
+    from fusezap_core_b200 import SamplingParams
+    greedy, temp = SamplingParams(), SamplingParams(temperature=0.7)
+    assert greedy.greedy and greedy.on_device and not greedy.filtered
+    assert not temp.greedy and temp.on_device and not temp.filtered
+    assert SamplingParams(temperature=0.7, top_k=1).greedy and not SamplingParams(temperature=0.7, top_k=1).filtered
+    assert SamplingParams(temperature=0.7, top_k=40).filtered and SamplingParams(temperature=0.7, top_p=0.9).filtered
+    assert not SamplingParams(top_k=40).filtered, "temperature 0 is greedy whatever the filters say"
+    pen = SamplingParams(temperature=0.7, top_k=40, repetition_penalty=1.2)
+    assert pen.filtered and not pen.on_device
+    for bad in (dict(max_tokens=0), dict(temperature=-1.0), dict(top_p=0.0), dict(top_p=1.5), dict(top_k=-1), dict(repetition_penalty=0.0)):
+        with pytest.raises(ValueError):
+            SamplingParams(**bad)
 
 
 def test_generation_config_adds_stop_ids(tmp_path):

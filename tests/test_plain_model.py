@@ -92,3 +92,33 @@ def test_sampling_rules():
     a = [plain_model.sample(lg, [], 0.8, 3, 0.9, 1.1, np.random.default_rng(5)) for _ in range(1)]
     b = [plain_model.sample(lg, [], 0.8, 3, 0.9, 1.1, np.random.default_rng(5)) for _ in range(1)]
     assert a == b
+
+
+def test_two_restatements_of_the_filters_agree():
+    """The product's host sampler (used for rows with a repetition penalty) and the plain kernel table's filtered
+    sampling (the reference of the device kernel) are written apart from each other; on rows with many equal values,
+    masked tokens and every mix of top-k and top-p they must pick the same token from the same uniform number."""
+    import torch
+    from plain_ops import PlainOps
+    from fusezap_core_b200.sampling import RequestSampler
+    from fusezap_core_b200 import SamplingParams
+    rng = np.random.default_rng(3)
+    V = 257
+    for trial in range(40):
+        lg = (rng.standard_normal(V) * 3).astype(np.float32)
+        if trial % 3 == 0:
+            lg = np.round(lg * 2) / 2
+        if trial % 5 == 0:
+            lg[::4] = -np.inf
+        k = [0, 2, 7, 50, V, V + 3][trial % 6]
+        p = [1.0, 0.95, 0.5, 0.1][(trial // 2) % 4]
+        t = [0.8, 1.7][trial % 2]
+        seed = 100 + trial
+        sampler = RequestSampler(SamplingParams(temperature=float(np.float32(t)), top_k=k, top_p=float(np.float32(p)), seed=seed))
+        want = sampler.host_choice(lg, [])
+        u = np.random.default_rng(seed).random()
+        out = torch.empty(1, dtype=torch.int32)
+        PlainOps().sample_filtered(torch.from_numpy(lg)[None], torch.tensor([t], dtype=torch.float32),
+                                   torch.tensor([k], dtype=torch.int32), torch.tensor([p], dtype=torch.float32),
+                                   torch.tensor([u], dtype=torch.float64), out)
+        assert int(out[0]) == want, (trial, k, p, t)
