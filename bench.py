@@ -79,17 +79,44 @@ class ClockSampler:
 
 
 def reference_arm(a) -> int:
-    """The unmodified reference through its own public API, if it is installed under baseline/_ref. The offline
-    install (`pip install --no-index --no-build-isolation --find-links /opt/wheelhouse --target baseline/_ref`) fails
-    here: the reference's build backend, hatchling, is not among the offline wheels, so no wheel can be built."""
-    ref = os.path.join(ROOT, "baseline", "_ref")
-    if not os.path.isdir(os.path.join(ref, "fusezap")):
-        why = ("the reference cannot be installed offline: its build backend (hatchling) is not in /opt/wheelhouse, "
-               "pip stops with ModuleNotFoundError: No module named 'hatchling'")
-    else:
-        why = ("the reference has no sm_100 path: its CUDA GEMMs are sm_90a wgmma strings compiled at run time, which do "
-               "not build for sm_100a")
-    print(json.dumps({"impl": "reference", "unavailable": why}))
+    """`--impl reference`: the unmodified reference (its `fusezap/` package under baseline/_ref) on the same workload,
+    through its own engine; see baseline/reference_arm.py. Prints the same kind of line with "impl": "reference", or
+    `{"impl": "reference", "unavailable": why}` when the reference is absent or raises."""
+    from baseline import reference_arm as ref
+    from fusezap_core_b200.cli import load_preset
+    cfg = load_preset(a.preset)
+    full_layers = cfg["num_hidden_layers"]
+    if a.layers:
+        cfg["num_hidden_layers"] = a.layers
+    a.warmup = max(a.warmup, 3)
+    clocks = ClockSampler()
+    clocks.start()
+    try:
+        r = ref.run(cfg, a.batch, a.context, a.steps, a.warmup, a.page_size, a.prefill_tokens, device=a.reference_device)
+    except BaseException as e:      # whatever the reference raises is the record
+        clocks.stop()
+        if isinstance(e, KeyboardInterrupt):
+            raise
+        print(json.dumps({"impl": "reference", "unavailable": ref.unavailable(e)}))
+        return 0
+    clk = clocks.stop()
+    Hkv = cfg["num_key_value_heads"]
+    hd = cfg.get("head_dim") or cfg["hidden_size"] // cfg["num_attention_heads"]
+    line = {
+        "metric": "decode_tokens_per_s", "value": round(r["tok_s"], 1), "unit": "tok/s", "n_gpus": 1, "steps": a.steps,
+        "warmup": a.warmup, "ms_per_step": round(r["ms"], 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "reference",
+        "config": {"model": a.preset, "layers": cfg["num_hidden_layers"], "layers_full": full_layers,
+                   "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": Hkv, "head_dim": hd,
+                   "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "global_batch": a.batch,
+                   "seq_len": a.context, "context_mean": round(r["context"], 1), "page_size": a.page_size,
+                   "parallelism": "single", "weights": "random N(0,0.02), the reference's own builder",
+                   "l2": "inputs larger than L2", "timing": "wall clock around engine.step(), device synchronised"},
+        "clocks": clk,
+        "e2e": {"value": round(r["tok_s"], 1), "unit": "tok/s", "ms_per_step": round(r["ms"], 4)},
+        "prefill": r.get("prefill"),
+    }
+    print(json.dumps(line))
     return 0
 
 
@@ -107,6 +134,7 @@ def main() -> int:
     ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page (the engine's block_size)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--reference-device", default="CUDA", help="the reference's device name for --impl reference")
     a = ap.parse_args()
     if a.impl == "reference":
         return reference_arm(a)
