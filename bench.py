@@ -179,7 +179,7 @@ def main() -> int:
         """Admits `batch` requests of n_prompt seeded tokens and steps until every one decodes."""
         rids = [eng.add_request(rng.integers(0, V, n_prompt).tolist(), SamplingParams(max_tokens=max_tokens, ignore_eos=True))
                 for _ in range(batch)]
-        while any(not eng.seqs[r].decoding for r in rids):
+        while any(not eng.requests[r].decoding for r in rids):
             eng.step()
         return rids
 
@@ -193,24 +193,24 @@ def main() -> int:
         out = {}
         # device-timed: metadata copy + graph replay per step, tokens fixed beforehand, no read-back inside
         runner, meta = eng.runner, eng.runner.meta
-        seqs = [eng.seqs[r] for r in rids]
+        seqs = [eng.requests[r] for r in rids]
         bucket = next(b for b in eng._buckets if b >= batch)
         def graph_key():      # the captured step of this bucket (greedy rows, ids picked on the device)
             return next(k for k in eng._graphs if k[0] == bucket)
         def one_step(i: int):
-            portions = [Portion(s.seq_id, [s.token_at(s.num_computed)], [0]) for s in seqs]
+            portions = [Portion(s.rid, [s.token(s.cached)], [0]) for s in seqs]
             starts = runner.prepare(portions, pad_rows=bucket, pad_wanted=bucket)
             eng._graphs[graph_key()].replay()
             runner.commit(portions, starts)
             for s, st in zip(seqs, starts):   # the next token is fixed beforehand: nothing is read back in this loop
-                s.num_computed = st + 1
-                s.output.append(int((s.seq_id * 7919 + i) % V))
+                s.cached = st + 1
+                s.generated.append(int((s.rid * 7919 + i) % V))
         eng.step()                      # builds the graph of this bucket
         for i in range(warmup - 1):
             one_step(i)
         torch.cuda.synchronize()
         launches0 = model.ops.launches
-        ctx0 = seqs[0].num_computed
+        ctx0 = seqs[0].cached
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
         for i in range(steps):

@@ -210,6 +210,20 @@ class CacheManager:
         self.computed.pop(req, None)
         self.states.release(req)
 
+    def reclaim(self, req: Hashable, n_tokens: int, victims) -> list[Hashable]:
+        """Frees requests out of `victims` (an iterable of request ids, taken in the order given) until `req` can be
+        backed for n_tokens or none is left. Returns the ids that were freed; whether it was enough is what
+        `can_ensure` says afterwards. A victim that holds nothing is passed over."""
+        freed = []
+        for v in victims:
+            if self.can_ensure(req, n_tokens):
+                break
+            if v == req or v not in self.computed:
+                continue
+            self.free(v)
+            freed.append(v)
+        return freed
+
     def reset(self) -> None:
         for req in list(self.computed):
             self.free(req)

@@ -6,7 +6,9 @@
 
 Engine options carry the names, meanings and defaults of the reference's `fusezap serve`
 (fusezap/serve/cli.py:8-41): --dtype auto|float32|bfloat16 (auto: bfloat16), --max-model-len 2048, --max-num-seqs 32,
---max-prefill-tokens, --num-blocks 1024, --block-size 16, --device; sampling options those of its `SamplingParams`
+--max-prefill-tokens, --num-blocks 1024, --block-size 16, --device, and the scheduler's own (--max-num-batched-tokens,
+--max-prefill-seqs, --mixed-prefill-tokens, --prefill-every, --prefill-first); they are generated from `EngineConfig`,
+which holds their defaults. Sampling options are those of the reference's `SamplingParams`
 (fusezap/serve/engine.py:39-50). The reference's text side (tokenizer, HTTP) is not part of this engine: prompts are
 token ids.
 """
@@ -33,21 +35,9 @@ def load_preset(name: str) -> dict:
 
 
 def add_engine_options(s: argparse.ArgumentParser) -> None:
-    s.add_argument("--device", default="cuda:0")
-    s.add_argument("--dtype", default="auto", choices=["auto", "float32", "bfloat16"], help="auto (default): bfloat16")
-    s.add_argument("--max-model-len", type=int, default=2048)
-    s.add_argument("--max-num-seqs", type=int, default=32, help="max concurrent requests (decode rows per step)")
-    s.add_argument("--max-prefill-tokens", type=int, default=None, help="prompt tokens per step (default 2048, at most max-model-len)")
-    s.add_argument("--num-blocks", type=int, default=1024, help="cache pages (shared by all requests)")
-    s.add_argument("--block-size", type=int, default=16, help="tokens per page")
-    s.add_argument("--max-num-batched-tokens", type=int, default=None,
-                   help="all tokens per step (default max-num-seqs + max-prefill-tokens)")
-    s.add_argument("--prefill-first", type=int, default=0,
-                   help="up to this many consecutive steps of prompt portions alone while others decode (default 0)")
-    s.add_argument("--no-cuda-graphs", action="store_true", help="launch every step kernel by kernel")
-    s.add_argument("--graph-rows", type=int, default=256,
-                   help="steps of at most this many rows that are not pure decode steps replay graphs captured by shape")
-    s.add_argument("--no-lookahead", action="store_true", help="read each decode step's tokens before launching the next")
+    """The engine's options: one flag per field of `EngineConfig`, which also holds their defaults and meanings."""
+    from .config import EngineConfig
+    EngineConfig.add_arguments(s)
 
 
 def build_parser() -> argparse.ArgumentParser:
@@ -86,25 +76,18 @@ def build_parser() -> argparse.ArgumentParser:
     return ap
 
 
-def resolve_dtype(name: str) -> str:
-    return "bfloat16" if name == "auto" else name
-
-
 def build_engine(a: argparse.Namespace):
+    from .config import EngineConfig
     from .engine.llm_engine import LLMEngine
-    from .engine.model import load_model, random_model
     if (a.model is None) == (a.random is None):
         raise SystemExit("give a model folder or --random PRESET (one of them)")
+    cfg = EngineConfig.from_arguments(a)
     if a.random is not None:
-        model = random_model(load_preset(a.random), resolve_dtype(a.dtype), a.device, seed=a.random_seed,
-                             max_len=a.max_model_len)
+        eng = LLMEngine.from_random(load_preset(a.random), seed=a.random_seed, config=cfg)
         a.model = f"random {a.random} (seed {a.random_seed})"
     else:
-        model = load_model(a.model, resolve_dtype(a.dtype), a.device, max_len=a.max_model_len)
-    return LLMEngine(model, num_blocks=a.num_blocks, block_size=a.block_size, max_num_seqs=a.max_num_seqs,
-                     max_prefill_tokens=a.max_prefill_tokens, max_model_len=a.max_model_len,
-                     max_num_batched_tokens=a.max_num_batched_tokens, prefill_first=a.prefill_first,
-                     cuda_graphs=not a.no_cuda_graphs, lookahead=not a.no_lookahead, graph_rows=a.graph_rows)
+        eng = LLMEngine.from_pretrained(a.model, config=cfg)
+    return eng
 
 
 def cmd_generate(a: argparse.Namespace) -> int:
@@ -112,7 +95,7 @@ def cmd_generate(a: argparse.Namespace) -> int:
     from .sampling import SamplingParams
     t0 = time.perf_counter()
     eng = build_engine(a)
-    print(f"fusezap_core_b200: loaded {a.model} on {a.device} ({resolve_dtype(a.dtype)}) in {time.perf_counter() - t0:.1f}s",
+    print(f"fusezap_core_b200: loaded {a.model} on {eng.cfg.device} ({eng.cfg.dtype}) in {time.perf_counter() - t0:.1f}s",
           file=sys.stderr, flush=True)
     prompts = [[int(t) for t in p.split(",") if t.strip()] for p in a.prompt_ids]
     if a.prompt_file:
@@ -142,6 +125,9 @@ def cmd_generate(a: argparse.Namespace) -> int:
                           "finish_reason": o.finish_reason}))
     n = sum(len(done[r].token_ids) for r in rids)
     print(f"fusezap_core_b200: {n} tokens in {dt:.2f}s ({n / dt:.1f} tok/s), {eng.stats}", file=sys.stderr, flush=True)
+    if eng.profile:
+        from .kernels.profile import format_report
+        print(format_report(eng.profile_report()), file=sys.stderr, flush=True)
     return 0
 
 

@@ -3,7 +3,7 @@
 The Python entry point, with the reference's names (fusezap/serve/engine.py:1-8, 366-369, 542-563, 750-763):
 
   model = load_model(path, dtype="bfloat16", device="cuda:0", max_len=4096)
-  eng = LLMEngine(model, num_blocks=1024, block_size=16, max_num_seqs=32)
+  eng = LLMEngine(model, num_blocks=1024, block_size=16, max_num_seqs=32)     # or LLMEngine(model, EngineConfig(...))
   rid = eng.add_request(prompt_ids, SamplingParams(max_tokens=64))
   while eng.has_unfinished():
       for out in eng.step():          # a RequestOutput per request that got a token (or finished) in this step
@@ -25,9 +25,11 @@ import numpy as np
 import torch
 
 from ..cache import CacheManager
+from ..config import EngineConfig
 from ..sampling import RequestSampler, SamplingParams
 from .model import DecoderModel
-from .scheduler import Scheduler, SchedulerConfig, SchedulerOutput, Sequence, SeqStatus
+from .request import Phase, Request
+from .scheduler import Scheduler, StepPlan
 from .step import Portion, StepRunner
 
 
@@ -52,28 +54,25 @@ class _Launched:
 
 
 class LLMEngine:
-    def __init__(self, model: DecoderModel, num_blocks: int = 1024, block_size: int = 16, max_num_seqs: int = 32,
-                 max_prefill_tokens: int | None = None, max_model_len: int | None = None,
-                 max_num_batched_tokens: int | None = None, prefill_first: int = 0, cuda_graphs: bool = True, lookahead: bool = True,
-                 graph_rows: int = 256):
-        self.model = model
-        self.max_model_len = int(max_model_len or model.max_len)
-        if self.max_model_len > model.max_len:
-            raise ValueError(f"max_model_len {self.max_model_len} exceeds the length the model was loaded for ({model.max_len})")
-        max_prefill_tokens = int(max_prefill_tokens or min(2048, self.max_model_len))
-        self.cfg = SchedulerConfig(max_num_seqs, max_prefill_tokens, max_num_batched_tokens, prefill_first)
+    def __init__(self, model: DecoderModel, config: EngineConfig | None = None, **options):
+        """`config`: the engine's options (`EngineConfig`); or give them as keywords (`num_blocks=..., block_size=...,
+        max_num_seqs=..., max_prefill_tokens=..., max_model_len=...`, the reference's argument names), not both."""
+        if config is not None and options:
+            raise TypeError("give either an EngineConfig or options as keywords, not both")
+        cfg = (config or EngineConfig(**options)).resolved(model.max_len)
+        self.model, self.cfg = model, cfg
+        self.max_model_len = cfg.max_model_len
         dev = model.device
-        self.cache = CacheManager(model.cache_needs(), model.state_needs(), block_size, num_blocks, max_num_seqs,
+        R = cfg.max_num_seqs
+        self.cache = CacheManager(model.cache_needs(), model.state_needs(), cfg.block_size, cfg.num_blocks, R,
                                   self.max_model_len, model.ops.dtype, dev)
-        self.scheduler = Scheduler(self.cfg, self.cache)
-        rows = self.cfg.token_budget
-        self.runner = StepRunner(model, self.cache, max_rows=rows, max_wanted=max_num_seqs, max_segments=max_num_seqs)
+        self.scheduler = Scheduler(cfg, self.cache)
+        self.runner = StepRunner(model, self.cache, max_rows=cfg.token_budget, max_wanted=R, max_segments=R)
         self.ops = model.ops
         self.stop_ids = set(model.spec.eos_token_ids)
-        self.seqs: dict[int, Sequence] = {}
-        self._ids, self._arrival = itertools.count(), itertools.count()
+        self.requests: dict[int, Request] = {}
+        self._next_id, self._clock = itertools.count(), itertools.count()
         pin = dev.type == "cuda"
-        R = max_num_seqs
         # per-step sampling inputs and outputs: pinned on the host, fixed buffers on the device
         # (two of each host buffer: a step may be launched while the one before it is still in flight)
         self._temp_h = torch.zeros(2, R, dtype=torch.float32, pin_memory=pin)
@@ -84,19 +83,20 @@ class LLMEngine:
         self._events = [torch.cuda.Event() for _ in range(2)] if pin else None
         self._slot = 0
         self._pending: _Launched | None = None
-        self.lookahead = bool(lookahead)
+        self.profile = bool(cfg.profile) and pin and hasattr(model.ops, "start_profile")
+        self.lookahead = bool(cfg.lookahead) and not self.profile
         self._temp_d = torch.zeros(R, dtype=torch.float32, device=dev)
         self._unif_d = torch.zeros(R, dtype=torch.float64, device=dev)
         self._topk_d = torch.zeros(R, dtype=torch.int32, device=dev)
         self._topp_d = torch.ones(R, dtype=torch.float32, device=dev)
         self._ids_d = torch.zeros(R, dtype=torch.int32, device=dev)
         self.runner.prev_ids = self._ids_d
-        self.cuda_graphs = bool(cuda_graphs) and pin and model.graph_safe()
+        self.cuda_graphs = bool(cfg.cuda_graphs) and pin and model.graph_safe() and not self.profile
         # Captured steps. Decode steps: by (padded row count, how the tokens are chosen). Other steps of at most
         # `graph_rows` rows (portions of prompts, with or without decoded tokens beside them) are bound by the host's
         # launches, not by the GPU: they are captured too, by the sizes that fix their launches, the second time such
         # a step comes up (all else a step depends on lies in device memory at fixed addresses).
-        self.graph_rows = int(graph_rows)
+        self.graph_rows = cfg.graph_rows
         self._step_seen: dict[tuple, int] = {}
         self._step_keys: list[tuple] = []                        # captured non-decode steps, oldest first
         self._graphs: dict[tuple, torch.cuda.CUDAGraph] = {}     # key -> captured step
@@ -104,68 +104,85 @@ class LLMEngine:
         self._greedy_step = True
         self._ids_only = False
         self._filtered_step = False
-        self._buckets = sorted({min(1 << i, R) for i in range(R.bit_length() + 1)})
+        # row counts of the captured decode steps: powers of two, none above what a step can hold
+        most = min(R, cfg.token_budget)
+        self._buckets = sorted({min(1 << i, most) for i in range(most.bit_length() + 1)})
         self.stats = {"steps": 0, "decode_steps": 0, "prefill_steps": 0, "mixed_steps": 0, "tokens": 0,
                       "preemptions": 0, "graph_replays": 0, "step_graph_replays": 0, "lookahead_steps": 0, "h2d_bytes": 0, "d2h_bytes": 0}
+        if self.profile:
+            model.ops.start_profile()
 
     # ---- a model and its engine in one call
     @classmethod
-    def from_pretrained(cls, path: str, dtype: str = "bfloat16", device: str = "cuda:0", max_model_len: int = 2048,
-                        ops=None, **engine_options) -> "LLMEngine":
-        """`load_model(path, dtype, device, max_len=max_model_len)` and an engine over it; `engine_options` are the
-        constructor's (num_blocks, block_size, max_num_seqs, ...)."""
+    def from_pretrained(cls, path: str, dtype: str | None = None, device: str | None = None,
+                        max_model_len: int | None = None, ops=None, config: EngineConfig | None = None,
+                        **options) -> "LLMEngine":
+        """`load_model(path, dtype, device, max_len=max_model_len)` and an engine over it. The options are
+        `EngineConfig`'s, given as one object or as keywords (dtype, device, max_model_len, num_blocks, ...)."""
         from .model import load_model
-        model = load_model(path, dtype, device, max_len=max_model_len, ops=ops)
-        return cls(model, max_model_len=max_model_len, **engine_options)
+        cfg = _config_from(config, dtype, device, max_model_len, options)
+        model = load_model(path, cfg.dtype, cfg.device, max_len=cfg.max_model_len, ops=ops)
+        return cls(model, cfg)
 
     @classmethod
-    def from_random(cls, config: dict | str, seed: int = 0, dtype: str = "bfloat16", device: str = "cuda:0",
-                    max_model_len: int = 2048, ops=None, **engine_options) -> "LLMEngine":
-        """An engine over a model with seeded random weights drawn on the device. `config`: a config.json dictionary, or
-        the name of a preset of this package (`tiny-llama`, `llama-3.1-8b`, ...)."""
+    def from_random(cls, config_json: dict | str, seed: int = 0, dtype: str | None = None, device: str | None = None,
+                    max_model_len: int | None = None, ops=None, config: EngineConfig | None = None,
+                    **options) -> "LLMEngine":
+        """An engine over a model with seeded random weights drawn on the device. `config_json`: a config.json
+        dictionary, or the name of a preset of this package (`tiny-llama`, `llama-3.1-8b`, ...)."""
         from .model import random_model
-        if isinstance(config, str):
+        if isinstance(config_json, str):
             from ..cli import load_preset
-            config = load_preset(config)
-        model = random_model(config, dtype, device, seed=seed, max_len=max_model_len, ops=ops)
-        return cls(model, max_model_len=max_model_len, **engine_options)
+            config_json = load_preset(config_json)
+        cfg = _config_from(config, dtype, device, max_model_len, options)
+        model = random_model(config_json, cfg.dtype, cfg.device, seed=seed, max_len=cfg.max_model_len, ops=ops)
+        return cls(model, cfg)
 
     # ---- requests
     def add_request(self, prompt_ids: Seq[int], params: SamplingParams | None = None, request_id: int | None = None) -> int:
-        params = params or SamplingParams()
-        rid = next(self._ids) if request_id is None else request_id
-        if rid in self.seqs:
-            raise ValueError(f"request id {rid} is in use")
-        if len(prompt_ids) + params.max_tokens > self.max_model_len:
-            raise ValueError(f"prompt ({len(prompt_ids)}) + max_tokens ({params.max_tokens}) exceeds max_model_len {self.max_model_len}")
-        vocab = self.model.spec.vocab_size
+        """Queues a prompt (token ids); returns the request's id. Refuses an id in use, a prompt that cannot fit with
+        its `max_tokens`, and token ids outside the vocabulary."""
+        if params is None:
+            params = SamplingParams()
+        if request_id is None:
+            request_id = next(self._next_id)
+            while request_id in self.requests:
+                request_id = next(self._next_id)
+        elif request_id in self.requests:
+            raise ValueError(f"request id {request_id} is in use")
         prompt = [int(t) for t in prompt_ids]
-        if any(t < 0 or t >= vocab for t in prompt):
+        room = self.max_model_len - len(prompt)
+        if params.max_tokens > room:
+            raise ValueError(f"prompt ({len(prompt)}) + max_tokens ({params.max_tokens}) exceeds max_model_len {self.max_model_len}")
+        vocab = self.model.spec.vocab_size
+        if prompt and not 0 <= min(prompt) <= max(prompt) < vocab:
             raise ValueError(f"a prompt token lies outside the vocabulary of {vocab}")
-        seq = Sequence(rid, prompt, params, arrival=next(self._arrival))
-        seq.sampler = RequestSampler(params)
-        self.scheduler.add(seq, params.max_tokens)
-        self.seqs[rid] = seq
-        return rid
+        req = Request(request_id, prompt, params, order=next(self._clock), sampler=RequestSampler(params))
+        self.scheduler.submit(req)
+        self.requests[request_id] = req
+        return request_id
 
     def abort(self, request_id: int) -> RequestOutput | None:
-        seq = self.seqs.get(request_id)
-        if seq is None or seq.status == SeqStatus.FINISHED:
+        """Ends a request now; None if it is unknown or has ended."""
+        req = self.requests.get(request_id)
+        if req is None or req.phase is Phase.DONE:
             return None
-        self.scheduler.finish(seq, "abort")
-        return self._out(seq, [])
+        self.scheduler.retire(req, "abort")
+        return self._report(req, ())
 
     def has_unfinished(self) -> bool:
         return self.scheduler.has_unfinished()
 
     def release(self, request_id: int) -> None:
-        s = self.seqs.get(request_id)
-        if s is not None and s.status == SeqStatus.FINISHED:
-            del self.seqs[request_id]
+        """Forgets a request that has ended (until then its tokens stay readable in `requests`)."""
+        req = self.requests.get(request_id)
+        if req is not None and req.phase is Phase.DONE:
+            self.requests.pop(request_id)
 
-    def _out(self, seq: Sequence, new: list[int]) -> RequestOutput:
-        return RequestOutput(seq.seq_id, new, list(seq.output), seq.status == SeqStatus.FINISHED, seq.finish_reason,
-                             len(seq.prompt))
+    def _report(self, req: Request, new_tokens) -> RequestOutput:
+        return RequestOutput(request_id=req.rid, new_token_ids=list(new_tokens), token_ids=list(req.generated),
+                             finished=req.phase is Phase.DONE, finish_reason=req.ended_by,
+                             num_prompt_tokens=len(req.prompt))
 
     # ---- one step
     def step(self) -> list[RequestOutput]:
@@ -173,22 +190,34 @@ class LLMEngine:
         whenever it is certain what it holds (see `_speculate`), so the device never waits for the host between
         decode steps."""
         cur, self._pending = self._pending, None
-        if cur is not None and not any(s.status == SeqStatus.RUNNING for s, _ in cur.rows):
+        if cur is not None and all(r.phase is not Phase.LIVE for r, _ in cur.rows):
             cur = None            # launched ahead for requests that have all ended since: nothing to read from it
         if cur is None:
-            so = self.scheduler.schedule()
-            self.stats["preemptions"] += len(so.preempted)
-            if so.empty:
+            plan = self.scheduler.plan()
+            self.stats["preemptions"] += len(plan.evicted)
+            if plan.empty:
                 return []
-            portions, owners = self._portions(so)
-            rows = [(s, i) for i, s in enumerate(s for s, p in zip(owners, portions) if p.want)]
-            kind = "decode_steps" if not so.prefill else "prefill_steps" if not so.decode else "mixed_steps"
-            cur = self._launch(portions, rows, decode_only=not so.prefill,
-                               all_produce=len(rows) == len(self.scheduler.running), kind=kind)
+            portions, rows = self._portions(plan)
+            n_decode = sum(1 for w in plan.work if w.decode)
+            kind = "decode_steps" if n_decode == len(plan.work) else "mixed_steps" if n_decode else "prefill_steps"
+            cur = self._launch(portions, rows, decode_only=n_decode == len(plan.work),
+                               all_produce=len(rows) == len(self.scheduler.live), kind=kind)
         nxt = self._speculate(cur) if self.lookahead else None
         outs = self._complete(cur)
         self._pending = nxt
         return outs
+
+    def _portions(self, plan: StepPlan) -> tuple[list[Portion], list[tuple[Request, int]]]:
+        """The plan as the step function's portions, and (request, index among the step's chosen ids) for every
+        request that gets a token from it: a request whose share reaches the end of what it knows."""
+        portions, rows = [], []
+        for w in plan.work:
+            req, end = w.request, w.start + w.count
+            last = end == req.known
+            portions.append(Portion(req.rid, req.span(w.start, end), [w.count - 1] if last else []))
+            if last:
+                rows.append((req, len(rows)))
+        return portions, rows
 
     def _speculate(self, cur: "_Launched") -> "_Launched | None":
         """Launches the decode step that follows `cur` before cur's tokens are known to the host: each row takes its
@@ -197,32 +226,32 @@ class LLMEngine:
         that cur ends by length is left out; one that cur ends by a stop token runs one token too many, which
         `_complete` drops (its pages are given back in stream order, so nobody reads what it wrote)."""
         sch, cache = self.scheduler, self.cache
-        if sch.waiting or not cur.all_produce or not cur.rows:
+        if sch.queue or not cur.all_produce or not cur.rows:
             return None
         rows = []
-        for seq, i in cur.rows:
-            p = seq.params
-            if seq.status != SeqStatus.RUNNING or not p.on_device:
+        for req, i in cur.rows:
+            p = req.params
+            if req.phase is not Phase.LIVE or not p.on_device:
                 return None
-            if len(seq.output) + 1 >= p.max_tokens or seq.num_tokens + 1 >= self.max_model_len:
+            if len(req.generated) + 1 >= p.max_tokens or req.known + 1 >= self.max_model_len:
                 continue
-            rows.append((seq, i))
+            rows.append((req, i))
         if not rows or len(rows) > self.cfg.token_budget:
             return None
         # the pages of all rows together: count them before taking any
         need = [0] * len(cache.groups)
-        for seq, _ in rows:
-            for g, n in enumerate(cache.pages_needed(seq.seq_id, seq.num_computed + 1)):
+        for req, _ in rows:
+            for g, n in enumerate(cache.pages_needed(req.rid, req.cached + 1)):
                 need[g] += n
         if any(n > g.allocator.num_free for n, g in zip(need, cache.groups)):
             return None
         portions = []
-        for seq, i in rows:
-            cache.ensure(seq.seq_id, seq.num_computed + 1)
-            portions.append(Portion(seq.seq_id, [0], [0], src=i))
+        for req, i in rows:
+            cache.ensure(req.rid, req.cached + 1)
+            portions.append(Portion(req.rid, [0], [0], src=i))
         sch.steps += 1
         self.stats["lookahead_steps"] += 1
-        return self._launch(portions, [(s, j) for j, (s, _) in enumerate(rows)], decode_only=True, all_produce=True)
+        return self._launch(portions, [(r, j) for j, (r, _) in enumerate(rows)], decode_only=True, all_produce=True)
 
     def _complete(self, cur: "_Launched") -> list[RequestOutput]:
         st = self.stats
@@ -231,28 +260,17 @@ class LLMEngine:
         self.ops.check_errors(copied=True)
         ids = self._ids_h[cur.slot].numpy()
         outs = []
-        for seq, i in cur.rows:
-            if seq.status != SeqStatus.RUNNING:        # aborted meanwhile, or ended by the step before
+        for req, i in cur.rows:
+            if req.phase is not Phase.LIVE:        # aborted meanwhile, or ended by the step before
                 continue
-            if seq.params.on_device:
+            if req.params.on_device:
                 tok = int(ids[i])
             else:
                 row = cur.logits[i].detach().to("cpu", torch.float32).numpy()
                 st["d2h_bytes"] += row.nbytes
-                tok = seq.sampler.host_choice(row, seq.tokens)
-            outs.append(self._emit(seq, tok))
+                tok = req.sampler.host_choice(row, req.history)
+            outs.append(self._take(req, tok))
         return outs
-
-    def _portions(self, so: SchedulerOutput) -> tuple[list[Portion], list[Sequence]]:
-        portions, owners = [], []
-        for seq in so.decode:
-            portions.append(Portion(seq.seq_id, [seq.token_at(seq.num_computed)], [0]))
-            owners.append(seq)
-        for seq, start, n in so.prefill:
-            toks = seq.tokens_between(start, start + n)
-            portions.append(Portion(seq.seq_id, toks, [n - 1] if start + n == seq.num_tokens else []))
-            owners.append(seq)
-        return portions, owners
 
     def _launch(self, portions, rows, decode_only: bool, all_produce: bool, kind: str = "decode_steps") -> "_Launched":
         """Puts one step on the stream: metadata and sampling inputs up, the model's step, the choice of tokens, the
@@ -262,11 +280,11 @@ class LLMEngine:
         temp_h, unif_h, topk_h, topp_h = self._temp_h[slot], self._unif_h[slot], self._topk_h[slot], self._topp_h[slot]
         R = len(rows)
         filtered = False
-        for seq, i in rows:
-            p = seq.params
+        for req, i in rows:
+            p = req.params
             device_row = p.on_device and not p.greedy
             temp_h[i] = p.temperature if device_row else 0.0
-            unif_h[i] = seq.sampler.next_uniform() if device_row else 0.0
+            unif_h[i] = req.sampler.next_uniform() if device_row else 0.0
             topk_h[i] = p.top_k if device_row else 0
             topp_h[i] = p.top_p if device_row else 1.0
             filtered = filtered or (device_row and p.filtered)
@@ -307,16 +325,16 @@ class LLMEngine:
         if key is not None:
             g = self._graphs.get(key)
             if g is None:
-                # warm-up (builds, sets kernel attributes, sizes the buffers) on a copy of the ids the step may read
-                keep = self._ids_d.clone()
-                self._eager(n_w)
-                torch.cuda.synchronize()
-                self._ids_d.copy_(keep)
+                # The first step of this shape runs kernel by kernel (which also builds what it needs, sets kernel
+                # attributes and sizes the buffers) and is then recorded for the next one; recording launches nothing,
+                # so the step runs exactly once (a part that updates per-request state in place is not advanced twice).
+                logits = self._eager(n_w)
                 g = torch.cuda.CUDAGraph()
                 before = ops.launches
                 with torch.cuda.graph(g):
                     self._eager(n_w)
                 self.launches_per_graph[key] = ops.launches - before
+                ops.launches = before
                 self._graphs[key] = g
                 if key[0] == "step":
                     self._step_keys.append(key)
@@ -324,18 +342,19 @@ class LLMEngine:
                         torch.cuda.synchronize()
                         old = self._step_keys.pop(0)
                         del self._graphs[old], self.launches_per_graph[old]
-            g.replay()
-            ops.launches += self.launches_per_graph[key]
-            st["graph_replays"] += 1
-            if key[0] == "step":
-                st["step_graph_replays"] += 1
-            logits = None if self._ids_only else runner.ws.get("logits", (n_w, self.model.spec.vocab_size), torch.float32)
+            else:
+                g.replay()
+                ops.launches += self.launches_per_graph[key]
+                st["graph_replays"] += 1
+                if key[0] == "step":
+                    st["step_graph_replays"] += 1
+                logits = None if self._ids_only else runner.ws.get("logits", (n_w, self.model.spec.vocab_size), torch.float32)
         else:
             logits = self._eager(n_w)
         runner.commit(portions, starts)
         n_tokens = 0
         for p, s in zip(portions, starts):
-            self.seqs[p.req].num_computed = s + len(p.tokens)
+            self.requests[p.req].cached = s + len(p.tokens)
             n_tokens += len(p.tokens)
         if n_w:
             self._ids_h[slot][:n_w].copy_(self._ids_d[:n_w], non_blocking=True)
@@ -366,28 +385,57 @@ class LLMEngine:
             self.ops.sample(logits, self._temp_d[:n_wanted], self._unif_d[:n_wanted], self._ids_d[:n_wanted])
         return logits
 
-    def _emit(self, s: Sequence, tok: int) -> RequestOutput:
-        s.output.append(tok)
-        p = s.params
-        if (not p.ignore_eos and tok in self.stop_ids) or tok in p.stop_token_ids:
-            self.scheduler.finish(s, "stop")
-        elif len(s.output) >= p.max_tokens or s.num_tokens >= self.max_model_len:
-            self.scheduler.finish(s, "length")
-        return self._out(s, [tok])
+    def _take(self, req: Request, tok: int) -> RequestOutput:
+        """The request's next token has been chosen: keep it, and end the request if this token or its count says so."""
+        req.generated.append(tok)
+        p = req.params
+        stops = tok in p.stop_token_ids or (tok in self.stop_ids and not p.ignore_eos)
+        if stops:
+            self.scheduler.retire(req, "stop")
+        elif len(req.generated) >= p.max_tokens or req.known >= self.max_model_len:
+            self.scheduler.retire(req, "length")
+        return self._report(req, (tok,))
 
     # ---- convenience
     def generate(self, prompts: Iterable[Seq[int]], params: SamplingParams | Seq[SamplingParams] | None = None,
                  max_steps: int | None = None) -> list[list[int]]:
+        """Runs the prompts to their ends; returns each one's new tokens, in the order of `prompts`. `params`: one for
+        all, or one per prompt."""
         prompts = list(prompts)
-        ps = list(params) if isinstance(params, (list, tuple)) else [params or SamplingParams()] * len(prompts)
-        rids = [self.add_request(p, q) for p, q in zip(prompts, ps)]
-        n = 0
-        while any(self.seqs[r].status != SeqStatus.FINISHED for r in rids):
-            self.step()
-            n += 1
-            if max_steps is not None and n > max_steps:
+        if isinstance(params, (list, tuple)):
+            each = list(params)
+            if len(each) != len(prompts):
+                raise ValueError(f"{len(prompts)} prompts but {len(each)} sampling params")
+        else:
+            each = [params if params is not None else SamplingParams()] * len(prompts)
+        mine = [self.requests[self.add_request(p, q)] for p, q in zip(prompts, each)]
+        steps = 0
+        while not all(r.phase is Phase.DONE for r in mine):
+            if max_steps is not None and steps >= max_steps:
                 raise RuntimeError(f"not finished after {max_steps} steps")
-        res = [list(self.seqs[r].output) for r in rids]
-        for r in rids:
-            self.release(r)
-        return res
+            self.step()
+            steps += 1
+        for r in mine:
+            self.release(r.rid)
+        return [list(r.generated) for r in mine]
+
+    def profile_report(self) -> dict:
+        """With `profile` on: per kernel class the launches and device time since the engine was made."""
+        if not self.profile:
+            raise RuntimeError("the engine was made without profile=True")
+        return self.ops.profile_report()
+
+
+def _config_from(config: EngineConfig | None, dtype, device, max_model_len, options: dict) -> EngineConfig:
+    from ..config.engine_config import DEFAULT_MODEL_LEN
+    given = {k: v for k, v in (("dtype", dtype), ("device", device), ("max_model_len", max_model_len)) if v is not None}
+    if config is not None:
+        if options or given:
+            raise TypeError("give either an EngineConfig or options as keywords, not both")
+        cfg = config
+    else:
+        cfg = EngineConfig(**given, **options)
+    if cfg.max_model_len is None:
+        import dataclasses
+        cfg = dataclasses.replace(cfg, max_model_len=DEFAULT_MODEL_LEN)
+    return cfg

@@ -123,7 +123,7 @@ class DecoderModel:
             raise ValueError(f"prompt ({len(prompt_ids)}) + max_tokens ({params.max_tokens}) exceeds the length the model "
                              f"was loaded for ({self.max_len})")
         eng = LLMEngine(self, num_blocks=-(-need // block_size) + 1, block_size=block_size, max_num_seqs=1,
-                        max_prefill_tokens=min(2048, self.max_len), max_model_len=self.max_len)
+                        max_model_len=self.max_len)
         return eng.generate([prompt_ids], params)[0]
 
     def weight_bytes(self) -> int:

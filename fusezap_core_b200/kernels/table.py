@@ -56,12 +56,26 @@ class CudaOps(Ops):
         self.fuse_swiglu = True            # gate/up product and SwiGLU in one kernel where the sizes allow it
         self.fuse_argmax = True            # lm_head product and argmax in one pass where no logits are asked for
         self.fuse_rope = True              # q/k/v product, rotation and cache write in one kernel (few-token steps)
+        self._profile = None               # a StepProfile while the engine profiles its steps
 
     # ---- plumbing
     def begin_step(self) -> None:
         """Called by the step function before it launches anything: the kernels of the step all go to the stream that
         is current now (asked for once; it changes when a graph is captured or a caller switches streams)."""
         self._stream_handle = c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+        if self._profile is not None:
+            self._profile.begin_step()
+
+    def start_profile(self) -> None:
+        """From now on a CUDA event is recorded after every launch (see kernels/profile.py)."""
+        from .profile import StepProfile
+        self._profile = StepProfile(lambda: torch.cuda.Event(enable_timing=True))
+
+    def profile_report(self) -> dict:
+        if self._profile is None:
+            raise KernelError("start_profile() was not called")
+        self._profile.collect(lambda: torch.cuda.synchronize(self.device))
+        return self._profile.report()
 
     def end_step(self) -> None:
         self._stream_handle = None
@@ -82,11 +96,13 @@ class CudaOps(Ops):
             self._scratch_bufs[name] = buf
         return buf
 
-    def _check(self, status: int, what: str) -> None:
+    def _check(self, status: int, what: str, ideal_bytes: int = 0) -> None:
         self.launches += 1
         if status != 0:
             why = _STATUS.get(status, f"CUDA error {status}")
             raise KernelError(f"{what}: {why}")
+        if self._profile is not None:
+            self._profile.note(what, ideal_bytes)
 
     def _want(self, t: torch.Tensor, name: str, dtypes: tuple, dims: int | None = None) -> None:
         if not t.is_cuda:

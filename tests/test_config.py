@@ -102,10 +102,36 @@ def test_schedule_validation():
 def test_engine_config():
     e = EngineConfig(max_num_seqs=8, max_prefill_tokens=64)
     assert e.token_budget == 72 and EngineConfig(max_num_batched_tokens=100).token_budget == 100
-    for bad in (dict(dtype="float16"), dict(block_size=0), dict(num_blocks=-1), dict(prefill_first=-1), dict(graph_rows=-1)):
+    for bad in (dict(dtype="float16"), dict(block_size=0), dict(num_blocks=-1), dict(prefill_first=-1), dict(graph_rows=-1),
+                dict(prefill_every=0), dict(max_prefill_seqs=0), dict(mixed_prefill_tokens=-3), dict(max_model_len=0)):
         with pytest.raises(ValueError):
             EngineConfig(**bad)
     assert EngineConfig().graph_rows == 256 and EngineConfig(graph_rows=0).graph_rows == 0
+    assert EngineConfig(dtype="auto").dtype == "bfloat16"
+    r = EngineConfig(max_num_seqs=4).resolved(model_max_len=512)
+    assert (r.max_model_len, r.max_prefill_tokens, r.max_prefill_seqs) == (512, 512, 4)
+    assert EngineConfig().resolved(8192).max_prefill_tokens == 2048
+    with pytest.raises(ValueError, match="exceeds the length"):
+        EngineConfig(max_model_len=1024).resolved(512)
+
+
+def test_the_command_line_is_generated_from_the_engine_config():
+    """One source of defaults: a flag that is not given leaves the field at `EngineConfig`'s own default, every field
+    that names a flag has one, and the engine, the scheduler and the command line read the same object."""
+    import dataclasses
+    from fusezap_core_b200.cli import build_parser
+    ap = build_parser()
+    a = ap.parse_args(["generate", "--random", "tiny-llama", "--prompt-ids", "1,2"])
+    assert EngineConfig.from_arguments(a) == EngineConfig()
+    a = ap.parse_args(["generate", "--random", "tiny-llama", "--max-num-seqs", "3", "--prefill-first", "2", "--no-lookahead",
+                       "--max-num-batched-tokens", "24", "--mixed-prefill-tokens", "5", "--prefill-every", "2",
+                       "--max-prefill-seqs", "1", "--dtype", "float32", "--block-size", "8", "--profile"])
+    c = EngineConfig.from_arguments(a)
+    assert (c.max_num_seqs, c.prefill_first, c.lookahead, c.max_num_batched_tokens, c.mixed_prefill_tokens, c.prefill_every,
+            c.max_prefill_seqs, c.dtype, c.block_size, c.profile, c.cuda_graphs) == (3, 2, False, 24, 5, 2, 1, "float32", 8, True, True)
+    flags = {x for act in ap._subparsers._group_actions[0].choices["generate"]._actions for x in act.option_strings}
+    for f in dataclasses.fields(EngineConfig):
+        assert f.metadata["flag"] in flags, f.name
 
 
 def test_sampling_params_say_who_picks_the_token():

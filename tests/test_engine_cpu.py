@@ -229,3 +229,38 @@ def test_launching_ahead_under_random_traffic(models, seed):
     assert res[True][1] > 0 and res[False][1] == 0
     if seed == 0:
         assert res[True][2] > 0 and res[False][2] > 0, "this seed is meant to run out of pages"
+
+
+@pytest.mark.parametrize("knobs", [dict(prefill_first=2), dict(max_num_batched_tokens=6), dict(mixed_prefill_tokens=3),
+                                   dict(prefill_every=2), dict(max_prefill_seqs=1),
+                                   dict(prefill_first=1, max_num_batched_tokens=9, max_prefill_seqs=2)])
+def test_scheduler_options_change_the_steps_not_the_tokens(models, knobs):
+    """Every scheduling option cuts the same work into other steps; each request's tokens stay the same, also with so
+    few pages that requests are evicted and recomputed."""
+    model, cfg, opts, w = models["tiny_qwen2"]
+    P = prompts(cfg, (1, 7, 23, 40), seed=2)
+    params = SamplingParams(max_tokens=12, ignore_eos=True)
+    base = dict(num_blocks=64, block_size=opts["page_size"], max_num_seqs=4, max_prefill_tokens=8, max_model_len=128)
+    plain = LLMEngine(model, **base)
+    ref = plain.generate(P, params)
+    eng = LLMEngine(model, **base, **knobs)
+    assert eng.generate(P, params) == ref
+    assert eng.stats["steps"] != plain.stats["steps"] or eng.stats["mixed_steps"] != plain.stats["mixed_steps"]
+    if "prefill_first" in knobs:
+        assert eng.scheduler.steps_held_back > 0
+    few = LLMEngine(model, **dict(base, num_blocks=-(-52 // opts["page_size"]) + 1), **knobs)
+    assert few.generate(P, params) == ref and few.stats["preemptions"] > 0 and few.cache.num_free_pages == few.cache.num_pages
+
+
+def test_engine_takes_one_config_object(models):
+    from fusezap_core_b200 import EngineConfig
+    model, cfg, opts, w = models["tiny_llama"]
+    c = EngineConfig(num_blocks=32, block_size=4, max_num_seqs=3, max_model_len=64, prefill_first=1)
+    eng = LLMEngine(model, c)
+    assert eng.cfg.max_prefill_tokens == 64 and eng.scheduler.cfg is eng.cfg and eng.cache.page_size == 4
+    with pytest.raises(TypeError, match="not both"):
+        LLMEngine(model, c, num_blocks=8)
+    with pytest.raises(ValueError, match="exceeds the length"):
+        LLMEngine(model, max_model_len=100000)
+    with pytest.raises(TypeError):
+        LLMEngine(model, no_such_option=1)
