@@ -2,7 +2,7 @@
 
   from fusezap_core_b200 import load_model, LLMEngine, SamplingParams
 """
-__version__ = "0.1.0"
+__version__ = "0.2.0"
 
 from .engine.model import load_model, DecoderModel
 from .engine.llm_engine import LLMEngine, RequestOutput

@@ -27,12 +27,15 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: how its parts are arranged (`block`), and the parts. `prefix` is the layer's tensor-name prefix."""
+    """One layer: how its parts are arranged (`block`), and the parts. `prefix` is the layer's tensor-name prefix.
+    Norms belong to the block: it decides how many it has, where they stand and what they are called, and its params
+    may name a spec for each (any number, any kinds). `norm` is only the kind a block falls back on for a norm that its
+    params leave open; a layer whose block names all its norms needs none."""
     prefix: str
     block: PartSpec
     mixer: PartSpec
     ffn: PartSpec
-    norm: PartSpec  # the norm kind used by the block (the block decides how many norms it has and their names)
+    norm: PartSpec | None = None
 
 
 @dataclass(frozen=True)
@@ -61,6 +64,9 @@ class ModelSpec:
     max_position: int
     eos_token_ids: tuple[int, ...] = ()
     bos_token_id: int | None = None
+    embed_scale: float | None = None          # embeddings are multiplied by this (in float32) as they are gathered
+    logit_transform: PartSpec | None = None   # a part (kind in the logit-transform registry) applied to the float32
+                                              # logits of the wanted rows, in place, before anything reads them
 
     def validate(self) -> None:
         if self.hidden_size <= 0 or self.vocab_size <= 0:

@@ -10,10 +10,11 @@
 
 // ------------------------------------------------------------------------------------------------ embedding
 // src (may be null): src[n] >= 0 takes the row's token from prev_ids[src[n]] (the ids the previous step chose, still on
-// the device) instead of tokens[n].
+// the device) instead of tokens[n]. scale: every value is multiplied by it in float32 (1 for the models that do not
+// scale their embeddings: the product is then exact).
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tokens, const int* __restrict__ src,
-                             const int* __restrict__ prev_ids, float* __restrict__ x, int D, int V, int* err) {
+                             const int* __restrict__ prev_ids, float* __restrict__ x, int D, int V, float scale, int* err) {
   fz_grid_launch_dependents();
   fz_grid_wait();
   const int n = blockIdx.x;
@@ -34,22 +35,22 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
       const T* v = (const T*)&raw;
       float f[PER];
 #pragma unroll
-      for (int i = 0; i < PER; ++i) f[i] = Cvt<T>::to_f(v[i]);
+      for (int i = 0; i < PER; ++i) f[i] = __fmul_rn(Cvt<T>::to_f(v[i]), scale);
 #pragma unroll
       for (int i = 0; i < PER; i += 4) *(float4*)(xr + d + i) = make_float4(f[i], f[i + 1], f[i + 2], f[i + 3]);
     }
     return;
   }
-  for (int d = threadIdx.x; d < D; d += blockDim.x) xr[d] = Cvt<T>::to_f(tr[d]);
+  for (int d = threadIdx.x; d < D; d += blockDim.x) xr[d] = __fmul_rn(Cvt<T>::to_f(tr[d]), scale);
 }
 
 FZ_API int fz_embed(const void* table, int table_dtype, const int* tokens, const int* src, const int* prev_ids, float* x,
-                    int N, int D, int V, int* err, cudaStream_t stream) {
+                    int N, int D, int V, float scale, int* err, cudaStream_t stream) {
   if (N <= 0) return FZ_OK;
   if (table_dtype == FZ_F32)
-    fz_launch(embed_kernel<float>, dim3(N), dim3(512), 0, stream, (const float*)table, tokens, src, prev_ids, x, D, V, err);
+    fz_launch(embed_kernel<float>, dim3(N), dim3(512), 0, stream, (const float*)table, tokens, src, prev_ids, x, D, V, scale, err);
   else if (table_dtype == FZ_BF16)
-    fz_launch(embed_kernel<__nv_bfloat16>, dim3(N), dim3(512), 0, stream, (const __nv_bfloat16*)table, tokens, src, prev_ids, x, D, V, err);
+    fz_launch(embed_kernel<__nv_bfloat16>, dim3(N), dim3(512), 0, stream, (const __nv_bfloat16*)table, tokens, src, prev_ids, x, D, V, scale, err);
   else
     return FZ_BAD_DTYPE;
   FZ_LAUNCH_CHECK();
@@ -516,7 +517,12 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int* __restrict_
 
 // scratch: float partial_val[R * S], int partial_idx[R * S], int counters[R] (zero before the first call; the kernel
 // leaves them zero). S = fz_argmax_slices(V).
-FZ_API int fz_argmax_slices(int V) { const int s = (V + 8191) / 8192; return s < 1 ? 1 : (s > 64 ? 64 : s); }
+constexpr int FZ_ARGMAX_MAX_SLICES = 64;
+FZ_API int fz_argmax_max_slices(void) { return FZ_ARGMAX_MAX_SLICES; }
+FZ_API int fz_argmax_slices(int V) {
+  const int s = (V + 8191) / 8192;
+  return s < 1 ? 1 : (s > FZ_ARGMAX_MAX_SLICES ? FZ_ARGMAX_MAX_SLICES : s);
+}
 
 FZ_API int fz_argmax(const float* logits, int* out, int R, int V, float* partial_val, int* partial_idx, int* counters,
                      cudaStream_t stream) {
@@ -879,6 +885,8 @@ FZ_API int fz_clear_error(int* err, cudaStream_t stream) {
 #include <stdio.h>
 
 static __device__ __align__(256) unsigned char fz_no_alloc_scratch[FZ_NO_ALLOC_SCRATCH_BYTES];
+static_assert(FZ_NO_ALLOC_MAX_SLICES == FZ_ARGMAX_MAX_SLICES,
+              "the fixed scratch is laid out for as many slices per row as the row-split argmax may use");
 
 namespace {
 constexpr int NO_ALLOC_MAX_DEVICES = 64;
@@ -930,6 +938,12 @@ FZ_API int fz_argmax_no_alloc(const float* logits, int* out, int rows, int vocab
              FZ_NO_ALLOC_MAX_ROWS);
     return FZ_TOO_LARGE;
   }
+  const int slices = fz_argmax_slices(vocab);
+  if (slices > FZ_NO_ALLOC_MAX_SLICES) {      // cannot happen while the two limits are equal (asserted above)
+    snprintf(g_no_alloc_error, sizeof g_no_alloc_error, "%d slices per row exceed the fixed scratch (at most %d)", slices,
+             FZ_NO_ALLOC_MAX_SLICES);
+    return FZ_TOO_LARGE;
+  }
   void* base = nullptr;
   const int st = no_alloc_scratch(&base);
   if (st != FZ_OK) return st;
@@ -943,7 +957,6 @@ FZ_API int fz_argmax_no_alloc(const float* logits, int* out, int rows, int vocab
     snprintf(g_no_alloc_error, sizeof g_no_alloc_error, "clearing the counters failed: %s", cudaGetErrorString(e));
     return (int)e;
   }
-  const int slices = fz_argmax_slices(vocab);     // at most FZ_NO_ALLOC_MAX_SLICES
   dim3 grid(rows, slices);
   // launched without the dependent-launch attribute: the memset above must be complete before the kernel starts
   argmax_kernel<<<grid, 512, 0, stream>>>(logits, out, vocab, partial_val, partial_idx, counters);

@@ -301,8 +301,8 @@ class LLMEngine:
             key = (bucket, self._greedy_step, self._ids_only, self._filtered_step)
         elif self.cuda_graphs and runner.meta.n_rows <= self.graph_rows:
             m = runner.meta
-            sig = ("step", m.n_rows, m.n_wanted, m.n_tiles, m.n_short_rows > 0, self._greedy_step, self._ids_only,
-                   self._filtered_step)
+            sig = ("step", m.n_rows, m.n_wanted, *getattr(ops, "step_signature", lambda _: ())(m), self._greedy_step,
+                   self._ids_only, self._filtered_step)
             if len(self._step_seen) > 4096:
                 self._step_seen.clear()
             self._step_seen[sig] = self._step_seen.get(sig, 0) + 1

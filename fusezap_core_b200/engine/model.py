@@ -12,7 +12,7 @@ import torch
 
 from ..cache import KVNeed
 from ..config import ModelSpec, describe, read_config_json
-from ..parts import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, build
+from ..parts import BLOCKS, FEED_FORWARDS, LOGIT_TRANSFORMS, MIXERS, NORMS, POSITIONS, build
 from ..weights import ParamSpec, load_weights
 from ..weights.loader import TORCH_DTYPE
 
@@ -24,8 +24,19 @@ def build_layers(spec: ModelSpec) -> list[Any]:
         ffn = build(FEED_FORWARDS, "feed-forward", ls.ffn)
         if ls.block.kind not in BLOCKS:
             raise NotImplementedError(f"block kind {ls.block.kind!r} is not registered (have {sorted(BLOCKS)})")
-        layers.append(BLOCKS[ls.block.kind](mixer, ffn, lambda ls=ls: build(NORMS, "norm", ls.norm), **ls.block.params))
+        layers.append(BLOCKS[ls.block.kind](mixer, ffn, _norm_maker(ls), **ls.block.params))
     return layers
+
+
+def _norm_maker(ls):
+    """What a block builds its norms with: the spec it names, else the layer's fallback kind."""
+    def make_norm(spec=None):
+        spec = spec if spec is not None else ls.norm
+        if spec is None:
+            raise ValueError(f"layer {ls.prefix!r}: the block asks for a norm that neither its params nor the layer's "
+                             f"`norm` describe")
+        return build(NORMS, "norm", spec)
+    return make_norm
 
 
 def declared_tensors(spec: ModelSpec, layers: list[Any] | None = None) -> dict[str, ParamSpec]:
@@ -58,6 +69,9 @@ class DecoderModel:
         self.layers = build_layers(spec)
         self.final_norm = build(NORMS, "norm", spec.final_norm)
         self.positions = {name: build(POSITIONS, "position encoding", p) for name, p in spec.positions.items()}
+        self.logit_transform = (build(LOGIT_TRANSFORMS, "logit transform", spec.logit_transform)
+                                if spec.logit_transform is not None else None)
+        self.embed_scale = 1.0 if spec.embed_scale is None else float(spec.embed_scale)
         for n, e in enumerate(spec.schedule):
             pn = self.layers[e.layer].mixer.position_name()
             if pn is not None and pn not in self.positions:
@@ -86,10 +100,27 @@ class DecoderModel:
 
     def graph_safe(self) -> bool:
         """True if every part's forward is a fixed sequence of kernels over device data (see `Part.graph_safe`)."""
-        parts = [self.final_norm, *self.positions.values()]
-        for block in self.layers:
-            parts += [block, block.mixer, block.ffn]
-        return all(getattr(p, "graph_safe", True) for p in parts)
+        return all(getattr(p, "graph_safe", True) for p in self.parts())
+
+    def parts(self) -> list[Any]:
+        """Every part of the model, blocks and what they hold included, each once."""
+        out, seen = [], set()
+        stack = [self.final_norm, *self.positions.values(), *self.layers]
+        if self.logit_transform is not None:
+            stack.append(self.logit_transform)
+        while stack:
+            p = stack.pop()
+            if id(p) in seen:
+                continue
+            seen.add(id(p))
+            out.append(p)
+            children = getattr(p, "children", None)
+            if children is not None:
+                stack += [c for _, c in children()]
+            for name in ("mixer", "ffn"):          # a block that does not list its children still has these two
+                if hasattr(p, name):
+                    stack.append(getattr(p, name))
+        return out
 
     def expected_tensors(self) -> dict[str, ParamSpec]:
         return declared_tensors(self.spec, self.layers)
@@ -127,26 +158,15 @@ class DecoderModel:
         return eng.generate([prompt_ids], params)[0]
 
     def weight_bytes(self) -> int:
-        """Bytes of every distinct tensor a step reads once (the decode roofline's weight term)."""
+        """Bytes of every distinct tensor a step reads once (the decode roofline's weight term): each part says which
+        tensors it reads (`Part.weight_tensors()`); the embedding table is not among them (a step gathers a few rows)
+        unless it also serves as the output matrix."""
         seen: dict[int, int] = {}
-        def add(t):
-            if isinstance(t, torch.Tensor):
+        for part in self.parts():
+            for t in part.weight_tensors():
                 seen[t.data_ptr()] = t.numel() * t.element_size()
-        for block in self.layers:
-            stack = [block]
-            while stack:
-                o = stack.pop()
-                for v in vars(o).values():
-                    if isinstance(v, torch.Tensor):
-                        add(v)
-                    elif isinstance(v, (tuple, list)):
-                        for t in v:
-                            add(t)
-                    elif hasattr(v, "bind") and hasattr(v, "tensors"):
-                        stack.append(v)
-        add(self.lm_head)
-        for v in vars(self.final_norm).values():
-            add(v)
+        if self.lm_head is not None:
+            seen[self.lm_head.data_ptr()] = self.lm_head.numel() * self.lm_head.element_size()
         return sum(seen.values())
 
 

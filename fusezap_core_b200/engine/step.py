@@ -7,9 +7,12 @@ two fixed-shape forwards over one packed int32 upload (fusezap/serve/engine.py:1
 fusezap/serve/kv_cache.py:382-405, 471-513); here it is one forward of any shape.
 
 Per step the host packs one int32 block and copies it to the device once:
-  tokens[N] | pos[N] | seq_row[N] | src[N] | sel[R] | segments[S x 4] | one block table (S x MB) per cache group | tiles
+  tokens[N] | pos[N] | seq_row[N] | src[N] | sel[R] | segments[S x 4] | one block table (S x MB) per cache group | extra
 seq_row[n] is the row of the request's block table in this step (-1: padding row), sel the rows whose logits are
-wanted (-1: none), a segment is (first row, rows, first position, state slot) of one request's portion.
+wanted (-1: none), a segment is (first row, rows, first position, state slot) of one request's portion. `extra` belongs
+to the kernel table: the mixers of the model say what kinds of step data their kernels need (`Mixer.step_needs()`), the
+table says how many int32 it wants for them (`Ops.step_extra_ints`) and fills them when the step is packed
+(`Ops.plan_step`), before the one copy. The step function itself knows nothing of any kernel's tiling.
 """
 from __future__ import annotations
 from dataclasses import dataclass, field
@@ -22,9 +25,6 @@ from ..cache import CacheManager
 from ..parts import LayerCache
 from .model import DecoderModel
 
-
-LONG_PORTION = 8    # portions of at least this many tokens go to the tile (prefill) attention kernel
-TILE_ROWS = 128     # token rows per tile of that kernel
 
 
 @dataclass
@@ -72,7 +72,7 @@ class Workspace:
 class StepMeta:
     """The step's int32 metadata: a pinned host block and its device copy with fixed offsets for a given capacity."""
     def __init__(self, device: torch.device, max_rows: int, max_wanted: int, max_segments: int, num_groups: int,
-                 pages_per_request: int):
+                 pages_per_request: int, extra_ints: int = 0):
         self.device = device
         self.max_rows, self.max_wanted, self.max_segments = max_rows, max_wanted, max_segments
         self.num_groups, self.mb = num_groups, pages_per_request
@@ -84,8 +84,8 @@ class StepMeta:
         self.o_sel, o = o, o + max_wanted
         self.o_seg, o = o, o + 4 * max_segments
         self.o_tab, o = o, o + num_groups * max_segments * pages_per_request
-        self.max_tiles = max_rows // TILE_ROWS + max_segments
-        self.o_tiles, o = o, o + 2 * self.max_tiles
+        self.extra_ints = extra_ints
+        self.o_extra, o = o, o + extra_ints
         self.size = o
         # a ring of pinned host blocks: a block is rewritten only after the copy that read it has finished
         pin = device.type == "cuda"
@@ -101,8 +101,7 @@ class StepMeta:
         self.segments: list[Segment] = []
         self.max_context = 0      # the longest context (position + 1) among the step's rows
         self.max_portion = 0      # the longest portion
-        self.n_tiles = 0          # TILE_ROWS-row tiles of the long portions (tile kernels); the other rows are "short"
-        self.n_short_rows = 0     # rows of short portions, padding rows included
+        self.plan = None          # whatever the kernel table's `plan_step` keeps about this step (launch sizes and the like)
 
     # device views (static addresses; sliced to the step's sizes)
     @property
@@ -118,15 +117,23 @@ class StepMeta:
     @property
     def seg(self) -> torch.Tensor: return self.dev[self.o_seg: self.o_seg + 4 * self.max_segments].view(self.max_segments, 4)
     @property
-    def tiles(self) -> torch.Tensor: return self.dev[self.o_tiles: self.o_tiles + 2 * self.max_tiles].view(self.max_tiles, 2)
+    def extra(self) -> torch.Tensor: return self.dev[self.o_extra: self.o_extra + self.extra_ints]
+    @property
+    def extra_host(self) -> np.ndarray: return self.np[self.o_extra: self.o_extra + self.extra_ints]
     def table(self, group: int) -> torch.Tensor:
         n = self.max_segments * self.mb
         return self.dev[self.o_tab + group * n: self.o_tab + (group + 1) * n].view(self.max_segments, self.mb)
 
     def fill(self, cache: CacheManager, portions: Sequence[Portion], starts: Sequence[int], pad_rows: int = 0,
              pad_wanted: int = 0) -> None:
-        """Pack the step. starts[i]: position of the first token of portions[i]. pad_rows / pad_wanted: run the step
-        with at least this many rows / wanted rows (padding rows are inert), for fixed-shape replay."""
+        """Pack the step and copy it to the device."""
+        self.pack(cache, portions, starts, pad_rows, pad_wanted)
+        self.upload()
+
+    def pack(self, cache: CacheManager, portions: Sequence[Portion], starts: Sequence[int], pad_rows: int = 0,
+             pad_wanted: int = 0) -> None:
+        """Pack the step on the host. starts[i]: position of the first token of portions[i]. pad_rows / pad_wanted: run
+        the step with at least this many rows / wanted rows (padding rows are inert), for fixed-shape replay."""
         self._turn = (self._turn + 1) % len(self._hosts)
         if self._used[self._turn] and self._events[self._turn] is not None:
             self._events[self._turn].synchronize()
@@ -174,17 +181,11 @@ class StepMeta:
                 row, used = cache.table_row(g, p.req)
                 t[s, :used] = row[:used]
                 t[s, used:] = -1
-        # TILE_ROWS-row tiles of the portions with at least LONG_PORTION tokens, the ones that see the most keys first
-        tl = [(sg.pos0 + min(r + TILE_ROWS, sg.n), sg.seq_row, r) for sg in self.segments if sg.n >= LONG_PORTION
-              for r in range(0, sg.n, TILE_ROWS)]
-        tl.sort(key=lambda x: -x[0])
-        tiles = a[self.o_tiles: self.o_tiles + 2 * self.max_tiles].reshape(self.max_tiles, 2)
-        tiles[len(tl):] = -1
-        for i, (_, s, r) in enumerate(tl):
-            tiles[i] = (s, r)
-        self.n_tiles = len(tl)
-        self.n_short_rows = n_rows - sum(sg.n for sg in self.segments if sg.n >= LONG_PORTION)
         self.n_rows, self.n_wanted, self.n_segments = n_rows, n_wanted, len(portions)
+        self.plan = None
+
+    def upload(self) -> None:
+        """The one host-to-device copy of the step's metadata."""
         self.dev.copy_(self.host, non_blocking=True)
         if self._events[self._turn] is not None:
             self._events[self._turn].record()
@@ -207,8 +208,12 @@ class StepRunner:
         self.model, self.cache, self.ops = model, cache, model.ops
         dev = model.device
         self.max_rows = max_rows
-        self.meta = StepMeta(dev, max_rows, max_wanted or max_rows, max_segments or max_rows, len(cache.groups),
-                             cache.max_pages_per_request)
+        # what kinds of step data the mixers' kernels need, and how many int32 the kernel table wants for them
+        self.needs = tuple(sorted({k for e in model.spec.schedule for k in model.layers[e.layer].mixer.step_needs()}))
+        max_segments = max_segments or max_rows
+        extra = getattr(self.ops, "step_extra_ints", lambda *a: 0)(self.needs, max_rows, max_segments)
+        self.meta = StepMeta(dev, max_rows, max_wanted or max_rows, max_segments, len(cache.groups),
+                             cache.max_pages_per_request, extra)
         self.ws = Workspace(dev, max_rows)
         self.ctx = StepContext(self.ops, self.ws, self.meta, model.positions, model)
         self.prev_ids: torch.Tensor | None = None     # device int32: the ids the previous step chose (see Portion.src)
@@ -240,17 +245,24 @@ class StepRunner:
 
     def _forward(self, model, ctx, meta, spec, ids_out):
         x = self.ws.get("x", (meta.n_rows, spec.hidden_size), torch.float32)
-        self.ops.embed(model.embed, meta.tokens, x, meta.src if self.prev_ids is not None else None, self.prev_ids)
+        src = meta.src if self.prev_ids is not None else None
+        if model.embed_scale != 1.0:
+            self.ops.embed(model.embed, meta.tokens, x, src, self.prev_ids, model.embed_scale)
+        else:
+            self.ops.embed(model.embed, meta.tokens, x, src, self.prev_ids)
         delta = None
         for e, lc in zip(spec.schedule, self.layer_caches):
             x, delta = model.layers[e.layer].forward(ctx, x, delta, lc)
         logits = self.ws.get("logits", (meta.n_wanted, spec.vocab_size), torch.float32)
         if meta.n_wanted:
             h = model.final_norm.forward(ctx, x, delta, rows=meta.sel, n_rows=meta.n_wanted)
-            fused = getattr(self.ops, "linear_argmax", None) if ids_out is not None else None
+            transform = model.logit_transform
+            fused = getattr(self.ops, "linear_argmax", None) if ids_out is not None and transform is None else None
             if fused is not None and fused(h, model.lm_head, None, ids_out):
                 return None
             self.ops.linear(h, model.lm_head, None, logits)
+            if transform is not None:
+                transform.forward(ctx, logits)
         return logits
 
     def prepare(self, portions: Sequence[Portion], pad_rows: int = 0, pad_wanted: int = 0) -> list[int]:
@@ -267,7 +279,11 @@ class StepRunner:
             start = cache.computed.get(p.req, 0)
             cache.ensure(p.req, start + len(p.tokens))
             starts.append(start)
-        self.meta.fill(cache, portions, starts, pad_rows, pad_wanted)
+        self.meta.pack(cache, portions, starts, pad_rows, pad_wanted)
+        plan_step = getattr(self.ops, "plan_step", None)
+        if plan_step is not None:
+            plan_step(self.meta, self.needs)
+        self.meta.upload()
         return starts
 
     def commit(self, portions: Sequence[Portion], starts: Sequence[int]) -> None:

@@ -19,13 +19,27 @@ import torch
 class Ops:
     dtype: torch.dtype
 
+    def step_extra_ints(self, needs: tuple, max_rows: int, max_segments: int) -> int:
+        """How many int32 of the step's metadata block this table wants for itself, given the kinds of step data the
+        model's mixers need (`Mixer.step_needs()`), for steps of at most max_rows rows of at most max_segments requests."""
+        return 0
+
+    def plan_step(self, meta: Any, needs: tuple) -> None:
+        """Called once per step, after the metadata is packed on the host and before its copy to the device: the table
+        may fill `meta.extra_host` (its int32 in the block) and keep launch sizes in `meta.plan`."""
+
+    def step_signature(self, meta: Any) -> tuple:
+        """What, beside the numbers of rows and wanted rows, fixes the kernel launches of the step just planned; two
+        steps with equal signatures may replay one captured graph."""
+        return ()
+
     def check_attention(self, num_heads: int, num_kv_heads: int, head_dim: int) -> None:
         """Raise ValueError if the attention kernels cannot take these sizes (nothing is ever computed wrongly)."""
         raise NotImplementedError
 
     def embed(self, table: torch.Tensor, tokens: torch.Tensor, x: torch.Tensor, src: torch.Tensor | None = None,
-              prev_ids: torch.Tensor | None = None) -> None:
-        """x[n, :] = float32(table[tokens[n], :]). tokens: int32 (N,). A token outside the table is an error.
+              prev_ids: torch.Tensor | None = None, scale: float = 1.0) -> None:
+        """x[n, :] = float32(table[tokens[n], :]) * scale. tokens: int32 (N,). A token outside the table is an error.
         With src (int32 (N,)) and prev_ids (int32): a row with src[n] >= 0 uses token prev_ids[src[n]] instead."""
         raise NotImplementedError
 

@@ -23,8 +23,34 @@ _DEVICE_ERRORS = {1: "a token id lies outside the embedding table", 2: "a positi
                   16: "a selected row lies outside the step"}
 
 
+LONG_PORTION = 8    # attention: portions of at least this many tokens go to the tile (prefill) kernels
+TILE_ROWS = 128     # token rows per tile of those kernels
+
+
 class KernelError(RuntimeError):
     pass
+
+
+def attention_tiles(portions, n_rows: int) -> tuple[list[tuple[int, int]], int]:
+    """How the attention kernels split a step. `portions`: (row of the block table, rows, first position) per request
+    in the step. Returns the TILE_ROWS-row tiles of the portions with at least LONG_PORTION tokens as (block-table row,
+    first row within the portion), the ones that see the most keys first, and the number of the step's other rows
+    (short portions, single tokens and padding), which go to the split-key kernel."""
+    tiles, long_rows = [], 0
+    for seq_row, n, pos0 in portions:
+        if n >= LONG_PORTION:
+            long_rows += n
+            tiles += [(pos0 + min(r + TILE_ROWS, n), seq_row, r) for r in range(0, n, TILE_ROWS)]
+    tiles.sort(key=lambda t: -t[0])
+    return [(s, r) for _, s, r in tiles], n_rows - long_rows
+
+
+class AttentionPlan:
+    """What `plan_step` keeps about a step for the attention kernels."""
+    __slots__ = ("tiles", "n_tiles", "n_short_rows")
+
+    def __init__(self, tiles: torch.Tensor | None, n_tiles: int, n_short_rows: int):
+        self.tiles, self.n_tiles, self.n_short_rows = tiles, n_tiles, n_short_rows
 
 
 def _p(t: torch.Tensor | None) -> c_void_p:
@@ -126,6 +152,29 @@ class CudaOps(Ops):
             self.err.zero_()
             raise KernelError("a kernel reported: " + "; ".join(m for b, m in _DEVICE_ERRORS.items() if word & b))
 
+    # ---- per-step planning (the step function calls these; it knows nothing of the kernels' tiling)
+    def step_extra_ints(self, needs: tuple, max_rows: int, max_segments: int) -> int:
+        """int32 this table wants in the step's metadata block for a model whose mixers need `needs`."""
+        return 2 * (max_rows // TILE_ROWS + max_segments) if "attention" in needs else 0
+
+    def plan_step(self, meta, needs: tuple) -> None:
+        """Called when a step has been packed on the host, before its one copy to the device: writes the attention
+        kernels' tile list into the block's extra part and keeps the launch sizes in `meta.plan`."""
+        if "attention" not in needs:
+            meta.plan = None
+            return
+        tiles, short = attention_tiles(((sg.seq_row, sg.n, sg.pos0) for sg in meta.segments), meta.n_rows)
+        host = meta.extra_host.reshape(-1, 2)
+        host[len(tiles):] = -1
+        if tiles:
+            host[:len(tiles)] = tiles
+        meta.plan = AttentionPlan(meta.extra.view(-1, 2), len(tiles), short)
+
+    def step_signature(self, meta) -> tuple:
+        """What, beside the row counts, fixes the kernel launches of a step (two steps that agree in it launch alike)."""
+        plan = meta.plan
+        return (plan.n_tiles, plan.n_short_rows > 0) if plan is not None else ()
+
     def check_attention(self, num_heads: int, num_kv_heads: int, head_dim: int) -> None:
         if head_dim % 16:
             raise ValueError(f"head_dim {head_dim} is not a multiple of 16; the attention kernels refuse it")
@@ -134,7 +183,7 @@ class CudaOps(Ops):
                              f"{head_dim} (need heads % kv_heads == 0, heads / kv_heads <= 32, head_dim <= 256)")
 
     # ---- kernels
-    def embed(self, table, tokens, x, src=None, prev_ids=None) -> None:
+    def embed(self, table, tokens, x, src=None, prev_ids=None, scale: float = 1.0) -> None:
         self._want(table, "embedding table", (torch.float32, torch.bfloat16), 2)
         self._want(tokens, "tokens", (torch.int32,), 1)
         self._want(x, "x", (torch.float32,), 2)
@@ -146,7 +195,8 @@ class CudaOps(Ops):
             self._want(prev_ids, "prev_ids", (torch.int32,), 1)
         self._check(self.core.fz_embed(_p(table), c_int(_CODE[table.dtype]), _p(tokens), _p(src),
                                        _p(prev_ids if src is not None else None), _p(x), c_int(n), c_int(d),
-                                       c_int(table.shape[0]), _p(self.err), self._stream()), "embed")
+                                       c_int(table.shape[0]), c_float(scale), _p(self.err), self._stream()), "embed",
+                    n * d * (table.element_size() + 4))
 
     def add_rmsnorm(self, x, delta, weight, eps, h, rows=None) -> None:
         self._want(x, "x", (torch.float32,), 2)
@@ -303,8 +353,10 @@ class CudaOps(Ops):
 
     def _attention(self, q, k, v, page_stride, cache, meta, table, out, n, hq, hkv, hd, scale, window) -> None:
         if self.use_tensor_cores and self.tc.fz_attn_decode_check(c_int(hq), c_int(hkv), c_int(hd)) == 0:
-            from ..engine.step import LONG_PORTION
-            if meta.n_short_rows > 0:
+            plan = meta.plan
+            if plan is None:
+                raise KernelError("paged_attention: the step was not planned (plan_step with the need 'attention')")
+            if plan.n_short_rows > 0:
                 # rows of short portions and decoded tokens: split over key partitions, partials in float32 scratch
                 parts = self.tc.fz_attn_partitions(c_int(meta.max_context))
                 need = n * hq * parts * (hd + 2)
@@ -316,17 +368,17 @@ class CudaOps(Ops):
                     c_int(hq), c_int(hkv), c_int(hd), c_float(scale), c_int(window), c_int(meta.max_context),
                     c_int(LONG_PORTION), c_int(k.shape[0]), _p(self.err), self._stream()), "paged_attention (decode)")
                 self.launches += 1    # the combine kernel
-            if meta.n_tiles > 0 and self.prefill_tcgen05 and \
+            if plan.n_tiles > 0 and self.prefill_tcgen05 and \
                     self.tc.fz_attn_prefill_tc_check(c_int(hq), c_int(hkv), c_int(hd), c_int(cache.page_size)) == 0:
                 # rows of long portions on the tcgen05 flash-attention kernel
                 self._check(self.tc.fz_attn_prefill_tc(
-                    _p(q), c_int(n), _p(k), _p(v), c_longlong(page_stride), c_int(k.shape[0]), _p(meta.seg), _p(meta.tiles),
-                    c_int(meta.n_tiles), _p(table), c_int(table.shape[1]), c_int(cache.page_size), _p(out), c_int(hq),
+                    _p(q), c_int(n), _p(k), _p(v), c_longlong(page_stride), c_int(k.shape[0]), _p(meta.seg), _p(plan.tiles),
+                    c_int(plan.n_tiles), _p(table), c_int(table.shape[1]), c_int(cache.page_size), _p(out), c_int(hq),
                     c_int(hkv), c_int(hd), c_float(scale), c_int(window), _p(self.err), self._stream()),
                     "paged_attention (prefill, tcgen05)")
-            elif meta.n_tiles > 0:
+            elif plan.n_tiles > 0:
                 self._check(self.tc.fz_attn_prefill(
-                    _p(q), _p(k), _p(v), _p(meta.seg), _p(meta.tiles), c_int(meta.n_tiles), _p(table),
+                    _p(q), _p(k), _p(v), _p(meta.seg), _p(plan.tiles), c_int(plan.n_tiles), _p(table),
                     c_int(table.shape[1]), c_longlong(page_stride), c_int(cache.page_size), _p(out), c_int(hq),
                     c_int(hkv), c_int(hd), c_float(scale), c_int(window), self._stream()), "paged_attention (prefill)")
             return
@@ -350,10 +402,10 @@ class CudaOps(Ops):
         r, v = logits.shape
         if out.shape[0] != r:
             raise KernelError(f"argmax: logits {tuple(logits.shape)}, out {tuple(out.shape)}")
-        # scratch of the row-split argmax: per row up to 64 partial (value, index) pairs and one counter (kept zero)
-        cap = max(r, 64)
-        pv = self._scratch("argmax partial values", cap * 64, torch.float32)
-        pi = self._scratch("argmax partial indices", cap * 64, torch.int32)
+        # scratch of the row-split argmax: per row up to S partial (value, index) pairs and one counter (kept zero)
+        cap, slices = max(r, 64), int(self.core.fz_argmax_max_slices())
+        pv = self._scratch("argmax partial values", cap * slices, torch.float32)
+        pi = self._scratch("argmax partial indices", cap * slices, torch.int32)
         cnt = self._scratch("argmax counters", cap, torch.int32, zero=True)
         self._check(self.core.fz_argmax(_p(logits), _p(out), c_int(r), c_int(v), _p(pv), _p(pi), _p(cnt), self._stream()),
                     "argmax")

@@ -54,6 +54,9 @@ class GQAttention(Mixer):
     def position_name(self) -> str | None:
         return self.position
 
+    def step_needs(self) -> tuple[str, ...]:
+        return ("attention",)
+
     def forward(self, ctx, h: torch.Tensor, cache: LayerCache) -> torch.Tensor:
         n, ops, ws = h.shape[0], ctx.ops, ctx.ws
         Hq, Hkv, hd = self.Hq, self.Hkv, self.hd

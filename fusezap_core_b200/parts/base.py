@@ -11,8 +11,9 @@ through the kernel table of the step (`ctx.ops`), taking scratch buffers from `c
   PositionEncoding.prepare(max_len, device)      builds its tables
   PositionEncoding.rotate_and_store(ctx, qkv, q_out, cache, num_heads, num_kv_heads, head_dim)
   Block.forward(ctx, x, delta, cache) -> (x, delta)   the arrangement of norms, mixer and feed-forward of one layer
+  LogitTransform.forward(ctx, logits) -> None    changes the float32 logits of the wanted rows in place
 
-Register a new part with `@register_mixer("name")` (or _feed_forward, _norm, _position, _block) and name it in a
+Register a new part with `@register_mixer("name")` (or _feed_forward, _norm, _position, _block, _logit_transform) and name it in a
 `PartSpec`; nothing else in the package changes.
 """
 from __future__ import annotations
@@ -33,6 +34,7 @@ FEED_FORWARDS: dict[str, type] = {}
 NORMS: dict[str, type] = {}
 POSITIONS: dict[str, type] = {}
 BLOCKS: dict[str, type] = {}
+LOGIT_TRANSFORMS: dict[str, type] = {}
 
 
 def _register(table: dict[str, type], what: str) -> Callable[[str], Callable[[type], type]]:
@@ -50,6 +52,7 @@ register_feed_forward = _register(FEED_FORWARDS, "feed-forward")
 register_norm = _register(NORMS, "norm")
 register_position = _register(POSITIONS, "position encoding")
 register_block = _register(BLOCKS, "block")
+register_logit_transform = _register(LOGIT_TRANSFORMS, "logit transform")
 
 
 def build(table: dict[str, type], what: str, spec: PartSpec) -> Any:
@@ -81,6 +84,18 @@ class Part:
     def bind(self, tensors: dict[str, torch.Tensor], ops: Any) -> None:
         """Receives the tensors of `tensors()` that the checkpoint has (optional ones may be absent)."""
 
+    def weight_tensors(self) -> list[torch.Tensor]:
+        """Every device tensor a step reads once for this part (sub-parts not included): what the decode roofline counts
+        as this part's weight bytes. The default finds the tensors the part keeps as attributes (alone, or in tuples
+        and lists); a part that keeps them elsewhere (a dict, a nested object) overrides this."""
+        found = []
+        for v in vars(self).values():
+            if isinstance(v, torch.Tensor):
+                found.append(v)
+            elif isinstance(v, (tuple, list)):
+                found += [t for t in v if isinstance(t, torch.Tensor)]
+        return found
+
 
 class Mixer(Part):
     def cache_need(self) -> KVNeed | None:
@@ -91,6 +106,11 @@ class Mixer(Part):
 
     def position_name(self) -> str | None:
         return None
+
+    def step_needs(self) -> tuple[str, ...]:
+        """Kinds of per-step data this mixer's kernels need beside the common metadata (for instance "attention": the
+        kernel table then plans its attention kernels' tiles for every step). None by default."""
+        return ()
 
     def forward(self, ctx: "StepContext", h: torch.Tensor, cache: LayerCache) -> torch.Tensor:
         raise NotImplementedError
@@ -124,7 +144,19 @@ class PositionEncoding(Part):
 
 
 class Block(Part):
-    """Arranges norm(s), mixer and feed-forward. Built with the already built parts of its layer."""
+    """Arranges norm(s), mixer and feed-forward. Built with the already built parts of its layer and `make_norm(spec)`,
+    which builds a norm from a `PartSpec` (None: the layer's fallback norm kind); `children()` lists (tensor-name
+    prefix, part) of everything it holds."""
+    def children(self) -> tuple:
+        return ()
+
     def forward(self, ctx: "StepContext", x: torch.Tensor, delta: torch.Tensor | None,
                 cache: LayerCache) -> tuple[torch.Tensor, torch.Tensor | None]:
+        raise NotImplementedError
+
+
+class LogitTransform(Part):
+    """Changes the logits of the wanted rows, (R, vocab) float32, in place (a soft cap, a scale, a bias...). With one in
+    the model the output product always writes its logits (no fused argmax)."""
+    def forward(self, ctx: "StepContext", logits: torch.Tensor) -> None:
         raise NotImplementedError

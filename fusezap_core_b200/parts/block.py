@@ -12,9 +12,13 @@ from .base import Block, FeedForward, LayerCache, Mixer, Norm, register_block
 @register_block("pre_norm")
 class PreNormBlock(Block):
     def __init__(self, mixer: Mixer, ffn: FeedForward, make_norm,
-                 names: tuple[str, str, str, str] = ("input_layernorm", "self_attn", "post_attention_layernorm", "mlp")):
-        """mixer, ffn: the layer's built parts; make_norm(): builds one more norm of the layer's norm kind."""
-        self.mixer, self.ffn, self.norm1, self.norm2, self.names = mixer, ffn, make_norm(), make_norm(), tuple(names)
+                 names: tuple[str, str, str, str] = ("input_layernorm", "self_attn", "post_attention_layernorm", "mlp"),
+                 norms: tuple = (None, None)):
+        """mixer, ffn: the layer's built parts; make_norm(spec): builds a norm. `norms`: a PartSpec for the norm before
+        the mixer and one for the norm before the feed-forward (None: the layer's fallback kind), so the two may be of
+        different kinds."""
+        self.mixer, self.ffn, self.names = mixer, ffn, tuple(names)
+        self.norm1, self.norm2 = make_norm(norms[0]), make_norm(norms[1])
 
     def children(self):
         n1, mx, n2, ff = self.names

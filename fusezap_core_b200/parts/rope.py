@@ -54,6 +54,9 @@ class RotaryEncoding(PositionEncoding):
         self.cos = torch.from_numpy(np.cos(fr).astype(np.float32)).to(device)
         self.sin = torch.from_numpy(np.sin(fr).astype(np.float32)).to(device)
 
+    def weight_tensors(self) -> list:
+        return []       # a step gathers one row of the tables per token; they are not streamed like weights
+
     def rotate_and_store(self, ctx, qkv: torch.Tensor, q_out: torch.Tensor, cache: LayerCache,
                          num_heads: int, num_kv_heads: int, head_dim: int) -> None:
         if head_dim != self.head_dim:

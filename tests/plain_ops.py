@@ -20,13 +20,13 @@ class PlainOps:
         if num_heads % num_kv_heads or head_dim % 2:
             raise ValueError("bad attention sizes")
 
-    def embed(self, table, tokens, x, src=None, prev_ids=None) -> None:
+    def embed(self, table, tokens, x, src=None, prev_ids=None, scale=1.0) -> None:
         t = tokens.long()
         if src is not None:
             t = torch.where(src >= 0, prev_ids.long()[src.long().clamp(min=0)], t)
         if ((t < 0) | (t >= table.shape[0])).any():
             raise ValueError("token id outside the embedding table")
-        x.copy_(table[t].float())
+        x.copy_(table[t].float() * torch.tensor(scale, dtype=torch.float32))
 
     def add_rmsnorm(self, x, delta, weight, eps, h, rows=None) -> None:
         if rows is None:

@@ -27,7 +27,8 @@ def follows_plain_model(cfg, w, dtype, prompt, toks, margin):
 
 @pytest.fixture(scope="module")
 def folders(tmp_path_factory):
-    return {n: make_model_dir(n, tmp_path_factory.mktemp(n)) for n in ("tiny_llama", "tiny_qwen2", "tiny_window")}
+    return {n: make_model_dir(n, tmp_path_factory.mktemp(n)) for n in ("tiny_llama", "tiny_qwen2", "tiny_window", "tiny_hd64",
+                                                                        "tiny_hd128")}
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -130,6 +131,89 @@ def test_small_steps_replay_captured_graphs(folders):
     assert only_decode.generate(P, ps) == without.generate(P, ps) and only_decode.stats["step_graph_replays"] == 0
 
 
+@pytest.mark.parametrize("name", ["tiny_hd64", "tiny_hd128"])
+def test_the_serving_path_at_tensor_core_head_sizes(folders, name):
+    """bfloat16 at head sizes 64 and 128, where attention runs on the tensor-core kernels (portions of 8 tokens and more
+    on the tcgen05 kernel, decoded tokens on the split-key kernel): the composition that serving and the benchmark use,
+    through the scheduler, with decode steps replayed from per-bucket graphs whose launch sizes cover `max_model_len`
+    (much larger than any live context here), mixed steps replayed from by-shape graphs, and decode steps launched
+    ahead. Contexts cross a 64-key unit and a 256-key block of the split-key kernel while decoding. The few-token kernels
+    compute a row independently of the other rows of a step and of padding, so graphs on / off and launching ahead on /
+    off must give equal tokens, not merely close ones; and the tokens follow the plain bfloat16 model."""
+    from fusezap_core_b200 import LLMEngine, SamplingParams, load_model
+    d, cfg, opts = folders[name]
+    w = read_weights(d)
+    model = load_model(d, "bfloat16", "cuda:0", max_len=1024)
+    P = prompts(cfg, (250, 60, 5, 130, 33, 71), seed=9)
+    ps = [SamplingParams(max_tokens=n, ignore_eos=True) for n in (14, 12, 20, 9, 16, 11)]
+    outs, engines = {}, {}
+    for graphs in (True, False):
+        for ahead in (True, False):
+            eng = LLMEngine(model, num_blocks=80, block_size=16, max_num_seqs=4, max_prefill_tokens=48, max_model_len=1024,
+                            cuda_graphs=graphs, lookahead=ahead)
+            seen = {}
+            launch = eng._launch
+            def spy(portions, rows, decode_only, all_produce, kind="decode_steps", eng=eng, seen=seen, launch=launch):
+                out = launch(portions, rows, decode_only, all_produce, kind)
+                m = eng.runner.meta
+                if not decode_only:
+                    sig = (m.n_rows, m.n_wanted, *eng.ops.step_signature(m))
+                    seen.setdefault(sig, set()).add(tuple((sg.row0, sg.n, sg.pos0) for sg in m.segments))
+                return out
+            eng._launch = spy
+            outs[graphs, ahead] = eng.generate(P, ps)
+            engines[graphs, ahead] = (eng, seen)
+            model.ops.check_errors()
+            assert eng.cache.num_free_pages == 80
+    eng, seen = engines[True, True]
+    assert eng.stats["graph_replays"] > 10 and eng.stats["step_graph_replays"] > 0 and eng.stats["lookahead_steps"] > 5
+    assert any(len(layouts) > 1 and sig[2] > 0 for sig, layouts in seen.items()), \
+        "two steps with equal sizes but different portion layouts, with rows on the tile kernel"
+    assert engines[False, False][0].stats["graph_replays"] == 0 and engines[False, False][0].stats["lookahead_steps"] == 0
+    for k, v in outs.items():
+        assert v == outs[False, False], f"graphs {k[0]}, launching ahead {k[1]}: tokens differ from kernel-by-kernel stepping"
+    for p, t, q in zip(P, outs[True, True], ps):
+        assert len(t) == q.max_tokens
+        follows_plain_model(cfg, w, "bfloat16", p, t, 0.15)
+    # so few pages that requests lose theirs and are recomputed (as portions, on the other attention kernel: close, not equal)
+    few = LLMEngine(model, num_blocks=-(-270 // 16) + 3, block_size=16, max_num_seqs=4, max_prefill_tokens=48, max_model_len=1024)
+    again = few.generate(P, ps)
+    assert few.stats["preemptions"] > 0 and few.cache.num_free_pages == few.cache.num_pages
+    for p, t in zip(P, again):
+        follows_plain_model(cfg, w, "bfloat16", p, t, 0.15)
+
+
+@pytest.mark.parametrize("dtype,name", [("float32", "tiny_qwen2"), ("bfloat16", "tiny_hd128")])
+def test_scheduler_options_through_the_engine(folders, dtype, name):
+    """`prefill_first`, `max_num_batched_tokens` (also below `max_num_seqs`, where the decode buckets must not outgrow
+    a step), `mixed_prefill_tokens`, `prefill_every`, `max_prefill_seqs`: other steps, and in float32 the same tokens
+    as the default engine (a row's bits do not depend on the batch or the cut); in bfloat16 tokens that follow the
+    plain model."""
+    from fusezap_core_b200 import LLMEngine, SamplingParams, load_model
+    d, cfg, opts = folders[name]
+    w = read_weights(d)
+    model = load_model(d, dtype, "cuda:0", max_len=256)
+    P = prompts(cfg, (30, 7, 55, 12, 41, 3, 26, 18), seed=5)
+    params = SamplingParams(max_tokens=10, ignore_eos=True)
+    base = dict(num_blocks=96, block_size=opts["page_size"], max_num_seqs=8, max_prefill_tokens=16, max_model_len=256)
+    ref = LLMEngine(model, **base).generate(P, params)
+    for knobs in (dict(prefill_first=2), dict(max_num_batched_tokens=20), dict(max_num_batched_tokens=6),
+                  dict(mixed_prefill_tokens=5, prefill_every=2), dict(max_prefill_seqs=1, prefill_first=1)):
+        eng = LLMEngine(model, **base, **knobs)
+        got = eng.generate(P, params)
+        model.ops.check_errors()
+        assert eng.stats["graph_replays"] > 0 and eng.cache.num_free_pages == 96
+        if "prefill_first" in knobs:
+            assert eng.scheduler.steps_held_back > 0
+        if knobs.get("max_num_batched_tokens") == 6:
+            assert max(eng._buckets) == 6, "no decode bucket is larger than a step may be"
+        if dtype == "float32":
+            assert got == ref, knobs
+        else:
+            for p, t in zip(P, got):
+                follows_plain_model(cfg, w, dtype, p, t, 0.15)
+
+
 def test_seeded_sampling_on_the_device(folders):
     from fusezap_core_b200 import LLMEngine, SamplingParams, load_model
     d, cfg, opts = folders["tiny_qwen2"]
@@ -173,6 +257,12 @@ def test_command_line(folders, tmp_path):
     assert lines[0]["num_prompt_tokens"] == 4 and lines[1]["num_prompt_tokens"] == 9
     w = read_weights(d)
     follows_plain_model(cfg, w, "float32", [5, 17, 3, 200], lines[0]["token_ids"], 1e-3)
+    # the scheduler's options on the command line: other steps, the same tokens (float32); and the per-step profile
+    p2 = subprocess.run(cmd + ["--prefill-first", "2", "--max-num-batched-tokens", "5", "--max-prefill-tokens", "4",
+                               "--mixed-prefill-tokens", "3", "--profile"], capture_output=True, text=True, cwd=ROOT, timeout=300)
+    assert p2.returncode == 0, p2.stderr[-2000:]
+    assert [json.loads(l)["token_ids"] for l in p2.stdout.splitlines() if l.startswith("{")] == [l["token_ids"] for l in lines]
+    assert "profile:" in p2.stderr and "paged_attention" in p2.stderr and "linear" in p2.stderr
     out = str(tmp_path / "rw")
     p = subprocess.run([sys.executable, "-m", "fusezap_core_b200", "random-weights", "--preset", "tiny-qwen2", "--out", out,
                         "--seed", "3", "--dtype", "bfloat16"], capture_output=True, text=True, cwd=ROOT, timeout=120)

@@ -29,7 +29,6 @@ def check(out, ref, K):
     out, ref = out.double().cpu(), ref.cpu()
     assert torch.isfinite(out).all(), "unwritten or non-finite outputs"
     scale = float(ref.abs().max())
-    tol = 2e-5 * scale if out.dtype == torch.float64 and False else None
     err = float((out - ref).abs().max())
     return err, scale
 

@@ -29,12 +29,12 @@ def close(got: torch.Tensor, ref: torch.Tensor, dtype: str, scale: float | None 
 class Meta:
     """Step metadata for kernel tests: the views the kernels read, on any device."""
     def __init__(self, pos, seq_row, table, device):
-        from fusezap_core_b200.engine.step import LONG_PORTION, TILE_ROWS
+        from fusezap_core_b200.kernels.table import AttentionPlan, attention_tiles
         self.pos = torch.tensor(pos, dtype=torch.int32, device=device)
         self.seq_row = torch.tensor(seq_row, dtype=torch.int32, device=device)
         self._table = torch.tensor(table, dtype=torch.int32, device=device)
         # portions = runs of rows of one request at consecutive positions: (first row, rows, first position, slot)
-        segs, tiles, i = {}, [], 0
+        segs, i = {}, 0
         while i < len(pos):
             j = i
             while j + 1 < len(pos) and seq_row[j + 1] == seq_row[i] and pos[j + 1] == pos[j] + 1:
@@ -43,14 +43,9 @@ class Meta:
                 segs[seq_row[i]] = (i, j - i + 1, pos[i], -1)
             i = j + 1
         seg = [segs.get(s, (0, 0, 0, -1)) for s in range(len(table))]
-        for s, (r0, n, p0, _) in enumerate(seg):
-            if n >= LONG_PORTION:
-                tiles += [(p0 + min(r + TILE_ROWS, n), s, r) for r in range(0, n, TILE_ROWS)]
-        tiles.sort(key=lambda x: -x[0])
+        tiles, short = attention_tiles([(s, n, p0) for s, (r0, n, p0, _) in enumerate(seg)], len(pos))
         self.seg = torch.tensor(seg, dtype=torch.int32, device=device)
-        self.tiles = torch.tensor([(s, r) for _, s, r in tiles] or [(-1, 0)], dtype=torch.int32, device=device)
-        self.n_tiles = len(tiles)
-        self.n_short_rows = len(pos) - sum(n for _, n, _, _ in seg if n >= LONG_PORTION)
+        self.plan = AttentionPlan(torch.tensor(tiles or [(-1, 0)], dtype=torch.int32, device=device), len(tiles), short)
         self.max_context = max(pos) + 1
     def table(self, group):
         return self._table

@@ -6,7 +6,9 @@ For each tiny configuration and both dtypes one `bin/trace_run` process replays,
   portions portions of changing size, down to two tokens
   mixed    up to four live requests, portions of some beside single tokens of others, in a pool so small that pages
            given back by finished requests are used again by later ones
-and every wanted position is compared with `plain_model.forward` of the whole request.
+and every wanted position is compared with `plain_model.forward` of the whole request. In float32 the four cuttings
+must also agree with each other bit for bit (the reference asserts the same of its engine:
+tests/test_serve_cuda.py:847-866): every sum's order is a function of the row alone.
 """
 import numpy as np
 import pytest
@@ -15,7 +17,8 @@ from util import TraceBuilder, assert_close, make_model_dir, plain_logits, promp
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = (70, 41, 97, 33, 58, 64)   # six requests; the pool below holds about three at a time
+LENGTHS = (70, 41, 97, 33, 58, 64)   # six requests; the pool below holds the four short ones at a time
+POOL_TOKENS = 256
 
 
 def build_trace(P: list[list[int]]) -> TraceBuilder:
@@ -40,15 +43,17 @@ def build_trace(P: list[list[int]]) -> TraceBuilder:
     # 4. mixed: a little scheduler that keeps up to four requests live; a request first gets portions of its prompt
     # part (two thirds), then single tokens; finished requests give their pages back and the next one starts
     rng = np.random.default_rng(5)
-    waiting = list(range(len(P)))
+    waiting = sorted(range(len(P)), key=lambda i: -(-len(P[i]) // 64))     # the four that fit together come first
     live: dict[int, int] = {}
     held = 0
-    budget = 192   # tokens the pool holds, each request rounded up to 64
+    budget = POOL_TOKENS   # tokens the pool holds, each request rounded up to 64
+    tb.most_live = 0
     while waiting or live:
         while waiting and len(live) < 4 and held + -(-len(P[waiting[0]]) // 64) * 64 <= budget:
             i = waiting.pop(0)
             live[i] = 0
             held += -(-len(P[i]) // 64) * 64
+        tb.most_live = max(tb.most_live, len(live))
         entries, ends = [], []
         for i in list(live):
             at, ids = live[i], P[i]
@@ -74,7 +79,8 @@ def test_replay_all_cuttings(name, dtype, tmp_path):
     P = prompts(cfg, LENGTHS, seed=3)
     ref = [plain_logits(cfg, weights, ids, dtype) for ids in P]
     tb = build_trace(P)
-    outs = run_trace(model_dir, dtype, str(tmp_path / "out"), max_tokens=192, steps=tb.steps, page_size=opts["page_size"])
+    assert tb.most_live == 4 and max(len(s["entries"]) for s in tb.steps) == 4, "four requests live, and in one step"
+    outs = run_trace(model_dir, dtype, str(tmp_path / "out"), max_tokens=POOL_TOKENS, steps=tb.steps, page_size=opts["page_size"])
     got = tb.collect(outs, cfg["vocab_size"])
     for rid, rows in sorted(got.items()):
         i = int(rid[1:])
@@ -82,6 +88,15 @@ def test_replay_all_cuttings(name, dtype, tmp_path):
         g = np.stack([rows[p] for p in range(len(P[i]))])
         assert_close(g, ref[i], dtype, f"{name} {dtype} request {rid}")
     assert {r[0] for r in got} == {"w", "d", "p", "m"}
+    if dtype == "float32":
+        # bit for bit among the cuttings: whole / last 32 one by one / portions / mixed
+        for rid, rows in sorted(got.items()):
+            if rid[0] == "w":
+                continue
+            whole = got["w" + rid[1:]]
+            for p, row in rows.items():
+                assert np.array_equal(row, whole[p]), (f"{name}: request {rid} position {p} differs from the whole request's "
+                                                       f"row by {np.abs(row - whole[p]).max():.3e}")
 
 
 def test_replay_default_pages_bf16_file(tmp_path):
