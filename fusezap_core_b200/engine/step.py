@@ -125,9 +125,13 @@ class StepMeta:
         return self.dev[self.o_tab + group * n: self.o_tab + (group + 1) * n].view(self.max_segments, self.mb)
 
     def fill(self, cache: CacheManager, portions: Sequence[Portion], starts: Sequence[int], pad_rows: int = 0,
-             pad_wanted: int = 0) -> None:
-        """Pack the step and copy it to the device."""
+             pad_wanted: int = 0, ops: Any = None, needs: tuple = ()) -> None:
+        """Pack the step, let the kernel table `ops` plan it for the kinds of step data in `needs`, and copy it to the
+        device."""
         self.pack(cache, portions, starts, pad_rows, pad_wanted)
+        plan_step = getattr(ops, "plan_step", None)
+        if plan_step is not None:
+            plan_step(self, needs)
         self.upload()
 
     def pack(self, cache: CacheManager, portions: Sequence[Portion], starts: Sequence[int], pad_rows: int = 0,
@@ -279,11 +283,7 @@ class StepRunner:
             start = cache.computed.get(p.req, 0)
             cache.ensure(p.req, start + len(p.tokens))
             starts.append(start)
-        self.meta.pack(cache, portions, starts, pad_rows, pad_wanted)
-        plan_step = getattr(self.ops, "plan_step", None)
-        if plan_step is not None:
-            plan_step(self.meta, self.needs)
-        self.meta.upload()
+        self.meta.fill(cache, portions, starts, pad_rows, pad_wanted, self.ops, self.needs)
         return starts
 
     def commit(self, portions: Sequence[Portion], starts: Sequence[int]) -> None:

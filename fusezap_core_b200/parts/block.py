@@ -18,7 +18,7 @@ class PreNormBlock(Block):
         the mixer and one for the norm before the feed-forward (None: the layer's fallback kind), so the two may be of
         different kinds."""
         self.mixer, self.ffn, self.names = mixer, ffn, tuple(names)
-        self.norm1, self.norm2 = make_norm(norms[0]), make_norm(norms[1])
+        self.norm1, self.norm2 = (make_norm(spec) if spec is not None else make_norm() for spec in norms)
 
     def children(self):
         n1, mx, n2, ff = self.names

@@ -21,7 +21,8 @@ def context(dtype, needs, page_size=8, pages=32, max_len=128, rows=128):
     ops = cuda_ops(dtype)
     dev = torch.device("cuda:0")
     cache = CacheManager(needs, {}, page_size, pages, 4, max_len, ops.dtype, dev)
-    meta = StepMeta(dev, rows, rows, 4, len(cache.groups), cache.max_pages_per_request)
+    meta = StepMeta(dev, rows, rows, 4, len(cache.groups), cache.max_pages_per_request,
+                    ops.step_extra_ints(("attention",), rows, 4))
     ctx = StepContext(ops, Workspace(dev, rows), meta, {}, None)
     return ops, cache, meta, ctx
 
@@ -68,7 +69,7 @@ def test_rotary_part(dtype, scaling):
     n, start = 13, 40
     cache.ensure("a", start + n)
     cache.computed["a"] = start
-    meta.fill(cache, [Portion("a", [0] * n, [])], [start])
+    meta.fill(cache, [Portion("a", [0] * n, [])], [start], ops=ops, needs=("attention",))
     qkv = torch.randn(n, (Hq + 2 * Hkv) * hd, generator=g)
     lc = LayerCache(*cache.groups[0].view(0), group=0, page_size=8, write=True)
     q = torch.empty(n, Hq * hd, dtype=DT[dtype], device="cuda")
@@ -141,7 +142,7 @@ def test_attention_part_and_block(dtype, Hq, Hkv, hd, window, bias):
     got = []
     for req, (lo, hi) in (("a", (0, cut)), ("a", (cut, T))):
         cache.ensure(req, hi)
-        meta.fill(cache, [Portion(req, [0] * (hi - lo), [])], [lo])
+        meta.fill(cache, [Portion(req, [0] * (hi - lo), [])], [lo], ops=ops, needs=("attention",))
         lc = LayerCache(*cache.groups[0].view(0), group=0, page_size=8, write=True)
         got.append(mixer.forward(ctx, h[lo:hi].cuda(), lc).cpu().clone())
         cache.commit(req, hi)
@@ -155,7 +156,7 @@ def test_attention_part_and_block(dtype, Hq, Hkv, hd, window, bias):
     block.bind({k: v.cuda() for k, v in w.items()}, ops)
     x = torch.randn(T, D, generator=g)
     cache.ensure("b", T)
-    meta.fill(cache, [Portion("b", [0] * T, [])], [0])
+    meta.fill(cache, [Portion("b", [0] * T, [])], [0], ops=ops, needs=("attention",))
     lc = LayerCache(*cache.groups[0].view(1), group=0, page_size=8, write=True)
     xc = x.clone().cuda()
     x_out, delta = block.forward(ctx, xc, None, lc)
