@@ -1,18 +1,27 @@
 """Benchmark: decode tokens per second of the Llama-3.1-8B-sized model (random bf16 weights) on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 4096] [--layers L] [--impl ours|reference]
+                    [--preset NAME] [--workload decode|stream]
 
 A "step" is one decode step of `--batch` requests whose contexts end at `--context` tokens. Prints ONE JSON line:
   value      decoded tokens per second, timed on the device (CUDA events around K steps: metadata copy + graph replay)
   e2e        the same through the Python entry point (`LLMEngine.step()`): host token ids in (pinned, copied to the device
              every step), chosen token ids out (copied back every step)
-  prefill    one 2,048-token prompt in one step: tokens per second, and the step's FLOPs / time / the measured bf16 peak
+  prefill    one 2,048-token prompt in one step: tokens per second (median of five runs after a warm-up run), and the
+             step's FLOPs / time / the measured bf16 peak
   roofline   the decode step's bytes (every weight once + the cache of the live requests) / time, against the measured
              copy bandwidth
-  points     decode tokens per second at batch 1 and 64
+  points     decode tokens per second at batch 1 and 64 (contexts ending at `--context`), and at the batch of the main
+             run with contexts at the start (prompt length = half of `--context`) and in the middle of generation;
+             `points_frac` gives each one's fraction of the copy bandwidth
 Peaks come from MEASURED_PEAKS.json beside this file when the driver wrote it, else the fallback figures.
 Weights are N(0, 0.02) drawn on the device, prompts are seeded uniform token ids ("data": "synthetic"); the weights
 (16 GB) are far larger than the L2, so nothing has to be flushed between steps.
+
+`--workload stream` times a continuous-batching stream instead (by default with the Qwen2.5-0.5B sizes): 32 requests
+with prompt lengths uniform in [16, 1024] and 256 new tokens each, one arriving per engine step, through
+`LLMEngine.add_request` / `step()`; the line's value is generated tokens per second of wall clock from the first
+arrival to the last token.
 """
 from __future__ import annotations
 import argparse
@@ -135,6 +144,9 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--reference-device", default="CUDA", help="the reference's device name for --impl reference")
+    ap.add_argument("--workload", default="decode", choices=["decode", "stream"])
+    ap.add_argument("--requests", type=int, default=32, help="stream workload: number of requests")
+    ap.add_argument("--new-tokens", type=int, default=256, help="stream workload: tokens generated per request")
     a = ap.parse_args()
     if a.impl == "reference":
         return reference_arm(a)
@@ -142,6 +154,8 @@ def main() -> int:
         print(f"bench.py: this engine runs on one GPU; --gpus {a.gpus} is not supported")
         return 2
     a.warmup = max(a.warmup, 3)
+    if a.workload == "stream":
+        return stream_workload(a)
 
     import numpy as np
     import torch
@@ -183,12 +197,12 @@ def main() -> int:
             eng.step()
         return rids
 
-    def decode_run(batch: int, steps: int, warmup: int, e2e: bool) -> dict:
-        """Times `steps` decode steps of `batch` requests whose contexts end at a.context."""
+    def decode_run(batch: int, steps: int, warmup: int, e2e: bool, ctx_end: int | None = None) -> dict:
+        """Times `steps` decode steps of `batch` requests whose contexts end at ctx_end (default a.context)."""
         eng = make_engine(batch)
         total = steps + warmup
         runs = 2 if e2e else 1
-        n_prompt = a.context - runs * total - 2
+        n_prompt = (ctx_end or a.context) - runs * total - 2
         rids = prefill_to(eng, batch, n_prompt, max_tokens=runs * total + 2)
         out = {}
         # device-timed: metadata copy + graph replay per step, tokens fixed beforehand, no read-back inside
@@ -246,7 +260,7 @@ def main() -> int:
         eng = make_engine(1)
         ids = rng.integers(0, V, tokens).tolist()
         times = []
-        for i in range(7):      # one warm-up, then the best of six (the clock under the power cap wanders between runs)
+        for i in range(6):      # one warm-up, then the median of five
             rid = eng.add_request(ids, SamplingParams(max_tokens=1, ignore_eos=True))
             torch.cuda.synchronize()
             start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -256,7 +270,7 @@ def main() -> int:
             torch.cuda.synchronize()
             times.append(start.elapsed_time(end))
             eng.release(rid)
-        ms = min(times[1:])
+        ms = sorted(times[1:])[2]
         D, I, Hq = cfg["hidden_size"], cfg["intermediate_size"], cfg["num_attention_heads"]
         lin = 2 * tokens * L * (D * (Hq + 2 * Hkv) * hd + Hq * hd * D + 3 * D * I) + 2 * D * V
         attn = 2 * tokens * tokens * hd * Hq * L     # causal: half of 4 T^2 hd Hq
@@ -269,10 +283,17 @@ def main() -> int:
     main_run = decode_run(a.batch, a.steps, a.warmup, e2e=not a.no_e2e)
     clk = clocks.stop()
     pre = prefill_run(a.prefill_tokens)
-    points = {}
+    points, points_frac = {}, {}
     if not a.no_points:
-        for b in (1, 64):
-            points[f"decode_b{b}"] = round(decode_run(b, max(8, a.steps // 2), a.warmup, e2e=False)["tok_s"], 1)
+        def point(name: str, batch: int, ctx_end: int | None = None) -> None:
+            r = decode_run(batch, max(8, a.steps // 2), a.warmup, e2e=False, ctx_end=ctx_end)
+            points[name] = round(r["tok_s"], 1)
+            points_frac[name] = round(r["bytes"] / (r["ms"] * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+        point("decode_b1", 1)
+        point("decode_b64", 64)
+        # the main batch where generation starts (after a prompt of half the context) and half-way through it
+        point(f"decode_b{a.batch}_ctx_start", a.batch, a.context // 2 + 2 * (max(8, a.steps // 2) + a.warmup))
+        point(f"decode_b{a.batch}_ctx_mean", a.batch, 3 * a.context // 4)
     achieved = main_run["bytes"] / (main_run["ms"] * 1e-3) / 1e9
     line = {
         "metric": "decode_tokens_per_s", "value": round(main_run["tok_s"], 1), "unit": "tok/s", "n_gpus": 1,
@@ -291,6 +312,73 @@ def main() -> int:
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": points,
+        "points_frac": points_frac,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def stream_workload(a) -> int:
+    """A continuous-batching stream (see the module docstring). One JSON line."""
+    import numpy as np
+    import torch
+    from fusezap_core_b200 import LLMEngine, SamplingParams
+    from fusezap_core_b200.cli import load_preset
+    from fusezap_core_b200.engine.model import random_model
+    preset = a.preset if a.preset != "llama-3.1-8b" else "qwen2.5-0.5b"
+    cfg = load_preset(preset)
+    full_layers = cfg["num_hidden_layers"]
+    if a.layers:
+        cfg["num_hidden_layers"] = a.layers
+    max_len = 1024 + a.new_tokens
+    model = random_model(cfg, "bfloat16", "cuda:0", seed=0, max_len=max_len)
+    rng = np.random.default_rng(5)
+    lens = rng.integers(16, 1025, a.requests)
+    prompts = [rng.integers(0, cfg["vocab_size"], int(n)).tolist() for n in lens]
+    params = SamplingParams(max_tokens=a.new_tokens, ignore_eos=True)
+    pages = a.requests * (-(-max_len // a.page_size)) + 8
+
+    def run_once() -> dict:
+        eng = LLMEngine(model, num_blocks=pages, block_size=a.page_size, max_num_seqs=a.requests,
+                        max_prefill_tokens=a.prefill_tokens, max_model_len=max_len)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        nxt = n_tok = n_steps = 0
+        first = {}
+        while nxt < len(prompts) or eng.has_unfinished():
+            if nxt < len(prompts):
+                eng.add_request(prompts[nxt], params)
+                nxt += 1
+            for o in eng.step():
+                n_tok += len(o.new_token_ids)
+                first.setdefault(o.request_id, time.perf_counter() - t0)
+            n_steps += 1
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        return {"s": dt, "tok_s": n_tok / dt, "tokens": n_tok, "steps": n_steps, "stats": dict(eng.stats),
+                "launches": model.ops.launches}
+
+    run_once()                       # warm-up: builds every graph the stream needs
+    clocks = ClockSampler()
+    clocks.start()
+    launches0 = model.ops.launches
+    runs = [run_once() for _ in range(3)]
+    clk = clocks.stop()
+    r = sorted(runs, key=lambda x: x["s"])[1]
+    line = {
+        "metric": "stream_generated_tokens_per_s", "value": round(r["tok_s"], 1), "unit": "tok/s", "n_gpus": 1,
+        "steps": r["steps"], "warmup": 1, "ms_per_step": round(1000 * r["s"] / r["steps"], 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+        "config": {"model": preset, "layers": cfg["num_hidden_layers"], "layers_full": full_layers,
+                   "requests": a.requests, "prompt_len_min": 16, "prompt_len_max": 1024, "new_tokens": a.new_tokens,
+                   "prompt_tokens": int(lens.sum()), "arrivals": "one per engine step", "page_size": a.page_size,
+                   "max_prefill_tokens": a.prefill_tokens, "timing": "wall clock, median of 3 runs after one warm-up run"},
+        "clocks": clk,
+        "e2e": {"value": round(r["tok_s"], 1), "unit": "tok/s", "seconds": round(r["s"], 4),
+                "prompt_tokens_per_s": round(float(lens.sum()) / r["s"], 1)},
+        "gpu_launches": int((model.ops.launches - launches0) // 3),
+        "engine_stats": {k: r["stats"][k] for k in ("steps", "decode_steps", "prefill_steps", "mixed_steps", "graph_replays",
+                                                      "step_graph_replays", "lookahead_steps", "preemptions")},
     }
     print(json.dumps(line))
     return 0

@@ -311,6 +311,7 @@ struct UnitCursor {
   int g, g_end;     // next group of 16 keys in the unit, one past the last
   int page0;        // first block-table entry the unit's groups need ...
   int pages;        // ... and entry page0 + lane of the table (-1 past the row's position), one per lane
+  int first_new;    // the first position of the row's request that this step writes: keys below it are from earlier steps
   bool valid;
 };
 
@@ -407,6 +408,7 @@ attn_decode_units_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_
     // the unit's block-table entries, one per lane (at most 32: 256 keys in pages of 8), asked for now and used
     // when the unit's loads are issued
     if (!with_pages) return;
+    c.first_new = seg[seq_row[n] * 4 + 2];
     c.page0 = (c.key0 + 16 * c.g) / page_size;
     const int pi = c.page0 + lane;
     c.pages = (pi < mb && pi * page_size <= c.p) ? __ldg(table + (size_t)seq_row[n] * mb + pi) : -1;
@@ -453,7 +455,6 @@ attn_decode_units_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_
   load_unit(cc, u_begin, 0, false);
   load_unit(ci, u_begin, 0, true);
   load_unit(cn, u_begin + 1, ci.n, true);
-  fz_grid_wait();      // the queries and the newest keys and values come from the kernels before
   auto advance_loads = [&]() {
     if (++ci.g >= ci.g_end) {
       ci = cn;
@@ -461,6 +462,15 @@ attn_decode_units_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_
     }
   };
   int issued = 0, consumed = 0;
+  // Keys and values below the first position that this step writes for the row's request were written by earlier steps
+  // (a step starts only after the one before it has finished, and nothing in a step writes below that position): the
+  // loads of such groups go out before the wait, so the first stages fill while the kernel before this one finishes.
+  while (ci.valid && issued < NSTAGE && ci.key0 + 16 * ci.g + 15 < ci.first_new) {
+    issue(ci, issued);
+    ++issued;
+    advance_loads();
+  }
+  fz_grid_wait();      // the queries and the newest keys and values come from the kernels before
   int q_n = -1, q_kvh = -1;
   uint32_t qf[KSTEPS][QW];
   float o[OB][4];

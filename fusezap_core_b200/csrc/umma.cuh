@@ -110,6 +110,16 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
+// 16 consecutive 32-bit columns of this thread's TMEM lane, written; complete when the call returns
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 // Shared-memory operand descriptors (64 bits): [0,14) address >> 4, [16,30) leading offset >> 4, [32,46) stride offset
 // >> 4, [46,48) version 1, [61,64) layout 2 = 128-byte swizzle.
 // K-major tile of rows x 64 bf16: rows are 128 bytes apart, 8-row groups 1024 bytes apart (stride offset); the leading

@@ -20,6 +20,7 @@ import time
 CSRC = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "csrc")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
+NVCC_FLAGS += os.environ.get("FZB200_NVCC_EXTRA", "").split()      # extra compiler flags (instrumented builds)
 LIBRARIES: dict[str, list[str]] = {
     "fzb200_core": ["rowwise.cu", "gemm_simt.cu", "attn_simt.cu"],
     "fzb200_tc": ["gemm_tc.cu", "attn_decode.cu", "attn_prefill.cu", "attn_prefill_tc.cu"],          # bfloat16 only: tcgen05 / TMA kernels

@@ -11,11 +11,13 @@ pytestmark = pytest.mark.gpu
 BF = torch.bfloat16
 
 
-def run_both(Hq, Hkv, hd, bs, window, lengths, rows, seed=0):
-    """rows: list of (request, first position, count). Returns (cuda out, plain out, ops)."""
+def run_both(Hq, Hkv, hd, bs, window, lengths, rows, seed=0, prefill_mode=0):
+    """rows: list of (request, first position, count). Returns (cuda out, plain out, ops). prefill_mode: which prompt
+    kernel takes the long portions (0: chosen by shape, 1: one head per block, 2: two heads per block)."""
     from fusezap_core_b200.kernels import cuda_ops
     cu, pl = cuda_ops("bfloat16"), PlainOps(BF)
     assert cu.use_tensor_cores and cu.tc.fz_attn_decode_check(Hq, Hkv, hd) == 0
+    assert cu.tc.fz_attn_prefill_tc_mode(prefill_mode) == 0
     g = torch.Generator().manual_seed(seed + Hq + hd + window)
     mb = -(-max(lengths) // bs)
     pages = mb * len(lengths) + 3
@@ -32,7 +34,10 @@ def run_both(Hq, Hkv, hd, bs, window, lengths, rows, seed=0):
     q = torch.randn(n, Hq * hd, generator=g).to(BF)
     o, op = torch.full((n, Hq * hd), float("nan"), dtype=BF, device="cuda"), torch.empty(n, Hq * hd, dtype=BF)
     scale = hd ** -0.5
-    cu.paged_attention(q.cuda(), cc, Meta(pos, seq_row, table, "cuda"), o, Hq, Hkv, hd, scale, window)
+    try:
+        cu.paged_attention(q.cuda(), cc, Meta(pos, seq_row, table, "cuda"), o, Hq, Hkv, hd, scale, window)
+    finally:
+        cu.tc.fz_attn_prefill_tc_mode(0)
     pl.paged_attention(q, cp, Meta(pos, seq_row, table, "cpu"), op, Hq, Hkv, hd, scale, window)
     cu.check_errors()
     return o.float().cpu(), op.float(), seq_row
@@ -67,15 +72,32 @@ def test_decode_rows_past_4096_keys(Hq, Hkv, hd, bs, window):
     close(o, op, "decode past 4096")
 
 
-@pytest.mark.parametrize("Hq,Hkv,hd", [(4, 1, 128), (14, 2, 64), (8, 8, 64), (2, 1, 128)])
+@pytest.mark.parametrize("mode", [1, 2])
+@pytest.mark.parametrize("Hq,Hkv,hd", [(4, 1, 128), (14, 2, 64), (8, 8, 64), (2, 1, 128), (10, 2, 128), (3, 3, 64)])
 @pytest.mark.parametrize("bs,window", [(16, 0), (8, 100), (3, 0), (64, 0), (128, 90), (48, 0)])
-def test_prefill_portions(Hq, Hkv, hd, bs, window):
+def test_prefill_portions(Hq, Hkv, hd, bs, window, mode):
+    """Both prompt kernels (one head per block, two heads of a kv head per block) on the same inputs: groups of 1, 2, 3,
+    4, 5 and 7 query heads per kv head (odd groups leave a block with a single head), both head sizes."""
     lengths = [400, 70, 200]
     # a first portion from position 0 (three tiles), a later portion that continues a request (ragged last tile),
     # a portion of exactly 8 rows, and single tokens beside them (mixed step)
     rows = [(0, 0, 150), (2, 61, 139), (1, 62, 8), (0, 399, 1), (1, 30, 1)]
-    o, op, _ = run_both(Hq, Hkv, hd, bs, window, lengths, rows)
+    o, op, _ = run_both(Hq, Hkv, hd, bs, window, lengths, rows, prefill_mode=mode)
     close(o, op, "prefill")
+
+
+@pytest.mark.parametrize("Hq,Hkv,hd,window", [(8, 2, 128, 0), (5, 1, 128, 700), (14, 2, 64, 0)])
+def test_prefill_kernels_agree_on_long_portions(Hq, Hkv, hd, window):
+    """A 1,300-token portion behind 900 cached tokens (eleven key tiles, through the lazy rescaling of the output many
+    times) and a second request: the two prompt kernels do the same arithmetic in the same order, so they give the same
+    bits, and both follow the plain reference."""
+    lengths = [2200, 517]
+    rows = [(0, 900, 1300), (1, 0, 517)]
+    one, ref, _ = run_both(Hq, Hkv, hd, 16, window, lengths, rows, seed=5, prefill_mode=1)
+    two, _, _ = run_both(Hq, Hkv, hd, 16, window, lengths, rows, seed=5, prefill_mode=2)
+    close(one, ref, "one head per block")
+    close(two, ref, "two heads per block")
+    assert torch.equal(one, two)
 
 
 def test_padding_rows_and_row_independence():
