@@ -600,6 +600,206 @@ int launch_rows(const CUtensorMap& mx, const CUtensorMap& mw, const Params& p, i
   return FZ_OK;
 }
 
+// ---------------------------------------------------------------------------------------------- rows mode, K split
+// C[rows, feats] = X . W^T (+ bias) for a few hundred token rows, where the 128 x 256 output tiles are far fewer than the
+// SMs: a tile's range of K is cut into `splits` pieces, one CTA each, and the CTAs of a tile form a thread-block cluster.
+// A CTA can draw operands from L2 / HBM only at the rate its shared-memory ring and the memory latency allow (about
+// 90 GB/s), so a tile that walks a long K alone takes its bytes / that rate, whatever the tensor core could do; cut in
+// pieces, more SMs draw at once. Every CTA leaves its float32 partial tile in its own shared memory (row-major, rows
+// padded by four floats so that neither the writes nor the reads collide on the banks); after a cluster barrier CTA r
+// adds, for its share of the tile's columns, the partials of all splits in split order through distributed shared
+// memory, adds the bias and stores. No partial goes to global memory; the sum has one fixed order.
+constexpr int SPLIT_BN = 256;
+constexpr int SPLIT_LD = SPLIT_BN + 4;      // floats per row of the partial tile
+
+__device__ __forceinline__ float4 ld_dsmem_v4(uint32_t addr, uint32_t rank) {
+  uint32_t remote;
+  float4 v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote));
+  return v;
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_rows_split_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const Params p) {
+  constexpr int BN = SPLIT_BN;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+  uint64_t* full = (uint64_t*)(smem + (size_t)p.stages * STAGE_BYTES);
+  uint64_t* empty = full + p.stages;
+  uint64_t* acc_ready = empty + p.stages;
+  uint32_t* tmem_slot = (uint32_t*)(acc_ready + 1);
+  int* flag = (int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tm = blockIdx.x, tn = blockIdx.y, split = blockIdx.z;
+  const int kblocks = (p.K + BK - 1) / BK;
+  const int kb0 = (int)((long long)kblocks * split / p.splits), kb1 = (int)((long long)kblocks * (split + 1) / p.splits);
+  const int nkb = kb1 - kb0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    mbar_init(acc_ready, 1);
+    flag[0] = 0;
+    mbar_init_fence();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, BN);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_d = *tmem_slot;
+  fz_grid_launch_dependents();
+  if (warp != 0) fz_grid_wait();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // the weights of the first stages before the wait on the previous kernel (they do not depend on it)
+      const int early = nkb < p.stages ? nkb : p.stages;
+      for (int i = 0; i < early; ++i) {
+        mbar_expect_tx(&full[i], STAGE_BYTES);
+        tma_load_2d(smem + (size_t)i * STAGE_BYTES + A_BYTES, &map_w, &full[i], (kb0 + i) * BK, tn * BN);
+      }
+      fz_grid_wait();
+      for (int i = 0, s = 0, round = 0; i < nkb; ++i) {
+        uint8_t* sa = smem + (size_t)s * STAGE_BYTES;
+        if (round > 0) {
+          if (!mbar_wait(&empty[s], (round - 1) & 1)) { flag[0] = 1; break; }
+          mbar_expect_tx(&full[s], STAGE_BYTES);
+          tma_load_2d(sa + A_BYTES, &map_w, &full[s], (kb0 + i) * BK, tn * BN);
+        }
+        tma_load_2d(sa, &map_x, &full[s], (kb0 + i) * BK, tm * BM);
+        if (++s == p.stages) { s = 0; ++round; }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(BM, BN);
+      for (int i = 0, s = 0, round = 0; i < nkb; ++i) {
+        if (!mbar_wait(&full[s], round & 1)) { flag[0] = 1; break; }
+        tc_fence_after();
+        const uint8_t* sa = smem + (size_t)s * STAGE_BYTES;
+        const uint64_t da = desc_k_major(smem_u32(sa)), db = desc_k_major(smem_u32(sa + A_BYTES));
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k)
+          umma_bf16(tmem_d, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (i > 0 || k > 0) ? 1u : 0u);
+        umma_commit(&empty[s]);
+        if (++s == p.stages) { s = 0; ++round; }
+      }
+      umma_commit(acc_ready);
+    }
+  } else {
+    // the accumulator -> this CTA's partial tile in shared memory (every stage has been consumed by now)
+    const int quad = warp & 3, r = quad * 32 + lane;
+    const bool ok = __all_sync(0xffffffffu, mbar_wait(acc_ready, 0));
+    if (!ok) flag[0] = 1;
+    tc_fence_after();
+    const uint32_t taddr = tmem_d + ((uint32_t)(quad * 32) << 16);
+    float* part = (float*)smem + (size_t)r * SPLIT_LD;
+    float v[16];
+#pragma unroll 1
+    for (int c = 0; c < BN; c += 16) {
+      if (ok && nkb > 0) tmem_ld16(taddr + (uint32_t)c, v);
+      else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 16; j += 4) *(float4*)(part + c + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+    }
+  }
+  // every thread of every CTA of the cluster passes both cluster barriers; only the epilogue warps work between them
+  cluster_sync_all();
+  if (warp >= 2) {
+    const int r = (warp & 3) * 32 + lane;
+    const int row = tm * BM + r;
+    const uint32_t rank = cluster_rank();
+    // this CTA's share of the tile's columns, in groups of four
+    const int groups = BN / 4;
+    const int g0 = (int)((long long)groups * rank / p.splits), g1 = (int)((long long)groups * (rank + 1) / p.splits);
+    const uint32_t base = smem_u32(smem) + (uint32_t)r * (uint32_t)(SPLIT_LD * 4);
+    if (row < p.rows) {
+#pragma unroll 2
+      for (int g = g0; g < g1; ++g) {
+        const int c = 4 * g, n = tn * BN + c;
+        if (n >= p.feats) break;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 v[8];
+#pragma unroll
+        for (int sp = 0; sp < 8; ++sp)
+          v[sp] = sp < p.splits ? ld_dsmem_v4(base + (uint32_t)c * 4u, (uint32_t)sp) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int sp = 0; sp < 8; ++sp) { acc.x += v[sp].x; acc.y += v[sp].y; acc.z += v[sp].z; acc.w += v[sp].w; }
+        float y[4] = {acc.x, acc.y, acc.z, acc.w};
+        if (p.vec_ok && n + 4 <= p.feats) {
+          if (p.bias) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) y[j] += p.bias[n + j];
+          }
+          if (p.c_f32) {
+            *(float4*)(p.c_f32 + (size_t)row * p.feats + n) = make_float4(y[0], y[1], y[2], y[3]);
+          } else {
+            const __nv_bfloat162 lo = __floats2bfloat162_rn(y[0], y[1]), hi = __floats2bfloat162_rn(y[2], y[3]);
+            *(uint2*)(p.c_bf16 + (size_t)row * p.feats + n) = make_uint2(*(const uint32_t*)&lo, *(const uint32_t*)&hi);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (n + j < p.feats) {
+              const float yj = y[j] + (p.bias ? p.bias[n + j] : 0.f);
+              if (p.c_f32) p.c_f32[(size_t)row * p.feats + n + j] = yj;
+              else p.c_bf16[(size_t)row * p.feats + n + j] = __float2bfloat16_rn(yj);
+            }
+          }
+        }
+      }
+    }
+  }
+  cluster_sync_all();      // nobody leaves while its shared memory may still be read
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_d, BN);
+  }
+  if (threadIdx.x == 0 && flag[0]) atomicOr(p.err, FZ_ERR_WAIT_TIMEOUT);
+}
+
+int launch_rows_split(const CUtensorMap& mx, const CUtensorMap& mw, const Params& p, int tiles_m, int tiles_n, cudaStream_t stream) {
+  constexpr int STAGE_BYTES = (BM + SPLIT_BN) * BK * 2;
+  const size_t ring = (size_t)p.stages * STAGE_BYTES, partial = (size_t)BM * SPLIT_LD * 4;
+  const size_t smem = (ring > partial ? ring : partial) + 1024 + 8 * (2 * p.stages + 1) + 16;
+  static size_t allowed = 48 * 1024;
+  if (smem > allowed) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_rows_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    allowed = smem;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(tiles_m, tiles_n, p.splits);
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (fz_pdl_enabled()) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  attr[na].id = cudaLaunchAttributeClusterDimension;
+  attr[na].val.clusterDim.x = 1;
+  attr[na].val.clusterDim.y = 1;
+  attr[na].val.clusterDim.z = (unsigned)p.splits;
+  ++na;
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_tc_rows_split_kernel, mx, mw, p);
+  if (le != cudaSuccess) return (int)le;
+  FZ_LAUNCH_CHECK();
+  return FZ_OK;
+}
+
 // ---------------------------------------------------------------------------------------------- host side
 template <int BN>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, dim3 grid, cudaStream_t stream) {
@@ -665,6 +865,26 @@ FZ_API int fz_gemm_tc_splits(int N, int K) {
   if (s > kblocks / 4) s = kblocks / 4;
   if (s > 8) s = 8;                  // a portable cluster holds at most 8 CTAs
   return s < 1 ? 1 : s;
+}
+
+// The number of K pieces a product of M > 128 token rows is cut into (1: not cut): only where the 128 x 256 tiles are at
+// most half as many as the SMs, no piece shorter than 8 k-blocks of 64, and a power of two: with one CTA per SM, clusters
+// of three do not pack the GPCs (measured: 48 clusters of 3 need a second wave, 45 us for the 256 x 6144 x 4096 product
+// where 48 of 2 take 29), clusters of 4 and 8 do as long as they cover at most 128 SMs.
+FZ_API int fz_gemm_tc_rows_splits(int M, int N, int K) {
+  if (M <= BM || N < 256) return 1;
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+      sms = 148;
+  }
+  const long long tiles = (long long)((M + BM - 1) / BM) * ((N + 255) / 256);
+  const int kblocks = (K + BK - 1) / BK;
+  if (2 * tiles > sms) return 1;
+  for (int s = 8; s >= 2; s >>= 1)
+    if (tiles * s <= (s == 2 ? sms : 128) && kblocks / 8 >= s) return s;
+  return 1;
 }
 
 // x: [M, K] bf16, w: [N, K] bf16, bias: [N] float32 or null, c: [M, N] float32 (out_dtype 0) or bf16 (1).
@@ -803,6 +1023,19 @@ static int gemm_tc_impl(const void* x, const void* w, const float* bias, void* c
   // rows mode: token rows are the 128 lanes; persistent CTAs with two accumulators
   p.swap = 0;
   int bn = N >= 256 ? 256 : N >= 128 ? 128 : 64;     // with the fused SwiGLU N = 2 I >= 128, so a tile holds whole blocks
+  if (bn == 256 && !p.swiglu) {
+    // So few 128 x 256 tiles that the SMs are not half used, and a K worth cutting: the tiles' K ranges are cut so that
+    // about one CTA per SM works (see `gemm_tc_rows_split_kernel`). The count follows from (M, N, K) of the product.
+    const int splits = fz_gemm_tc_rows_splits(M, N, K);
+    if (splits > 1) {
+      p.splits = splits;
+      const int stage = (BM + SPLIT_BN) * BK * 2;
+      p.stages = (200 * 1024) / stage;
+      if ((st = get_map_bf16(x, M, K, BM, &ma)) != FZ_OK) return st;
+      if ((st = get_map_bf16(w, N, K, SPLIT_BN, &mb)) != FZ_OK) return st;
+      return launch_rows_split(ma, mb, p, (M + BM - 1) / BM, (N + SPLIT_BN - 1) / SPLIT_BN, stream);
+    }
+  }
   if (bn == 256 && !p.swiglu) {
     // Few token rows: when the 256-wide tiles do not fill the SMs even once, the narrowest width that still fits one
     // round is the fastest (256 x 4096 x 4096 is 32 tiles of 256 columns for 148 SMs, but 52 of 160). Not below 160:

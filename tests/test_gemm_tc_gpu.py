@@ -48,6 +48,8 @@ def test_few_rows(M, N, K):
                                    # fewer tiles than SMs, or a partial last round, with a long K
                                    (256, 4096, 4096), (512, 6144, 4096), (200, 1000, 8192), (2048, 4096, 4096), (640, 4096, 1024),
                                    (512, 8192, 512),      # tiles 160, 192, 160, 256, 160 and 224 columns wide
+                                   # few tiles and a long K: the K range of a tile is cut over a cluster of 2 to 8 CTAs
+                                   (300, 4096, 14336), (384, 777, 1024), (130, 256, 8200), (256, 6144, 4096),
                                    # many rounds and a short K
                                    (150, 151936, 896)])
 def test_many_rows(M, N, K):
@@ -56,6 +58,15 @@ def test_many_rows(M, N, K):
         err, scale = check(out, ref, K)
         lim = 1e-4 * scale if out_dtype == torch.float32 else 2.0 ** -8 * scale
         assert err <= lim, f"M={M} N={N} K={K} {out_dtype}: max |diff| {err:.3e} > {lim:.3e}"
+
+
+def test_which_products_are_cut_along_k():
+    from fusezap_core_b200.kernels import cuda_ops
+    tc = cuda_ops("bfloat16").tc
+    assert tc.fz_gemm_tc_rows_splits(256, 6144, 4096) == 2 and tc.fz_gemm_tc_rows_splits(256, 4096, 14336) == 4
+    assert tc.fz_gemm_tc_rows_splits(200, 1000, 8192) == 8 and tc.fz_gemm_tc_rows_splits(384, 777, 1024) == 2
+    for M, N, K in ((2048, 4096, 4096), (512, 6144, 4096), (128, 4096, 4096), (256, 4096, 256), (256, 128, 4096)):
+        assert tc.fz_gemm_tc_rows_splits(M, N, K) == 1, (M, N, K)
 
 
 def test_a_row_does_not_depend_on_the_other_rows():
