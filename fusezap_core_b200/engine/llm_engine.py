@@ -299,18 +299,22 @@ class LLMEngine:
         key = None
         if bucket is not None:
             key = (bucket, self._greedy_step, self._ids_only, self._filtered_step)
+            # a captured decode step must cover every context it may be replayed with (its launch sizes are fixed)
+            runner.meta.max_context = self.max_model_len
         elif self.cuda_graphs and runner.meta.n_rows <= self.graph_rows:
             m = runner.meta
-            sig = ("step", m.n_rows, m.n_wanted, *getattr(ops, "step_signature", lambda _: ())(m), self._greedy_step,
+            # Other captured steps cover contexts up to the next power of two (at least 1,024) of the step's own, which is
+            # part of their key: kernels size their scratch by rows x the context covered, and a step of a few hundred
+            # rows sized for the whole `max_model_len` would hold hundreds of megabytes at long model lengths.
+            covered = min(self.max_model_len, max(1024, 1 << (max(m.max_context, 1) - 1).bit_length()))
+            sig = ("step", m.n_rows, m.n_wanted, covered, *getattr(ops, "step_signature", lambda _: ())(m), self._greedy_step,
                    self._ids_only, self._filtered_step)
             if len(self._step_seen) > 4096:
                 self._step_seen.clear()
             self._step_seen[sig] = self._step_seen.get(sig, 0) + 1
             if sig in self._graphs or self._step_seen[sig] >= 2:
                 key = sig
-        if key is not None:
-            # a captured step must cover every context it may be replayed with (its launch sizes are fixed)
-            runner.meta.max_context = self.max_model_len
+                m.max_context = covered
         n_w = runner.meta.n_wanted
         if n_w:
             temp_h[R:n_w] = 0.0

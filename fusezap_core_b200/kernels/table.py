@@ -13,6 +13,7 @@ import torch
 
 from .build import load
 from .interface import Ops
+from .profile import contexts, ideal_linear_bytes
 
 F32, BF16 = 0, 1
 _CODE = {torch.float32: F32, torch.bfloat16: BF16}
@@ -216,7 +217,8 @@ class CudaOps(Ops):
             raise KernelError(f"add_rmsnorm: h {tuple(h.shape)}, expected {(n_out, d)}; weight {tuple(weight.shape)}")
         self._check(self.core.fz_add_rmsnorm(_p(x), _p(delta), _p(weight), c_int(_CODE[weight.dtype]), _p(h),
                                              c_int(_CODE[h.dtype]), _p(rows), c_int(n_out), c_int(n_src), c_int(d),
-                                             c_float(eps), _p(self.err), self._stream()), "add_rmsnorm")
+                                             c_float(eps), _p(self.err), self._stream()), "add_rmsnorm",
+                    n_out * d * (4 + (8 if delta is not None and rows is None else 4 if delta is not None else 0) + h.element_size()))
 
     def linear(self, a, w, bias, out) -> None:
         self._want(a, "linear input", (self.dtype,), 2)
@@ -234,11 +236,12 @@ class CudaOps(Ops):
         if self.use_tensor_cores and self.tc.fz_gemm_tc_check(_p(a), _p(w), c_int(m), c_int(n), c_int(k)) == 0:
             self._check(self.tc.fz_gemm_tc(
                 _p(a), _p(w), _p(bias), _p(out), c_int(_CODE[out.dtype]), c_int(m), c_int(n), c_int(k),
-                _p(self.err), self._stream()), "linear (tensor cores)")
+                _p(self.err), self._stream()), "linear (tensor cores)",
+                ideal_linear_bytes(m, n, k, 2, 2, out.element_size()))
             return
         self._check(self.core.fz_gemm_simt(_p(a), _p(w), _p(bias), _p(out), c_int(_CODE[a.dtype]),
                                            c_int(_CODE[out.dtype]), c_int(m), c_int(n), c_int(k), self._stream()),
-                    "linear")
+                    "linear", ideal_linear_bytes(m, n, k, a.element_size(), w.element_size(), out.element_size()))
 
     def linear_add(self, a, w, bias, x) -> bool:
         m, k = a.shape
@@ -278,7 +281,8 @@ class CudaOps(Ops):
         if w.shape != (2 * i, k) or out.shape != (m, i):
             raise KernelError(f"linear_swiglu: a {tuple(a.shape)}, packed {tuple(w.shape)}, out {tuple(out.shape)}")
         self._check(self.tc.fz_gemm_tc_swiglu(_p(a), _p(w), _p(b), _p(out), c_int(m), c_int(i), c_int(k), _p(self.err),
-                                              self._stream()), "linear_swiglu (tensor cores)")
+                                              self._stream()), "linear_swiglu (tensor cores)",
+                    ideal_linear_bytes(m, 2 * i, k, 2, 2, 1))
 
     def _pool(self, cache, hkv: int, hd: int):
         k, v = cache.keys, cache.values
@@ -334,7 +338,8 @@ class CudaOps(Ops):
             _p(a), _p(w), _p(bias), c_int(m), c_int(k), _p(cos), _p(sin), _p(meta.pos), _p(meta.seq_row), _p(table),
             c_int(table.shape[1]), _p(kp), _p(vp), c_longlong(page_stride), c_int(cache.page_size),
             c_int(1 if cache.write else 0), _p(q_out), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
-            c_int(cos.shape[0]), _p(self.err), self._stream()), "linear_rope_kv_write (tensor cores)")
+            c_int(cos.shape[0]), _p(self.err), self._stream()), "linear_rope_kv_write (tensor cores)",
+            ideal_linear_bytes(m, n, k, 2, 2, 2))
         return True
 
     def linear_argmax(self, a, w, bias, out) -> bool:
@@ -356,7 +361,7 @@ class CudaOps(Ops):
         tile_idx = self._scratch("lm_head tile indices", need, torch.int32)
         self._check(self.tc.fz_gemm_tc_argmax(_p(a), _p(w), _p(bias), c_int(m), c_int(n), c_int(k), _p(tile_val),
                                               _p(tile_idx), _p(out), _p(self.err), self._stream()),
-                    "linear_argmax (tensor cores)")
+                    "linear_argmax (tensor cores)", ideal_linear_bytes(m, n, k, 2, 2, 0))
         self.launches += 1     # the reduction over the tiles
         return True
 
@@ -371,6 +376,10 @@ class CudaOps(Ops):
         self._attention(q, k, v, page_stride, cache, meta, table, out, n, num_heads, num_kv_heads, head_dim, scale, window)
 
     def _attention(self, q, k, v, page_stride, cache, meta, table, out, n, hq, hkv, hd, scale, window) -> None:
+        # least bytes: the keys and values every row may see (each once per row), the queries and the output
+        kv = 0
+        if self._profile is not None:
+            kv = contexts(getattr(meta, "segments", ())) * hkv * hd * 2 * k.element_size() + 2 * n * hq * hd * q.element_size()
         if self.use_tensor_cores and self.tc.fz_attn_decode_check(c_int(hq), c_int(hkv), c_int(hd)) == 0:
             plan = meta.plan
             if plan is None:
@@ -385,7 +394,8 @@ class CudaOps(Ops):
                     _p(q), _p(k), _p(v), _p(meta.pos), _p(meta.seq_row), _p(meta.seg), _p(table), c_int(table.shape[1]),
                     c_longlong(page_stride), c_int(cache.page_size), _p(out), _p(part_o), _p(part_ml), c_int(n),
                     c_int(hq), c_int(hkv), c_int(hd), c_float(scale), c_int(window), c_int(meta.max_context),
-                    c_int(LONG_PORTION), c_int(k.shape[0]), _p(self.err), self._stream()), "paged_attention (decode)")
+                    c_int(LONG_PORTION), c_int(k.shape[0]), _p(self.err), self._stream()), "paged_attention (decode)",
+                    kv if plan.n_tiles == 0 else 0)
                 self.launches += 1    # the combine kernel
             if plan.n_tiles > 0 and self.prefill_tcgen05 and \
                     self.tc.fz_attn_prefill_tc_check(c_int(hq), c_int(hkv), c_int(hd), c_int(cache.page_size)) == 0:
@@ -394,7 +404,7 @@ class CudaOps(Ops):
                     _p(q), c_int(n), _p(k), _p(v), c_longlong(page_stride), c_int(k.shape[0]), _p(meta.seg), _p(plan.tiles),
                     c_int(plan.n_tiles), _p(table), c_int(table.shape[1]), c_int(cache.page_size), _p(out), c_int(hq),
                     c_int(hkv), c_int(hd), c_float(scale), c_int(window), _p(self.err), self._stream()),
-                    "paged_attention (prefill, tcgen05)")
+                    "paged_attention (prefill, tcgen05)", kv)
             elif plan.n_tiles > 0:
                 self._check(self.tc.fz_attn_prefill(
                     _p(q), _p(k), _p(v), _p(meta.seg), _p(plan.tiles), c_int(plan.n_tiles), _p(table),
@@ -404,7 +414,7 @@ class CudaOps(Ops):
         self._check(self.core.fz_attn_simt(
             _p(q), _p(k), _p(v), _p(meta.pos), _p(meta.seq_row), _p(table), c_int(table.shape[1]),
             c_longlong(page_stride), c_int(cache.page_size), _p(out), c_int(_CODE[self.dtype]), c_int(n), c_int(hq),
-            c_int(hkv), c_int(hd), c_float(scale), c_int(window), _p(self.err), self._stream()), "paged_attention")
+            c_int(hkv), c_int(hd), c_float(scale), c_int(window), _p(self.err), self._stream()), "paged_attention", kv)
 
     def swiglu(self, gate_up, out) -> None:
         self._want(gate_up, "gate_up", (self.dtype,), 2)

@@ -13,6 +13,10 @@ from .params import ParamSpec
 from .safetensors_io import read_model_dir
 
 _FLOATS = (torch.float64, torch.float32, torch.float16, torch.bfloat16)
+# Buffers that some exporters write beside the parameters and that no model reads (they are recomputed from config.json):
+# a tensor whose name ends in one of these is passed over instead of being reported as unexpected. (The reference loads
+# by name and ignores every extra tensor; here any other extra tensor is an error.)
+NON_PARAMETER_SUFFIXES = ("rotary_emb.inv_freq",)
 TORCH_DTYPE = {"float32": torch.float32, "bfloat16": torch.bfloat16}
 
 
@@ -47,7 +51,7 @@ def check_tensors(expected: dict[str, ParamSpec], found: dict[str, torch.Tensor]
             wrong.append(f"{name}: dtype {t.dtype}, expected an integer table")
         elif p.role != "int_table" and t.dtype not in _FLOATS:
             wrong.append(f"{name}: dtype {t.dtype}, expected a floating-point tensor")
-    unexpected = sorted(n for n in found if n not in expected)
+    unexpected = sorted(n for n in found if n not in expected and not n.endswith(NON_PARAMETER_SUFFIXES))
     if missing or unexpected or wrong:
         raise WeightsError(missing, unexpected, wrong, where)
 

@@ -73,14 +73,16 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
     w = read_weights(d)
     del w["model.layers.1.mlp.up_proj.weight"]
     del w["model.layers.2.self_attn.k_proj.bias"]                      # breaks an all-or-none group
-    w["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(16)
+    w["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(16)    # a buffer some exporters write: passed over
+    w["model.layers.0.self_attn.extra_gate.weight"] = torch.zeros(16)
     w["model.norm.weight"] = torch.ones(97)
     write_file(os.path.join(d, "model.safetensors"), w)
     with pytest.raises(WeightsError) as e:
         load_model(d, "float32", "cpu", ops=PlainOps())
     msg = str(e.value)
     assert "model.layers.1.mlp.up_proj.weight" in msg and "model.layers.2.self_attn.k_proj.bias" in msg
-    assert "rotary_emb.inv_freq" in msg and "model.norm.weight: shape (97,), expected (96,)" in msg
+    assert "extra_gate.weight" in msg and "rotary_emb.inv_freq" not in msg
+    assert "model.norm.weight: shape (97,), expected (96,)" in msg
     assert e.value.missing and e.value.unexpected and e.value.wrong
     assert "missing (2)" in msg and "unexpected (1)" in msg and "wrong shape or dtype (1)" in msg
 
