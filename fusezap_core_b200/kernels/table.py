@@ -376,10 +376,14 @@ class CudaOps(Ops):
         self._attention(q, k, v, page_stride, cache, meta, table, out, n, num_heads, num_kv_heads, head_dim, scale, window)
 
     def _attention(self, q, k, v, page_stride, cache, meta, table, out, n, hq, hkv, hd, scale, window) -> None:
-        # least bytes: the keys and values every row may see (each once per row), the queries and the output
-        kv = 0
+        # least bytes: keys and values (a short row reads every key it sees; the rows of a long portion share them, so its
+        # keys count once), the queries and the output
+        kv = kv_tiles = 0
         if self._profile is not None:
-            kv = contexts(getattr(meta, "segments", ())) * hkv * hd * 2 * k.element_size() + 2 * n * hq * hd * q.element_size()
+            segs = list(getattr(meta, "segments", ()))
+            key_bytes = hkv * hd * 2 * k.element_size()
+            kv = contexts([sg for sg in segs if sg.n < LONG_PORTION]) * key_bytes + 2 * n * hq * hd * q.element_size()
+            kv_tiles = sum(sg.pos0 + sg.n for sg in segs if sg.n >= LONG_PORTION) * key_bytes
         if self.use_tensor_cores and self.tc.fz_attn_decode_check(c_int(hq), c_int(hkv), c_int(hd)) == 0:
             plan = meta.plan
             if plan is None:
@@ -394,8 +398,7 @@ class CudaOps(Ops):
                     _p(q), _p(k), _p(v), _p(meta.pos), _p(meta.seq_row), _p(meta.seg), _p(table), c_int(table.shape[1]),
                     c_longlong(page_stride), c_int(cache.page_size), _p(out), _p(part_o), _p(part_ml), c_int(n),
                     c_int(hq), c_int(hkv), c_int(hd), c_float(scale), c_int(window), c_int(meta.max_context),
-                    c_int(LONG_PORTION), c_int(k.shape[0]), _p(self.err), self._stream()), "paged_attention (decode)",
-                    kv if plan.n_tiles == 0 else 0)
+                    c_int(LONG_PORTION), c_int(k.shape[0]), _p(self.err), self._stream()), "paged_attention (decode)", kv)
                 self.launches += 1    # the combine kernel
             if plan.n_tiles > 0 and self.prefill_tcgen05 and \
                     self.tc.fz_attn_prefill_tc_check(c_int(hq), c_int(hkv), c_int(hd), c_int(cache.page_size)) == 0:
@@ -404,7 +407,7 @@ class CudaOps(Ops):
                     _p(q), c_int(n), _p(k), _p(v), c_longlong(page_stride), c_int(k.shape[0]), _p(meta.seg), _p(plan.tiles),
                     c_int(plan.n_tiles), _p(table), c_int(table.shape[1]), c_int(cache.page_size), _p(out), c_int(hq),
                     c_int(hkv), c_int(hd), c_float(scale), c_int(window), _p(self.err), self._stream()),
-                    "paged_attention (prefill, tcgen05)", kv)
+                    "paged_attention (prefill, tcgen05)", kv_tiles)
             elif plan.n_tiles > 0:
                 self._check(self.tc.fz_attn_prefill(
                     _p(q), _p(k), _p(v), _p(meta.seg), _p(plan.tiles), c_int(plan.n_tiles), _p(table),
