@@ -104,8 +104,16 @@ class KVGroup:
         return s[:, 0], s[:, 1]
 
 
+def state_shape_dtype(need: Any) -> tuple[tuple[int, ...], torch.dtype]:
+    """A mixer declares a piece of state as a shape (float32) or as (shape, torch dtype)."""
+    if len(need) == 2 and isinstance(need[1], torch.dtype):
+        return tuple(int(x) for x in need[0]), need[1]
+    return tuple(int(x) for x in need), torch.float32
+
+
 class StateSlots:
-    """Slots of fixed size for per-request state. `tensors[(entry, name)]` is (num_slots, *shape) float32."""
+    """Slots of fixed size for per-request state. `tensors[(entry, name)]` is (num_slots, *shape) in the dtype the mixer
+    declared (float32 unless it says otherwise)."""
     def __init__(self, num_slots: int):
         self.num_slots = num_slots
         self._free = list(range(num_slots - 1, -1, -1))
@@ -138,7 +146,8 @@ class CacheManager:
     def __init__(self, needs: dict[int, KVNeed], state_needs: dict[tuple[int, str], tuple[int, ...]], page_size: int,
                  num_pages: int, max_requests: int, max_model_len: int, dtype: torch.dtype,
                  device: torch.device | str, allocate: bool = True):
-        """needs: cache slot id -> KVNeed. state_needs: (schedule entry, name) -> shape of one request's state.
+        """needs: cache slot id -> KVNeed. state_needs: (schedule entry, name) -> shape of one request's state (float32),
+        or (shape, torch dtype).
         num_pages is the page count of every group (a window group never needs more than a full one)."""
         if page_size <= 0:
             raise ValueError(f"page_size must be positive, got {page_size}")
@@ -157,8 +166,9 @@ class CacheManager:
             for grp in self.groups:
                 grp.pool = torch.zeros((len(grp.slots), num_pages, 2, grp.need.num_kv_heads, page_size, grp.need.head_dim),
                                        dtype=dtype, device=self.device)
-            for key, shape in state_needs.items():
-                self.states.tensors[key] = torch.zeros((max_requests, *shape), dtype=torch.float32, device=self.device)
+            for key, need in state_needs.items():
+                shape, state_dtype = state_shape_dtype(need)
+                self.states.tensors[key] = torch.zeros((max_requests, *shape), dtype=state_dtype, device=self.device)
         self.has_state = bool(state_needs)
 
     # ---- capacity

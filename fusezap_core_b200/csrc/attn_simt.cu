@@ -1,8 +1,8 @@
 // Paged attention with 32-bit arithmetic on CUDA cores: the attention of the float32 path (prompt portions and decoded
 // tokens alike), and the general fallback of the bfloat16 path.
 //
-// One block per (token row, kv head); warp w serves the query heads w, w + W, ... of that kv head's group, so the
-// group shares every key/value load. Keys are walked in chunks of 32 whose boundaries are multiples of 32 in absolute
+// One block per (token row, kv head, slice of up to 32 query heads of that kv head's group); warp w serves the query
+// heads w, w + W, ... of the slice, so they share every key/value load. Any number of heads and any group size. Keys are walked in chunks of 32 whose boundaries are multiples of 32 in absolute
 // position: chunk c holds keys 32c .. 32c+31, lane j scores key 32c+j, and the running (max, sum, accumulator) is
 // updated chunk by chunk in rising c. The order of every sum therefore depends only on the row's own position and
 // window, never on the batch, the cut of the prompt or the pages used (the reference's general kernel stages 32-key
@@ -16,7 +16,9 @@
 namespace {
 constexpr int CHUNK = 32;
 constexpr int MAX_WARPS = 8;
-constexpr int MAX_HPW = 4;   // query heads per warp -> groups of up to 32 query heads per kv head
+constexpr int MAX_HPW = 4;   // query heads per warp -> up to 32 query heads per block; larger groups take more blocks
+constexpr int MAX_GROUP = MAX_WARPS * MAX_HPW;
+constexpr int MAX_HD = 512;
 
 template <typename T, int DPL>   // DPL: output dims per lane = ceil(hd / 32)
 __global__ void attn_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, const T* __restrict__ v_pool,
@@ -27,13 +29,14 @@ __global__ void attn_simt_kernel(const T* __restrict__ q, const T* __restrict__ 
   fz_grid_wait();
   extern __shared__ float smem[];
   const int n = blockIdx.x, kvh = blockIdx.y;
-  const int G = Hq / Hkv;
+  const int G_all = Hq / Hkv, g_base = blockIdx.z * MAX_GROUP;
+  const int G = min(MAX_GROUP, G_all - g_base);           // the query heads of this block: g_base .. g_base + G - 1 of the group
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, W = blockDim.x >> 5;
   const int kstride = hd + 1;
   float* Ks = smem;                       // [CHUNK][hd + 1]
   float* Vs = Ks + CHUNK * kstride;       // [CHUNK][hd]
   float* Qs = Vs + CHUNK * hd;            // [G][hd]
-  T* orow = out + (size_t)n * Hq * hd + (size_t)kvh * G * hd;
+  T* orow = out + (size_t)n * Hq * hd + ((size_t)kvh * G_all + g_base) * hd;
   const int row = seq_row[n];
   if (row < 0) {
     for (int i = threadIdx.x; i < G * hd; i += blockDim.x) orow[i] = Cvt<T>::from_f(0.f);
@@ -41,7 +44,7 @@ __global__ void attn_simt_kernel(const T* __restrict__ q, const T* __restrict__ 
   }
   const int p = pos[n];
   const int lo = window > 0 ? max(0, p - window + 1) : 0;
-  const T* qrow = q + (size_t)n * Hq * hd + (size_t)kvh * G * hd;
+  const T* qrow = q + (size_t)n * Hq * hd + ((size_t)kvh * G_all + g_base) * hd;
   for (int i = threadIdx.x; i < G * hd; i += blockDim.x) Qs[i] = Cvt<T>::to_f(qrow[i]);
 
   float m[MAX_HPW], l[MAX_HPW], acc[MAX_HPW][DPL];
@@ -120,7 +123,7 @@ template <typename T, int DPL>
 int launch(const void* q, const void* k_pool, const void* v_pool, const int* pos, const int* seq_row, const int* table,
            int mb, long long page_stride, int page_size, void* out, int N, int Hq, int Hkv, int hd, float scale,
            int window, int* err, cudaStream_t stream) {
-  const int G = Hq / Hkv;
+  const int G_all = Hq / Hkv, G = G_all < MAX_GROUP ? G_all : MAX_GROUP;
   const int W = G < MAX_WARPS ? G : MAX_WARPS;
   const size_t smem = sizeof(float) * ((size_t)CHUNK * (hd + 1) + (size_t)CHUNK * hd + (size_t)G * hd);
   auto kern = attn_simt_kernel<T, DPL>;
@@ -131,7 +134,7 @@ int launch(const void* q, const void* k_pool, const void* v_pool, const int* pos
     if (e != cudaSuccess) return (int)e;
     allowed = smem;
   }
-  dim3 grid(N, Hkv);
+  dim3 grid(N, Hkv, (G_all + MAX_GROUP - 1) / MAX_GROUP);
   fz_launch(kern, grid, dim3(32 * W), smem, stream, (const T*)q, (const T*)k_pool, (const T*)v_pool, pos, seq_row, table, mb,
             page_stride, page_size, (T*)out, Hq, Hkv, hd, scale, window, err);
   FZ_LAUNCH_CHECK();
@@ -148,15 +151,16 @@ int dispatch(const void* q, const void* k_pool, const void* v_pool, const int* p
   if (dpl <= 2) FZ_GO(2);
   if (dpl <= 4) FZ_GO(4);
   if (dpl <= 8) FZ_GO(8);
+  if (dpl <= 16) FZ_GO(16);
 #undef FZ_GO
   return FZ_BAD_SHAPE;
 }
 }  // namespace
 
-// Sizes taken: any Hkv, Hq a multiple of Hkv with Hq / Hkv <= 32, 0 < hd <= 256. Anything else returns FZ_BAD_SHAPE.
+// Sizes taken: any Hkv, Hq any multiple of Hkv, 0 < hd <= 512. Anything else returns FZ_BAD_SHAPE.
 FZ_API int fz_attn_simt_check(int Hq, int Hkv, int hd) {
   if (Hq <= 0 || Hkv <= 0 || hd <= 0 || Hq % Hkv) return FZ_BAD_SHAPE;
-  if (Hq / Hkv > MAX_WARPS * MAX_HPW || hd > 256) return FZ_BAD_SHAPE;
+  if (hd > MAX_HD || (Hq / Hkv + MAX_GROUP - 1) / MAX_GROUP > 65535) return FZ_BAD_SHAPE;
   return FZ_OK;
 }
 

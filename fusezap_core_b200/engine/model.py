@@ -94,9 +94,10 @@ class DecoderModel:
             needs[e.cache] = need
         return needs
 
-    def state_needs(self) -> dict[tuple[int, str], tuple[int, ...]]:
-        return {(n, name): tuple(shape) for n, e in enumerate(self.spec.schedule)
-                for name, shape in self.layers[e.layer].mixer.state_need().items()}
+    def state_needs(self) -> dict[tuple[int, str], Any]:
+        """(schedule entry, name) -> what the mixer declares: a shape (float32), or (shape, torch dtype)."""
+        return {(n, name): need for n, e in enumerate(self.spec.schedule)
+                for name, need in self.layers[e.layer].mixer.state_need().items()}
 
     def graph_safe(self) -> bool:
         """True if every part's forward is a fixed sequence of kernels over device data (see `Part.graph_safe`)."""

@@ -182,7 +182,7 @@ class CudaOps(Ops):
             raise ValueError(f"head_dim {head_dim} is not a multiple of 16; the attention kernels refuse it")
         if self.core.fz_attn_simt_check(c_int(num_heads), c_int(num_kv_heads), c_int(head_dim)) != 0:
             raise ValueError(f"attention sizes not supported: {num_heads} heads, {num_kv_heads} kv heads, head_dim "
-                             f"{head_dim} (need heads % kv_heads == 0, heads / kv_heads <= 32, head_dim <= 256)")
+                             f"{head_dim} (need heads % kv_heads == 0 and head_dim <= 512)")
 
     # ---- kernels
     def embed(self, table, tokens, x, src=None, prev_ids=None, scale: float = 1.0) -> None:

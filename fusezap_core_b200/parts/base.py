@@ -106,7 +106,8 @@ class Mixer(Part):
     def cache_need(self) -> KVNeed | None:
         return None
 
-    def state_need(self) -> dict[str, tuple[int, ...]]:
+    def state_need(self) -> dict[str, Any]:
+        """Per-request state of fixed size: {name: shape} (float32) or {name: (shape, torch dtype)}."""
         return {}
 
     def position_name(self) -> str | None:

@@ -125,3 +125,18 @@ def test_random_lives(seed):
         m.free(r)
     m.check()
     assert all(g.allocator.num_free == 24 for g in m.groups) and m.states.num_free == 5
+
+
+def test_state_slots_take_the_dtype_the_mixer_declares():
+    cm = CacheManager({0: KVNeed(1, 16, 0)}, {(0, "s"): (5,), (1, "count"): ((2, 3), torch.int32), (2, "h"): ((4,), torch.bfloat16)},
+                      4, 8, 3, 32, torch.float32, "cpu")
+    t = cm.states.tensors
+    assert t[(0, "s")].shape == (3, 5) and t[(0, "s")].dtype == torch.float32
+    assert t[(1, "count")].shape == (3, 2, 3) and t[(1, "count")].dtype == torch.int32
+    assert t[(2, "h")].dtype == torch.bfloat16
+    cm.ensure("a", 3)
+    slot = cm.state_slot("a")
+    t[(1, "count")][slot] += 7
+    cm.free("a")
+    cm.ensure("b", 3)
+    assert cm.state_slot("b") == slot and int(t[(1, "count")][slot].sum()) == 0, "a slot is zeroed when it is handed out"

@@ -182,7 +182,10 @@ def fill_cache(cache, table, lengths, g, scale=1.0):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("Hq,Hkv,hd,bs,window", [(4, 2, 16, 4, 0), (3, 1, 32, 8, 0), (5, 5, 48, 4, 12), (14, 2, 64, 16, 0),
-                                                  (8, 2, 128, 16, 37), (20, 2, 80, 16, 0), (2, 1, 256, 8, 0)])
+                                                  (8, 2, 128, 16, 37), (20, 2, 80, 16, 0), (2, 1, 256, 8, 0),
+                                                  # more query heads per kv head than one block takes (32), an odd remainder,
+                                                  # and head sizes beyond 256
+                                                  (70, 2, 16, 8, 0), (33, 1, 48, 4, 20), (2, 2, 384, 16, 0), (3, 1, 512, 8, 0)])
 def test_paged_attention(dtype, Hq, Hkv, hd, bs, window):
     cu, pl = ops_pair(dtype)
     g = torch.Generator().manual_seed(Hq * hd + window)
@@ -325,6 +328,9 @@ def test_refusals():
     with pytest.raises(ValueError, match="multiple of 16"):
         cu.check_attention(4, 2, 24)
     with pytest.raises(ValueError, match="not supported"):
-        cu.check_attention(66, 2, 64)
+        cu.check_attention(8, 2, 528)
+    with pytest.raises(ValueError, match="not supported"):
+        cu.check_attention(7, 2, 64)
+    cu.check_attention(66, 2, 64)      # any group size
     with pytest.raises(KernelError, match="CUDA tensors only"):
         cu.swiglu(torch.zeros(2, 8), torch.zeros(2, 4))
