@@ -145,6 +145,10 @@ def main() -> int:
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--reference-device", default="CUDA", help="the reference's device name for --impl reference")
     ap.add_argument("--workload", default="decode", choices=["decode", "stream"])
+    ap.add_argument("--leave-out", default="", metavar="OPS",
+                    help="measurement aid, NOT a benchmark: comma-separated kernel-table operations turned into no-ops "
+                         "(e.g. paged_attention, add_rmsnorm, linear_swiglu), to read an operation's cost inside the "
+                         "captured step off the difference to a run without it; the line is marked invalid")
     ap.add_argument("--requests", type=int, default=32, help="stream workload: number of requests")
     ap.add_argument("--new-tokens", type=int, default=256, help="stream workload: tokens generated per request")
     a = ap.parse_args()
@@ -175,6 +179,11 @@ def main() -> int:
     t0 = time.time()
     model = random_model(cfg, "bfloat16", dev, seed=0, max_len=a.context)
     torch.cuda.synchronize()
+    left_out = [name for name in a.leave_out.split(",") if name]
+    for name in left_out:
+        if not callable(getattr(model.ops, name, None)):
+            raise SystemExit(f"--leave-out: the kernel table has no operation {name!r}")
+        setattr(model.ops, name, lambda *args, **kw: None)      # (a fused operation that returns None falls back to its parts)
     print(f"bench: model built in {time.time() - t0:.1f}s, {model.weight_bytes() / 1e9:.2f} GB of weights read per step",
           file=sys.stderr, flush=True)
     Hkv, hd = cfg["num_key_value_heads"], cfg["head_dim"]
@@ -314,6 +323,8 @@ def main() -> int:
         "points": points,
         "points_frac": points_frac,
     }
+    if left_out:
+        line["invalid"] = "operations left out: " + ", ".join(left_out)
     print(json.dumps(line))
     return 0
 

@@ -79,7 +79,6 @@ struct Params {
   int splits;
   int stages;
   int vec_ok;              // rows mode: C rows are 16-byte aligned, so full groups of 16 columns go out as vectors
-  int accum;               // float32 output only: C += X . W^T + bias (the product is added to what C holds: a residual stream)
   int swiglu;              // W holds [64 gate rows | 64 up rows] blocks: store silu(gate) * up as bf16 [rows, feats / 2]
   // rope != 0 (swap mode, hd divides 128): the features are [q heads | k heads | v heads] of size hd; q and k are rotated
   // by the token's position, q goes to c_bf16 [rows, Hq * hd], k and v to the token's slot of the paged pool
@@ -209,7 +208,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           const int m = b0 + c + j;
           if (m < b_limit) {
             const float y = x[j] + bv;
-            if (p.c_f32) { float* d = p.c_f32 + (size_t)m * p.feats + a_row; *d = p.accum ? *d + y : y; }
+            if (p.c_f32) p.c_f32[(size_t)m * p.feats + a_row] = y;
             else p.c_bf16[(size_t)m * p.feats + a_row] = __float2bfloat16_rn(y);
           }
         }
@@ -221,11 +220,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (p.c_f32) {
           float4* dst = (float4*)(p.c_f32 + (size_t)a_row * p.feats + n);
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            float4 o = make_float4(y[4 * j], y[4 * j + 1], y[4 * j + 2], y[4 * j + 3]);
-            if (p.accum) { const float4 c0 = dst[j]; o.x += c0.x; o.y += c0.y; o.z += c0.z; o.w += c0.w; }
-            dst[j] = o;
-          }
+          for (int j = 0; j < 4; ++j) dst[j] = make_float4(y[4 * j], y[4 * j + 1], y[4 * j + 2], y[4 * j + 3]);
         } else {
           uint32_t w[8];
 #pragma unroll
@@ -243,7 +238,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           const int n = b0 + c + j;
           if (n < b_limit) {
             const float y = x[j] + (p.bias ? p.bias[n] : 0.f);
-            if (p.c_f32) { float* d = p.c_f32 + (size_t)a_row * p.feats + n; *d = p.accum ? *d + y : y; }
+            if (p.c_f32) p.c_f32[(size_t)a_row * p.feats + n] = y;
             else p.c_bf16[(size_t)a_row * p.feats + n] = __float2bfloat16_rn(y);
           }
         }
@@ -336,7 +331,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             ex[i * BM + r] = y;
           } else if (feat < p.feats) {
             const int m = tile_b * BN + c;
-            if (p.c_f32) { float* d = p.c_f32 + (size_t)m * p.feats + feat; *d = p.accum ? *d + y : y; }
+            if (p.c_f32) p.c_f32[(size_t)m * p.feats + feat] = y;
             else p.c_bf16[(size_t)m * p.feats + feat] = __float2bfloat16_rn(y);
           }
         }
@@ -545,11 +540,7 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
           if (p.c_f32) {
             float4* dst = (float4*)(p.c_f32 + (size_t)row * p.feats + n);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              float4 o = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-              if (p.accum) { const float4 c0 = dst[i]; o.x += c0.x; o.y += c0.y; o.z += c0.z; o.w += c0.w; }
-              dst[i] = o;
-            }
+            for (int i = 0; i < 4; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
           } else {
             uint32_t w[8];
 #pragma unroll
@@ -566,7 +557,7 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
           for (int i = 0; i < 16; ++i) {
             if (n + i < p.feats) {
               const float y = v[i] + (p.bias ? p.bias[n + i] : 0.f);
-              if (p.c_f32) { float* d = p.c_f32 + (size_t)row * p.feats + n + i; *d = p.accum ? *d + y : y; }
+              if (p.c_f32) p.c_f32[(size_t)row * p.feats + n + i] = y;
               else p.c_bf16[(size_t)row * p.feats + n + i] = __float2bfloat16_rn(y);
             }
           }
@@ -746,10 +737,7 @@ gemm_tc_rows_split_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
             for (int j = 0; j < 4; ++j) y[j] += p.bias[n + j];
           }
           if (p.c_f32) {
-            float4* dst = (float4*)(p.c_f32 + (size_t)row * p.feats + n);
-            float4 o = make_float4(y[0], y[1], y[2], y[3]);
-            if (p.accum) { const float4 c0 = *dst; o.x += c0.x; o.y += c0.y; o.z += c0.z; o.w += c0.w; }
-            *dst = o;
+            *(float4*)(p.c_f32 + (size_t)row * p.feats + n) = make_float4(y[0], y[1], y[2], y[3]);
           } else {
             const __nv_bfloat162 lo = __floats2bfloat162_rn(y[0], y[1]), hi = __floats2bfloat162_rn(y[2], y[3]);
             *(uint2*)(p.c_bf16 + (size_t)row * p.feats + n) = make_uint2(*(const uint32_t*)&lo, *(const uint32_t*)&hi);
@@ -759,7 +747,7 @@ gemm_tc_rows_split_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
           for (int j = 0; j < 4; ++j) {
             if (n + j < p.feats) {
               const float yj = y[j] + (p.bias ? p.bias[n + j] : 0.f);
-              if (p.c_f32) { float* d = p.c_f32 + (size_t)row * p.feats + n + j; *d = p.accum ? *d + yj : yj; }
+              if (p.c_f32) p.c_f32[(size_t)row * p.feats + n + j] = yj;
               else p.c_bf16[(size_t)row * p.feats + n + j] = __float2bfloat16_rn(yj);
             }
           }
@@ -906,15 +894,6 @@ static int gemm_tc_impl(const void* x, const void* w, const float* bias, void* c
 FZ_API int fz_gemm_tc(const void* x, const void* w, const float* bias, void* c, int out_dtype, int M, int N, int K,
                       int* err, cudaStream_t stream) {
   return gemm_tc_impl(x, w, bias, c, out_dtype, M, N, K, Params{}, err, stream);
-}
-
-// c [M, N] float32 += x . w^T + bias: the product (with its bias, rounded to float32 once) is added to what c holds, as
-// the separate "residual += sublayer output" would add it; every element of c is read and written by one thread.
-FZ_API int fz_gemm_tc_accum(const void* x, const void* w, const float* bias, float* c, int M, int N, int K, int* err,
-                            cudaStream_t stream) {
-  Params f{};
-  f.accum = 1;
-  return gemm_tc_impl(x, w, bias, c, FZ_F32, M, N, K, f, err, stream);
 }
 
 // Can the query/key/value product of M token rows with heads of size hd end in the rotation and the cache write?

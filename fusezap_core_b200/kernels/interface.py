@@ -54,13 +54,6 @@ class Ops:
         accumulation in float32, one rounding into out."""
         raise NotImplementedError
 
-    def linear_add(self, a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, x: torch.Tensor) -> bool:
-        """x[m, n] += float32(sum_k a[m, k] * w[n, k] + bias[n]): `linear` into float32 followed by the residual add, as
-        one operation (the same two roundings). x: (M, N) float32, updated in place. Optional: returns False, having
-        done nothing, if this table has no such kernel for these sizes; the caller then runs `linear` and leaves the
-        addition to the next norm."""
-        return False
-
     def pack_gate_up(self, gate: torch.Tensor, up: torch.Tensor, gate_bias: torch.Tensor | None = None,
                      up_bias: torch.Tensor | None = None):
         """Prepares the gate and up matrices ((I, K) each) for `linear_swiglu` in whatever layout the kernels want, or

@@ -83,7 +83,6 @@ class CudaOps(Ops):
         self.fuse_swiglu = True            # gate/up product and SwiGLU in one kernel where the sizes allow it
         self.fuse_argmax = True            # lm_head product and argmax in one pass where no logits are asked for
         self.fuse_rope = True              # q/k/v product, rotation and cache write in one kernel (few-token steps)
-        self.fuse_residual = True          # a sublayer's last product adds its result to the residual stream itself
         self._profile = None               # a StepProfile while the engine profiles its steps
 
     # ---- plumbing
@@ -242,24 +241,6 @@ class CudaOps(Ops):
         self._check(self.core.fz_gemm_simt(_p(a), _p(w), _p(bias), _p(out), c_int(_CODE[a.dtype]),
                                            c_int(_CODE[out.dtype]), c_int(m), c_int(n), c_int(k), self._stream()),
                     "linear", ideal_linear_bytes(m, n, k, a.element_size(), w.element_size(), out.element_size()))
-
-    def linear_add(self, a, w, bias, x) -> bool:
-        m, k = a.shape
-        n = w.shape[0]
-        if not (self.use_tensor_cores and self.fuse_residual and self.dtype == torch.bfloat16) or \
-                self.tc.fz_gemm_tc_check(_p(a), _p(w), c_int(m), c_int(n), c_int(k)) != 0:
-            return False
-        self._want(a, "linear input", (torch.bfloat16,), 2)
-        self._want(w, "linear weight", (torch.bfloat16,), 2)
-        self._want(x, "residual stream", (torch.float32,), 2)
-        if bias is not None:
-            self._want(bias, "linear bias", (torch.float32,), 1)
-        if w.shape[1] != k or x.shape != (m, n) or (bias is not None and bias.shape[0] != n):
-            raise KernelError(f"linear_add: a {tuple(a.shape)}, w {tuple(w.shape)}, x {tuple(x.shape)}")
-        self._check(self.tc.fz_gemm_tc_accum(_p(a), _p(w), _p(bias), _p(x), c_int(m), c_int(n), c_int(k), _p(self.err),
-                                             self._stream()), "linear_add (tensor cores)",
-                    m * k * 2 + n * k * 2 + 2 * m * n * 4)
-        return True
 
     def pack_gate_up(self, gate, up, gate_bias=None, up_bias=None):
         """Rows in blocks of 128 = [64 gate rows | 64 up rows] of the same 64 features, so that one 128-row tile of the

@@ -18,8 +18,6 @@ from .base import LayerCache, Mixer, register_mixer
 
 @register_mixer("gqa_attention")
 class GQAttention(Mixer):
-    adds_to_residual = True
-
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
                  window: int = 0, position: str | None = "rope",
                  names: tuple[str, str, str, str] = ("q_proj", "k_proj", "v_proj", "o_proj")):
@@ -59,7 +57,7 @@ class GQAttention(Mixer):
     def step_needs(self) -> tuple[str, ...]:
         return ("attention",)
 
-    def forward(self, ctx, h: torch.Tensor, cache: LayerCache, residual: torch.Tensor | None = None) -> torch.Tensor | None:
+    def forward(self, ctx, h: torch.Tensor, cache: LayerCache) -> torch.Tensor:
         n, ops, ws = h.shape[0], ctx.ops, ctx.ws
         Hq, Hkv, hd = self.Hq, self.Hkv, self.hd
         q = ws.get("q", (n, Hq * hd), ops.dtype)
@@ -70,9 +68,6 @@ class GQAttention(Mixer):
             position.rotate_and_store(ctx, qkv, q, cache, Hq, Hkv, hd)
         o = ws.get("attn_out", (n, Hq * hd), ops.dtype)
         ops.paged_attention(q, cache, ctx.meta, o, Hq, Hkv, hd, self.scale, self.window)
-        # the output product adds its result to the residual stream itself where the kernel table can (None: added)
-        if residual is not None and getattr(ops, "linear_add", None) is not None and ops.linear_add(o, self.wo, self.bo, residual):
-            return None
         delta = ws.get("delta", (n, self.D), torch.float32)
         ops.linear(o, self.wo, self.bo, delta)
         return delta

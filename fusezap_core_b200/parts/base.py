@@ -98,11 +98,6 @@ class Part:
 
 
 class Mixer(Part):
-    # True for a mixer / feed-forward whose `forward` takes `residual=` (the float32 residual stream, (N, D)) and may
-    # add its result to it in place, returning None instead of the result. The block passes `residual` only to parts
-    # that say so; a part that ignores the idea returns its result as ever and the next norm adds it.
-    adds_to_residual = False
-
     def cache_need(self) -> KVNeed | None:
         return None
 
@@ -123,8 +118,6 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
-    adds_to_residual = False      # as for `Mixer`
-
     def forward(self, ctx: "StepContext", h: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
 

@@ -33,15 +33,8 @@ class PreNormBlock(Block):
             part.bind(own, ops)
 
     def forward(self, ctx, x, delta, cache: LayerCache):
-        # `delta` is what the sublayer before still owes the residual stream (None: nothing, or it added it itself)
         h = self.norm1.forward(ctx, x, delta)
-        if self.mixer.adds_to_residual:
-            delta = self.mixer.forward(ctx, h, cache, residual=x)
-        else:
-            delta = self.mixer.forward(ctx, h, cache)
+        delta = self.mixer.forward(ctx, h, cache)
         h = self.norm2.forward(ctx, x, delta)
-        if self.ffn.adds_to_residual:
-            delta = self.ffn.forward(ctx, h, residual=x)
-        else:
-            delta = self.ffn.forward(ctx, h)
+        delta = self.ffn.forward(ctx, h)
         return x, delta

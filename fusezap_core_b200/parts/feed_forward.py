@@ -14,8 +14,6 @@ from .base import FeedForward, register_feed_forward
 
 @register_feed_forward("swiglu")
 class SwiGLU(FeedForward):
-    adds_to_residual = True
-
     def __init__(self, hidden_size: int, intermediate_size: int,
                  names: tuple[str, str, str] = ("gate_proj", "up_proj", "down_proj")):
         self.D, self.I, self.names = hidden_size, intermediate_size, tuple(names)
@@ -43,7 +41,7 @@ class SwiGLU(FeedForward):
         self.wd = tensors[f"{d}.weight"]
         self.bd = tensors[f"{d}.bias"].float() if f"{d}.bias" in tensors else None
 
-    def forward(self, ctx, h: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor | None:
+    def forward(self, ctx, h: torch.Tensor) -> torch.Tensor:
         n, ops, ws = h.shape[0], ctx.ops, ctx.ws
         a = ws.get("act", (n, self.I), ops.dtype)
         if self.packed is not None:
@@ -52,9 +50,6 @@ class SwiGLU(FeedForward):
             gu = ws.get("gate_up", (n, 2 * self.I), ops.dtype)
             ops.linear(h, self.wgu, self.bgu, gu)
             ops.swiglu(gu, a)
-        # the down product adds its result to the residual stream itself where the kernel table can (None: added)
-        if residual is not None and getattr(ops, "linear_add", None) is not None and ops.linear_add(a, self.wd, self.bd, residual):
-            return None
         delta = ws.get("delta", (n, self.D), torch.float32)
         ops.linear(a, self.wd, self.bd, delta)
         return delta

@@ -216,24 +216,3 @@ def test_product_that_keeps_only_the_largest_of_each_row(M, N, K):
     a3 = torch.randn(M, 4096, generator=g).to(torch.bfloat16).cuda()
     w3 = torch.randn(1024, 4096, generator=g).to(torch.bfloat16).cuda()
     assert ops.linear_argmax(a3, w3, None, got) is False
-
-
-@pytest.mark.parametrize("M,N,K", [(8, 4096, 4096), (1, 1000, 512), (100, 384, 96), (128, 4096, 14336), (256, 4096, 14336),
-                                   (300, 777, 1024), (2048, 4096, 512), (640, 1000, 200)])
-def test_product_added_to_the_residual_stream(M, N, K):
-    """`linear_add` (x += a . w^T + bias inside the product's epilogue) gives the bits of `linear` into a float32
-    buffer followed by the addition, in every mode of the kernel: few rows with and without split K, many rows, many
-    rows with K cut over a cluster."""
-    from fusezap_core_b200.kernels import cuda_ops
-    ops = cuda_ops("bfloat16")
-    g = torch.Generator().manual_seed(M + N + K)
-    a = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
-    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).cuda()
-    for bias in (None, torch.randn(N, generator=g).cuda()):
-        x0 = torch.randn(M, N, generator=g).cuda()
-        delta = torch.empty(M, N, device="cuda")
-        ops.linear(a, w, bias, delta)
-        x = x0.clone()
-        assert ops.linear_add(a, w, bias, x)
-        ops.check_errors()
-        assert torch.equal(x, x0 + delta)

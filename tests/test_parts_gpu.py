@@ -161,6 +161,6 @@ def test_attention_part_and_block(dtype, Hq, Hkv, hd, window, bias):
     xc = x.clone().cuda()
     x_out, delta = block.forward(ctx, xc, None, lc)
     full = plain_model.layer(x, pw, 0, cfg, cos, sin, DT[dtype])
-    res = (x_out if delta is None else x_out + delta).cpu()      # (None: the feed-forward added its result to x itself)
+    res = (x_out + delta).cpu()
     assert float((res - full).abs().max()) <= tol(dtype, full, 3.0), float((res - full).abs().max())
     ops.check_errors()
