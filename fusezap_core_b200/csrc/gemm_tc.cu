@@ -397,6 +397,74 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   if (threadIdx.x == 0 && flag[1]) atomicOr(p.err, FZ_ERR_WAIT_TIMEOUT);
 }
 
+// Rows mode: one thread's lane (token row `row`) of a finished accumulator of BN columns at `taddr`, with the bias added,
+// to the output's columns n0 .. n0 + BN - 1 (or, with the fused SwiGLU, to its packed half). Every lane of the warp takes
+// part in the loads from tensor memory whether or not its row exists.
+template <int BN>
+__device__ __forceinline__ void rows_store_tile(const Params& p, uint32_t taddr, int row, int n0) {
+  float v[16];
+  if (p.swiglu) {
+    // columns [128 b, 128 b + 64) are gate, [128 b + 64, 128 b + 128) up of output features 64 (n0 / 128 + b) ..
+    float u[16];
+#pragma unroll 1
+    for (int c = 0; c < BN; c += 16) {
+      if ((c & 64) != 0) continue;
+      tmem_ld16(taddr + (uint32_t)c, v);
+      tmem_ld16(taddr + (uint32_t)(c + 64), u);
+      const int n = n0 + c;                       // packed index of the gate column
+      if (row >= p.rows || n >= p.feats) continue;
+      uint32_t w[8];
+#pragma unroll
+      for (int i = 0; i < 16; i += 2) {
+        const float g0 = v[i] + (p.bias ? p.bias[n + i] : 0.f), g1 = v[i + 1] + (p.bias ? p.bias[n + i + 1] : 0.f);
+        const float u0 = u[i] + (p.bias ? p.bias[n + 64 + i] : 0.f), u1 = u[i + 1] + (p.bias ? p.bias[n + 64 + i + 1] : 0.f);
+        const __nv_bfloat162 h2 = __floats2bfloat162_rn(silu_mul(g0, u0), silu_mul(g1, u1));
+        w[i >> 1] = *(const uint32_t*)&h2;
+      }
+      uint4* dst = (uint4*)(p.c_bf16 + (size_t)row * (p.feats >> 1) + (n >> 7) * 64 + (n & 63));
+      dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+      dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    }
+    return;
+  }
+#pragma unroll 1
+  for (int c = 0; c < BN; c += 16) {
+    tmem_ld16(taddr + (uint32_t)c, v);
+    if (row >= p.rows) continue;
+    const int n = n0 + c;
+    if (p.vec_ok && n + 16 <= p.feats) {
+      if (p.bias) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] += p.bias[n + i];
+      }
+      if (p.c_f32) {
+        float4* dst = (float4*)(p.c_f32 + (size_t)row * p.feats + n);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+      } else {
+        uint32_t w[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const __nv_bfloat162 h2 = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+          w[i] = *(const uint32_t*)&h2;
+        }
+        uint4* dst = (uint4*)(p.c_bf16 + (size_t)row * p.feats + n);
+        dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+        dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        if (n + i < p.feats) {
+          const float y = v[i] + (p.bias ? p.bias[n + i] : 0.f);
+          if (p.c_f32) p.c_f32[(size_t)row * p.feats + n + i] = y;
+          else p.c_bf16[(size_t)row * p.feats + n + i] = __float2bfloat16_rn(y);
+        }
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------------- rows mode, persistent
 // C[rows, feats] = X . W^T (+ bias) for many token rows. grid = min(tiles, SMs); tile i of a CTA is tile number
 // blockIdx.x + i * gridDim.x, token tile = number % tiles_m, feature tile = number / tiles_m.
@@ -499,70 +567,7 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       if (!ok) { flag[0] = 1; break; }
       tc_fence_after();
       const uint32_t taddr = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(quad * 32) << 16);
-      const int row = tm * BM + r, n0 = tn * BN;
-      float v[16];
-      if (p.swiglu) {
-        // columns [128 b, 128 b + 64) are gate, [128 b + 64, 128 b + 128) up of output features 64 (n0 / 128 + b) ..
-        float u[16];
-#pragma unroll 1
-        for (int c = 0; c < BN; c += 16) {
-          if ((c & 64) != 0) continue;
-          tmem_ld16(taddr + (uint32_t)c, v);
-          tmem_ld16(taddr + (uint32_t)(c + 64), u);
-          const int n = n0 + c;                       // packed index of the gate column
-          if (row >= p.rows || n >= p.feats) continue;
-          uint32_t w[8];
-#pragma unroll
-          for (int i = 0; i < 16; i += 2) {
-            const float g0 = v[i] + (p.bias ? p.bias[n + i] : 0.f), g1 = v[i + 1] + (p.bias ? p.bias[n + i + 1] : 0.f);
-            const float u0 = u[i] + (p.bias ? p.bias[n + 64 + i] : 0.f), u1 = u[i + 1] + (p.bias ? p.bias[n + 64 + i + 1] : 0.f);
-            const __nv_bfloat162 h2 = __floats2bfloat162_rn(silu_mul(g0, u0), silu_mul(g1, u1));
-            w[i >> 1] = *(const uint32_t*)&h2;
-          }
-          uint4* dst = (uint4*)(p.c_bf16 + (size_t)row * (p.feats >> 1) + (n >> 7) * 64 + (n & 63));
-          dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
-          dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
-        }
-        tc_fence_before();
-        mbar_arrive(&acc_empty[acc]);
-        continue;
-      }
-#pragma unroll 1
-      for (int c = 0; c < BN; c += 16) {
-        tmem_ld16(taddr + (uint32_t)c, v);
-        if (row >= p.rows) continue;
-        const int n = n0 + c;
-        if (p.vec_ok && n + 16 <= p.feats) {
-          if (p.bias) {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) v[i] += p.bias[n + i];
-          }
-          if (p.c_f32) {
-            float4* dst = (float4*)(p.c_f32 + (size_t)row * p.feats + n);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-          } else {
-            uint32_t w[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const __nv_bfloat162 h2 = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-              w[i] = *(const uint32_t*)&h2;
-            }
-            uint4* dst = (uint4*)(p.c_bf16 + (size_t)row * p.feats + n);
-            dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
-            dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            if (n + i < p.feats) {
-              const float y = v[i] + (p.bias ? p.bias[n + i] : 0.f);
-              if (p.c_f32) p.c_f32[(size_t)row * p.feats + n + i] = y;
-              else p.c_bf16[(size_t)row * p.feats + n + i] = __float2bfloat16_rn(y);
-            }
-          }
-        }
-      }
+      rows_store_tile<BN>(p, taddr, tm * BM + r, tn * BN);
       tc_fence_before();
       mbar_arrive(&acc_empty[acc]);      // this thread has read its lane of the accumulator
     }
@@ -596,6 +601,216 @@ int launch_rows(const CUtensorMap& mx, const CUtensorMap& mw, const Params& p, i
   const int total = tiles_m * tiles_n;
   dim3 grid(total < sms ? total : sms);
   fz_launch(gemm_tc_rows_kernel<BN>, grid, dim3(NUM_THREADS), smem, stream, mx, mw, p, tiles_m, tiles_n);
+  FZ_LAUNCH_CHECK();
+  return FZ_OK;
+}
+
+// ---------------------------------------------------------------------------------------------- rows mode, two SMs per tile
+// The same product with a pair of CTAs (a cluster of two, on the two SMs of one TPC) on every 256 x 256 output tile:
+// `tcgen05.mma.cta_group::2` multiplies 256 token rows by 256 features per instruction, each CTA holding its 128 token
+// rows of X and its 128 of the 256 features of W in its own shared memory, and its 128 rows of the accumulator in its own
+// tensor memory. Per SM and k-block that is 32 KB of operands instead of 48 KB for the same 128 x 256 outputs: less L2
+// and shared-memory traffic, more stages in the ring, half as many instructions to issue.
+//
+// Who signals whom: each CTA's producer lane loads its own two operand tiles (`cp.async.bulk.tensor ... .cta_group::2`,
+// which may count its bytes on the other CTA's barrier; no multicast) and has them counted on the `full` barrier of the
+// leader (cluster rank 0), whose producer expects both CTAs' bytes. The leader's MMA lane issues the instructions for
+// the pair and commits them to the `empty` (and, per tile, `acc_full`) barriers of BOTH CTAs (`tcgen05.commit` with a CTA
+// mask), so each producer refills its own ring and each CTA's epilogue warps read their own tensor memory. One lane of
+// each epilogue warp of both CTAs then arrives on the leader's `acc_empty` barrier (count 8). Every wait is bounded;
+// both CTAs pass a cluster barrier after the barriers' initialisation and before they leave.
+constexpr int PAIR_BN = 256;
+
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+  return remote;
+}
+__device__ __forceinline__ uint32_t ld_dsmem_u32(uint32_t cluster_addr) {
+  uint32_t v;
+  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(cluster_addr) : "memory");
+  return v;
+}
+// A tile into this CTA's shared memory, its bytes counted on a barrier given by its cluster address (this CTA's or its
+// pair's).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_dst), "l"(map), "r"(bar_cluster_addr), "r"(x), "r"(y) : "memory");
+}
+// D (256 rows over the pair's tensor memories) (+)= A (each CTA's 128 rows) * B (each CTA's half of the N columns)
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Arrives on the barrier at this shared-memory offset in both CTAs of the pair when the MMAs issued so far are complete.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"((uint16_t)3) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_rows_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const Params p,
+                         int tiles_m, int tiles_n) {
+  constexpr int BN = PAIR_BN;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  constexpr int A_BYTES = BM * BK * 2, B_BYTES = (BN / 2) * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int TMEM_COLS = 2 * BN;          // two accumulators of 256 columns
+  uint64_t* full = (uint64_t*)(smem + (size_t)p.stages * STAGE_BYTES);      // used in the leader only
+  uint64_t* empty = full + p.stages;
+  uint64_t* acc_full = empty + p.stages;     // [2]
+  uint64_t* acc_empty = acc_full + 2;        // [2], used in the leader only
+  uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+  int* flag = (int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_rank();      // 0: the leader
+  const int pair = (int)blockIdx.x >> 1, pairs = (int)gridDim.x >> 1;
+  const int kblocks = (p.K + BK - 1) / BK;
+  const int total = tiles_m * tiles_n;
+  const int my_tiles = total > pair ? (total - pair + pairs - 1) / pairs : 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 8); }
+    flag[0] = 0;
+    mbar_init_fence();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();      // the pair's barriers exist and its tensor memory is allocated before anything crosses over
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  // One instruction writes the same tensor-memory address in both CTAs: each allocated all of it once, so the two bases
+  // are equal; if they ever were not, nothing is computed and the error is reported.
+  const bool same_base = ld_dsmem_u32(map_to_cta(smem_u32(tmem_slot), rank ^ 1u)) == tmem_base;
+  fz_grid_launch_dependents();
+  if (warp != 0) fz_grid_wait();
+
+  if (!same_base) {
+    if (threadIdx.x == 0) flag[0] = 1;
+  } else if (warp == 0) {
+    if (lane == 0) {
+      const uint32_t full0 = map_to_cta(smem_u32(full), 0u);      // the leader's `full` barriers, 8 bytes apart
+      const uint32_t s0 = smem_u32(smem);
+      // weights of the first stages before the wait on the previous kernel (they do not depend on it)
+      const int first = pair;
+      const int early = my_tiles > 0 ? (kblocks < p.stages ? kblocks : p.stages) : 0;
+      for (int i = 0; i < early; ++i) {
+        if (rank == 0) mbar_expect_tx(&full[i], 2 * STAGE_BYTES);
+        tma_load_2d_pair(s0 + (uint32_t)(i * STAGE_BYTES + A_BYTES), &map_w, full0 + 8u * (uint32_t)i, i * BK,
+                         (first / tiles_m) * BN + (int)rank * (BN / 2));
+      }
+      fz_grid_wait();
+      int it = 0, s = 0, round = 0;
+      bool ok = true;
+      for (int j = 0; j < my_tiles && ok; ++j) {
+        const int tile = pair + j * pairs;
+        const int tm = tile % tiles_m, tn = tile / tiles_m;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const uint32_t sa = s0 + (uint32_t)(s * STAGE_BYTES);
+          if (it >= early) {
+            if (round > 0 && !mbar_wait(&empty[s], (round - 1) & 1)) { flag[0] = 1; ok = false; break; }
+            if (rank == 0) mbar_expect_tx(&full[s], 2 * STAGE_BYTES);
+            tma_load_2d_pair(sa + A_BYTES, &map_w, full0 + 8u * (uint32_t)s, kb * BK, tn * BN + (int)rank * (BN / 2));
+          }
+          tma_load_2d_pair(sa, &map_x, full0 + 8u * (uint32_t)s, kb * BK, (2 * tm + (int)rank) * BM);
+          if (++s == p.stages) { s = 0; ++round; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = make_idesc(2 * BM, BN);
+      int s = 0, round = 0;
+      bool ok = true;
+      for (int j = 0; j < my_tiles && ok; ++j) {
+        const int acc = j & 1;
+        if (j >= 2 && !mbar_wait(&acc_empty[acc], ((j >> 1) - 1) & 1)) { flag[0] = 1; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(&full[s], round & 1)) { flag[0] = 1; ok = false; break; }
+          tc_fence_after();
+          const uint8_t* sa = smem + (size_t)s * STAGE_BYTES;
+          const uint64_t da = desc_k_major(smem_u32(sa)), db = desc_k_major(smem_u32(sa + A_BYTES));
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_bf16_pair(tmem_d, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          umma_commit_pair(&empty[s]);
+          if (++s == p.stages) { s = 0; ++round; }
+        }
+        umma_commit_pair(&acc_full[acc]);
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const uint32_t acc_empty0 = map_to_cta(smem_u32(acc_empty), 0u);
+    bool ok = true;
+    for (int j = 0; j < my_tiles && ok; ++j) {
+      const int tile = pair + j * pairs;
+      const int tm = tile % tiles_m, tn = tile / tiles_m;
+      const int acc = j & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(&acc_full[acc], (j >> 1) & 1));
+      if (!ok) { flag[0] = 1; break; }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(quad * 32) << 16);
+      rows_store_tile<BN>(p, taddr, (2 * tm + (int)rank) * BM + r, tn * BN);
+      tc_fence_before();
+      __syncwarp();      // every lane of the warp has read its lane of the accumulator
+      if (lane == 0) mbar_arrive_cluster(acc_empty0 + 8u * (uint32_t)acc);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();      // nobody leaves while the other CTA may still signal its barriers or write its tensor memory
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && flag[0]) atomicOr(p.err, FZ_ERR_WAIT_TIMEOUT);
+}
+
+int launch_rows_pair(const CUtensorMap& mx, const CUtensorMap& mw, const Params& p, int tiles_m, int tiles_n, int sms, cudaStream_t stream) {
+  constexpr int STAGE_BYTES = (BM + PAIR_BN / 2) * BK * 2;
+  const size_t smem = (size_t)p.stages * STAGE_BYTES + 1024 + 8 * (2 * p.stages + 4) + 16;
+  static size_t allowed = 48 * 1024;
+  if (smem > allowed) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_rows_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    allowed = smem;
+  }
+  const int total = tiles_m * tiles_n, most = sms / 2;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * (unsigned)(total < most ? total : most));
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (fz_pdl_enabled()) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  attr[na].id = cudaLaunchAttributeClusterDimension;
+  attr[na].val.clusterDim.x = 2;
+  attr[na].val.clusterDim.y = 1;
+  attr[na].val.clusterDim.z = 1;
+  ++na;
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_tc_rows_pair_kernel, mx, mw, p, tiles_m, tiles_n);
+  if (le != cudaSuccess) return (int)le;
   FZ_LAUNCH_CHECK();
   return FZ_OK;
 }
@@ -887,6 +1102,32 @@ FZ_API int fz_gemm_tc_rows_splits(int M, int N, int K) {
   return 1;
 }
 
+static int device_sms() {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+      sms = 148;
+  }
+  return sms;
+}
+
+// Which many-token kernel takes a product: 0 by the rule below, 1 always one SM per tile, 2 a pair of SMs per tile
+// wherever the tile is 256 wide (for measurements and tests; the results differ by nothing but the kernel).
+static int g_rows_mode = 0;
+FZ_API void fz_gemm_tc_rows_mode(int mode) { g_rows_mode = mode; }
+
+// Does a pair of SMs work on each 256 x 256 tile of this product (M > 128 token rows, not cut along K)? Where the pairs
+// have at least half a round of tiles, and the token rows fill the pairs' second halves: an even count of 128-row tiles,
+// or so many that the one empty half costs less than the pair gains (measured: 10 to 14 % at 1,024 rows and more).
+FZ_API int fz_gemm_tc_rows_pairs(int M, int N, int K) {
+  if (M <= BM || N < 256 || g_rows_mode == 1) return 0;
+  if (g_rows_mode == 2) return 1;
+  const int t128 = (M + BM - 1) / BM;
+  const long long tiles = (long long)((t128 + 1) / 2) * ((N + PAIR_BN - 1) / PAIR_BN);
+  return ((t128 % 2 == 0 || t128 >= 9) && 4 * tiles >= device_sms()) ? 1 : 0;
+}
+
 // x: [M, K] bf16, w: [N, K] bf16, bias: [N] float32 or null, c: [M, N] float32 (out_dtype 0) or bf16 (1).
 static int gemm_tc_impl(const void* x, const void* w, const float* bias, void* c, int out_dtype, int M, int N, int K,
                         const Params& fused, int* err, cudaStream_t stream);
@@ -1054,6 +1295,13 @@ static int gemm_tc_impl(const void* x, const void* w, const float* bias, void* c
       for (int cand : {224, 192, 160})
         if (tm * ((N + cand - 1) / cand) <= sms) bn = cand;
     }
+  }
+  if (bn == 256 && fz_gemm_tc_rows_pairs(M, N, K)) {
+    // many token rows: a pair of SMs on every 256 x 256 tile (see `gemm_tc_rows_pair_kernel`)
+    p.stages = (200 * 1024) / ((BM + PAIR_BN / 2) * BK * 2);
+    if ((st = get_map_bf16(x, M, K, BM, &ma)) != FZ_OK) return st;
+    if ((st = get_map_bf16(w, N, K, PAIR_BN / 2, &mb)) != FZ_OK) return st;
+    return launch_rows_pair(ma, mb, p, (M + 2 * BM - 1) / (2 * BM), (N + PAIR_BN - 1) / PAIR_BN, device_sms(), stream);
   }
   {
     const int stage = (BM + bn) * BK * 2;

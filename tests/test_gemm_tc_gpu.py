@@ -60,6 +60,48 @@ def test_many_rows(M, N, K):
         assert err <= lim, f"M={M} N={N} K={K} {out_dtype}: max |diff| {err:.3e} > {lim:.3e}"
 
 
+@pytest.fixture
+def rows_mode():
+    """Forces one of the many-token kernels (1: one SM per tile, 2: a pair of SMs per 256 x 256 tile) and puts the rule
+    back afterwards."""
+    from fusezap_core_b200.kernels import cuda_ops
+    tc = cuda_ops("bfloat16").tc
+    yield tc.fz_gemm_tc_rows_mode
+    tc.fz_gemm_tc_rows_mode(0)
+
+
+@pytest.mark.parametrize("M,N,K", [(129, 256, 64), (256, 256, 128), (257, 300, 72), (300, 777, 200), (1000, 4096, 1024),
+                                   (2048, 1024, 512), (640, 6144, 4096), (1153, 5000, 264),
+                                   (150, 151936, 896)])      # one pair of SMs walks more tiles than it has accumulators
+def test_many_rows_on_pairs_of_sms(M, N, K, rows_mode):
+    """The two-SM kernel (each CTA of a cluster of two holds half of the tile's token rows and half of its features)
+    against float64, with ragged edges in every dimension and token rows that leave the pair's second half empty; and
+    bit for bit against the one-SM kernel, whose sums over K have the same order."""
+    outs = {}
+    for mode in (1, 2):
+        rows_mode(mode)
+        for out_dtype, bias in ((torch.float32, True), (torch.bfloat16, False)):
+            out, ref = run(M, N, K, out_dtype, bias)
+            err, scale = check(out, ref, K)
+            lim = 1e-4 * scale if out_dtype == torch.float32 else 2.0 ** -8 * scale
+            assert err <= lim, f"mode {mode} M={M} N={N} K={K} {out_dtype}: max |diff| {err:.3e} > {lim:.3e}"
+            outs[mode, out_dtype] = out
+    for out_dtype in (torch.float32, torch.bfloat16):
+        assert torch.equal(outs[1, out_dtype], outs[2, out_dtype]), f"{out_dtype}: the two kernels differ"
+
+
+def test_which_products_go_to_pairs_of_sms():
+    from fusezap_core_b200.kernels import cuda_ops
+    tc = cuda_ops("bfloat16").tc
+    tc.fz_gemm_tc_rows_mode(0)
+    for M, N, K in ((2048, 6144, 4096), (2048, 4096, 14336), (1024, 28672, 4096), (512, 28672, 4096), (256, 28672, 4096),
+                    (1200, 4096, 4096)):
+        assert tc.fz_gemm_tc_rows_pairs(M, N, K) == 1, (M, N, K)
+    # few rows, an odd count of 128-row tiles below nine, narrow outputs, or too few tiles for half a round
+    for M, N, K in ((128, 4096, 4096), (384, 28672, 4096), (640, 28672, 4096), (2048, 128, 4096), (256, 1024, 4096)):
+        assert tc.fz_gemm_tc_rows_pairs(M, N, K) == 0, (M, N, K)
+
+
 def test_which_products_are_cut_along_k():
     from fusezap_core_b200.kernels import cuda_ops
     tc = cuda_ops("bfloat16").tc
@@ -100,11 +142,15 @@ def test_refused_shapes_fall_back_to_the_plain_kernel():
 
 @pytest.mark.parametrize("M", [1, 8, 40, 128, 129, 700])
 @pytest.mark.parametrize("I,K", [(128, 64), (448, 96), (4864, 896), (1024, 4096)])
-def test_fused_gate_up_swiglu(M, I, K):
+@pytest.mark.parametrize("mode", [1, 2])
+def test_fused_gate_up_swiglu(M, I, K, mode, rows_mode):
     """The fused product + SwiGLU against silu(x.gate^T + bg) * (x.up^T + bu) in float64, in both modes (few rows: with
-    and without a split of K; many rows: persistent tiles)."""
+    and without a split of K; many rows: persistent tiles on one SM or on a pair)."""
     from fusezap_core_b200.kernels import cuda_ops
     ops = cuda_ops("bfloat16")
+    if mode == 2 and M <= 128:
+        pytest.skip("few rows never go to the many-token kernels")
+    rows_mode(mode)
     g = torch.Generator().manual_seed(M + I + K)
     x = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
     wg = (torch.randn(I, K, generator=g) * K ** -0.5).to(torch.bfloat16).cuda()
