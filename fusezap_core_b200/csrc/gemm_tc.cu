@@ -646,10 +646,11 @@ __device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t desc_a,
       "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
 }
-// Arrives on the barrier at this shared-memory offset in both CTAs of the pair when the MMAs issued so far are complete.
-__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+// Arrives on the barrier at this shared-memory offset in both CTAs of the pair (cluster ranks `first` and `first` + 1) when
+// the MMAs issued so far are complete.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint32_t first = 0u) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-               ::"r"(smem_u32(bar)), "h"((uint16_t)3) : "memory");
+               ::"r"(smem_u32(bar)), "h"((uint16_t)(3u << first)) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
@@ -835,20 +836,29 @@ __device__ __forceinline__ float4 ld_dsmem_v4(uint32_t addr, uint32_t rank) {
   return v;
 }
 
+// PAIR: the tile is 256 token rows by 256 features on a pair of CTAs (`tcgen05.mma.cta_group::2`, as in
+// `gemm_tc_rows_pair_kernel`: each CTA loads its 128 rows of X and 128 of the 256 features of W, so a CTA draws 32 KB per
+// k-block instead of 48 KB), the cluster is (2, 1, splits) with the two CTAs of a pair at neighbouring ranks, and a CTA
+// adds up the partial tiles of its own half of the rows.
+template <bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_rows_split_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const Params p) {
   constexpr int BN = SPLIT_BN;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-  uint64_t* full = (uint64_t*)(smem + (size_t)p.stages * STAGE_BYTES);
+  constexpr int A_BYTES = BM * BK * 2, B_BYTES = (PAIR ? BN / 2 : BN) * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+  uint64_t* full = (uint64_t*)(smem + (size_t)p.stages * STAGE_BYTES);      // PAIR: used in the pair's leader only
   uint64_t* empty = full + p.stages;
   uint64_t* acc_ready = empty + p.stages;
   uint32_t* tmem_slot = (uint32_t*)(acc_ready + 1);
   int* flag = (int*)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tm = blockIdx.x, tn = blockIdx.y, split = blockIdx.z;
+  const uint32_t rank = cluster_rank();
+  const uint32_t half = PAIR ? (rank & 1u) : 0u, leader = PAIR ? (rank & ~1u) : rank;      // which rows of the pair's tile; its first CTA
+  const int tm = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x, tn = blockIdx.y, split = blockIdx.z;
+  const int row0 = PAIR ? (2 * tm + (int)half) * BM : tm * BM;
+  const int w_row0 = tn * BN + (PAIR ? (int)half * (BN / 2) : 0);
   const int kblocks = (p.K + BK - 1) / BK;
   const int kb0 = (int)((long long)kblocks * split / p.splits), kb1 = (int)((long long)kblocks * (split + 1) / p.splits);
   const int nkb = kb1 - kb0;
@@ -862,49 +872,64 @@ gemm_tc_rows_split_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
   if (warp == 1) tmem_alloc(tmem_slot, BN);
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();      // the pair's barriers and tensor memory exist before anything crosses over
   tc_fence_after();
   const uint32_t tmem_d = *tmem_slot;
+  bool same_base = true;      // (one instruction writes the same tensor-memory address in both CTAs of a pair)
+  if constexpr (PAIR) same_base = ld_dsmem_u32(map_to_cta(smem_u32(tmem_slot), rank ^ 1u)) == tmem_d;
   fz_grid_launch_dependents();
   if (warp != 0) fz_grid_wait();
 
-  if (warp == 0) {
+  if (!same_base) {
+    if (threadIdx.x == 0) flag[0] = 1;
+  } else if (warp == 0) {
     if (lane == 0) {
+      const uint32_t s0 = smem_u32(smem);
+      const uint32_t full0 = PAIR ? map_to_cta(smem_u32(full), leader) : smem_u32(full);      // barriers are 8 bytes apart
+      const uint32_t expect = PAIR ? 2 * STAGE_BYTES : STAGE_BYTES;
+      auto load = [&](uint32_t dst, const CUtensorMap* map, int stage, int x, int y) {
+        if constexpr (PAIR) tma_load_2d_pair(dst, map, full0 + 8u * (uint32_t)stage, x, y);
+        else tma_load_2d_u32(dst, map, full0 + 8u * (uint32_t)stage, x, y);
+      };
       // the weights of the first stages before the wait on the previous kernel (they do not depend on it)
       const int early = nkb < p.stages ? nkb : p.stages;
       for (int i = 0; i < early; ++i) {
-        mbar_expect_tx(&full[i], STAGE_BYTES);
-        tma_load_2d(smem + (size_t)i * STAGE_BYTES + A_BYTES, &map_w, &full[i], (kb0 + i) * BK, tn * BN);
+        if (half == 0) mbar_expect_tx(&full[i], expect);
+        load(s0 + (uint32_t)(i * STAGE_BYTES + A_BYTES), &map_w, i, (kb0 + i) * BK, w_row0);
       }
       fz_grid_wait();
       for (int i = 0, s = 0, round = 0; i < nkb; ++i) {
-        uint8_t* sa = smem + (size_t)s * STAGE_BYTES;
+        const uint32_t sa = s0 + (uint32_t)(s * STAGE_BYTES);
         if (round > 0) {
           if (!mbar_wait(&empty[s], (round - 1) & 1)) { flag[0] = 1; break; }
-          mbar_expect_tx(&full[s], STAGE_BYTES);
-          tma_load_2d(sa + A_BYTES, &map_w, &full[s], (kb0 + i) * BK, tn * BN);
+          if (half == 0) mbar_expect_tx(&full[s], expect);
+          load(sa + A_BYTES, &map_w, s, (kb0 + i) * BK, w_row0);
         }
-        tma_load_2d(sa, &map_x, &full[s], (kb0 + i) * BK, tm * BM);
+        load(sa, &map_x, s, (kb0 + i) * BK, row0);
         if (++s == p.stages) { s = 0; ++round; }
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(BM, BN);
+    if (lane == 0 && half == 0) {
+      constexpr uint32_t idesc = make_idesc(PAIR ? 2 * BM : BM, BN);
       for (int i = 0, s = 0, round = 0; i < nkb; ++i) {
         if (!mbar_wait(&full[s], round & 1)) { flag[0] = 1; break; }
         tc_fence_after();
         const uint8_t* sa = smem + (size_t)s * STAGE_BYTES;
         const uint64_t da = desc_k_major(smem_u32(sa)), db = desc_k_major(smem_u32(sa + A_BYTES));
 #pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k)
-          umma_bf16(tmem_d, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (i > 0 || k > 0) ? 1u : 0u);
-        umma_commit(&empty[s]);
+        for (int k = 0; k < BK / UMMA_K; ++k) {
+          if constexpr (PAIR) umma_bf16_pair(tmem_d, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (i > 0 || k > 0) ? 1u : 0u);
+          else umma_bf16(tmem_d, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (i > 0 || k > 0) ? 1u : 0u);
+        }
+        if constexpr (PAIR) umma_commit_pair(&empty[s], leader); else umma_commit(&empty[s]);
         if (++s == p.stages) { s = 0; ++round; }
       }
-      umma_commit(acc_ready);
+      if constexpr (PAIR) umma_commit_pair(acc_ready, leader); else umma_commit(acc_ready);
     }
   } else {
-    // the accumulator -> this CTA's partial tile in shared memory (every stage has been consumed by now)
+    // the accumulator -> this CTA's partial tile in shared memory (every stage has been consumed by now, in both CTAs
+    // of a pair: the commit covers the pair's instructions, which read both)
     const int quad = warp & 3, r = quad * 32 + lane;
     const bool ok = __all_sync(0xffffffffu, mbar_wait(acc_ready, 0));
     if (!ok) flag[0] = 1;
@@ -925,13 +950,12 @@ gemm_tc_rows_split_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
   }
   // every thread of every CTA of the cluster passes both cluster barriers; only the epilogue warps work between them
   cluster_sync_all();
-  if (warp >= 2) {
+  if (warp >= 2 && same_base) {
     const int r = (warp & 3) * 32 + lane;
-    const int row = tm * BM + r;
-    const uint32_t rank = cluster_rank();
+    const int row = row0 + r;
     // this CTA's share of the tile's columns, in groups of four
     const int groups = BN / 4;
-    const int g0 = (int)((long long)groups * rank / p.splits), g1 = (int)((long long)groups * (rank + 1) / p.splits);
+    const int g0 = (int)((long long)groups * split / p.splits), g1 = (int)((long long)groups * (split + 1) / p.splits);
     const uint32_t base = smem_u32(smem) + (uint32_t)r * (uint32_t)(SPLIT_LD * 4);
     if (row < p.rows) {
 #pragma unroll 2
@@ -941,8 +965,9 @@ gemm_tc_rows_split_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
         float4 v[8];
 #pragma unroll
-        for (int sp = 0; sp < 8; ++sp)
-          v[sp] = sp < p.splits ? ld_dsmem_v4(base + (uint32_t)c * 4u, (uint32_t)sp) : make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int sp = 0; sp < 8; ++sp)      // the CTA of split sp that holds the same rows: cluster rank sp, or 2 sp + half
+          v[sp] = sp < p.splits ? ld_dsmem_v4(base + (uint32_t)c * 4u, PAIR ? 2u * (uint32_t)sp + half : (uint32_t)sp)
+                                : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
         for (int sp = 0; sp < 8; ++sp) { acc.x += v[sp].x; acc.y += v[sp].y; acc.z += v[sp].z; acc.w += v[sp].w; }
         float y[4] = {acc.x, acc.y, acc.z, acc.w};
@@ -980,18 +1005,19 @@ gemm_tc_rows_split_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
   if (threadIdx.x == 0 && flag[0]) atomicOr(p.err, FZ_ERR_WAIT_TIMEOUT);
 }
 
+template <bool PAIR>
 int launch_rows_split(const CUtensorMap& mx, const CUtensorMap& mw, const Params& p, int tiles_m, int tiles_n, cudaStream_t stream) {
-  constexpr int STAGE_BYTES = (BM + SPLIT_BN) * BK * 2;
+  constexpr int STAGE_BYTES = (BM + (PAIR ? SPLIT_BN / 2 : SPLIT_BN)) * BK * 2;
   const size_t ring = (size_t)p.stages * STAGE_BYTES, partial = (size_t)BM * SPLIT_LD * 4;
   const size_t smem = (ring > partial ? ring : partial) + 1024 + 8 * (2 * p.stages + 1) + 16;
   static size_t allowed = 48 * 1024;
   if (smem > allowed) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_rows_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_rows_split_kernel<PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     allowed = smem;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(tiles_m, tiles_n, p.splits);
+  cfg.gridDim = dim3((PAIR ? 2 : 1) * tiles_m, tiles_n, p.splits);      // PAIR: tiles_m counts tiles of 256 rows
   cfg.blockDim = dim3(NUM_THREADS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
@@ -1003,13 +1029,13 @@ int launch_rows_split(const CUtensorMap& mx, const CUtensorMap& mw, const Params
     ++na;
   }
   attr[na].id = cudaLaunchAttributeClusterDimension;
-  attr[na].val.clusterDim.x = 1;
+  attr[na].val.clusterDim.x = PAIR ? 2 : 1;
   attr[na].val.clusterDim.y = 1;
   attr[na].val.clusterDim.z = (unsigned)p.splits;
   ++na;
   cfg.attrs = attr;
   cfg.numAttrs = na;
-  cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_tc_rows_split_kernel, mx, mw, p);
+  cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_tc_rows_split_kernel<PAIR>, mx, mw, p);
   if (le != cudaSuccess) return (int)le;
   FZ_LAUNCH_CHECK();
   return FZ_OK;
@@ -1126,6 +1152,19 @@ FZ_API int fz_gemm_tc_rows_pairs(int M, int N, int K) {
   const int t128 = (M + BM - 1) / BM;
   const long long tiles = (long long)((t128 + 1) / 2) * ((N + PAIR_BN - 1) / PAIR_BN);
   return ((t128 % 2 == 0 || t128 >= 9) && 4 * tiles >= device_sms()) ? 1 : 0;
+}
+
+// The number of K pieces when pairs of SMs work on 256 x 256 tiles of a product that is cut along K (1: not this way).
+// Only where the one-SM rule cuts K in two and the 128-row tiles come in an even count (no pair's second half empty):
+// the clusters are then (2, 1, 2), as many CTAs as before draw a third fewer bytes each (measured: 29.5 -> 27.6 us for
+// 256 x 6144 x 4096, 62.6 -> 54.7 us for 512 x 4096 x 14336). Clusters of (2, 1, 4) do not pack the GPCs: 16 of them
+// took 41 us for 256 x 4096 x 4096 where 32 clusters of four one-SM pieces take 24.
+FZ_API int fz_gemm_tc_rows_pair_splits(int M, int N, int K) {
+  if (g_rows_mode == 1 || fz_gemm_tc_rows_splits(M, N, K) != 2) return 1;
+  const int t128 = (M + BM - 1) / BM;
+  if (t128 % 2) return 1;
+  const long long tiles = (long long)(t128 / 2) * ((N + SPLIT_BN - 1) / SPLIT_BN);
+  return tiles * 4 <= 128 ? 2 : 1;
 }
 
 // x: [M, K] bf16, w: [N, K] bf16, bias: [N] float32 or null, c: [M, N] float32 (out_dtype 0) or bf16 (1).
@@ -1267,6 +1306,14 @@ static int gemm_tc_impl(const void* x, const void* w, const float* bias, void* c
   if (bn == 256 && !p.swiglu) {
     // So few 128 x 256 tiles that the SMs are not half used, and a K worth cutting: the tiles' K ranges are cut so that
     // about one CTA per SM works (see `gemm_tc_rows_split_kernel`). The count follows from (M, N, K) of the product.
+    const int pair_splits = fz_gemm_tc_rows_pair_splits(M, N, K);
+    if (pair_splits > 1) {      // the same with a pair of SMs on each 256 x 256 tile
+      p.splits = pair_splits;
+      p.stages = (200 * 1024) / ((BM + SPLIT_BN / 2) * BK * 2);
+      if ((st = get_map_bf16(x, M, K, BM, &ma)) != FZ_OK) return st;
+      if ((st = get_map_bf16(w, N, K, SPLIT_BN / 2, &mb)) != FZ_OK) return st;
+      return launch_rows_split<true>(ma, mb, p, (M + 2 * BM - 1) / (2 * BM), (N + SPLIT_BN - 1) / SPLIT_BN, stream);
+    }
     const int splits = fz_gemm_tc_rows_splits(M, N, K);
     if (splits > 1) {
       p.splits = splits;
@@ -1274,7 +1321,7 @@ static int gemm_tc_impl(const void* x, const void* w, const float* bias, void* c
       p.stages = (200 * 1024) / stage;
       if ((st = get_map_bf16(x, M, K, BM, &ma)) != FZ_OK) return st;
       if ((st = get_map_bf16(w, N, K, SPLIT_BN, &mb)) != FZ_OK) return st;
-      return launch_rows_split(ma, mb, p, (M + BM - 1) / BM, (N + SPLIT_BN - 1) / SPLIT_BN, stream);
+      return launch_rows_split<false>(ma, mb, p, (M + BM - 1) / BM, (N + SPLIT_BN - 1) / SPLIT_BN, stream);
     }
   }
   if (bn == 256 && !p.swiglu) {
