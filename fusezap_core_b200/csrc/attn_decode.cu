@@ -773,6 +773,15 @@ int launch_units(const void* q, const void* k_pool, long long pool_rows, const i
   return FZ_OK;
 }
 
+inline int units_sms() {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+      sms = 148;
+  }
+  return sms;
+}
 template <int HD, int BOX>
 int launch_tma(const void* q, const void* k_pool, long long pool_rows, const int* pos, const int* seq_row, const int* seg,
                const int* table, int mb, int page_size, void* out, float* part_o, float* part_ml, int N, int Hq, int Hkv,
@@ -780,6 +789,10 @@ int launch_tma(const void* q, const void* k_pool, long long pool_rows, const int
 #define FZ_U(NS_, MB_, SG_) return launch_units<HD, BOX, NS_, MB_, SG_>(q, k_pool, pool_rows, pos, seq_row, seg, table, mb, page_size, out, part_o, part_ml, N, Hq, Hkv, scale, window, NPU, long_from, err, stream)
   // three stages of 16 keys per warp and two CTAs per SM (eight warps with 24 KB in flight each) measured best
   if (Hq / Hkv > 8) FZ_U(3, 2, false);
+  // So few units that every warp of one CTA per SM gets at most one (a single row at 4,096 keys): four stages, so that
+  // a unit's four groups of 16 keys are all asked for at once instead of the fourth waiting for the first to be
+  // consumed, one memory round trip later (measured at batch 1: 3.337 -> 3.294 ms per step of 32 layers).
+  if ((long long)N * Hkv * NPU <= 4LL * units_sms()) FZ_U(4, 1, true);
   FZ_U(3, 2, true);
 #undef FZ_U
 }
