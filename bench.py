@@ -140,6 +140,9 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--preset", default="llama-3.1-8b")
     ap.add_argument("--prefill-tokens", type=int, default=2048)
+    ap.add_argument("--prefill-prompt", type=int, default=0,
+                    help="also time a prompt of this many tokens taken in portions of --prefill-tokens (chunked prefill): "
+                         "the whole prompt and its last portion, which has the longest prefix behind it")
     ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page (the engine's block_size)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
     ap.add_argument("--no-e2e", action="store_true")
@@ -149,6 +152,9 @@ def main() -> int:
                     help="measurement aid, NOT a benchmark: comma-separated kernel-table operations turned into no-ops "
                          "(e.g. paged_attention, add_rmsnorm, linear_swiglu), to read an operation's cost inside the "
                          "captured step off the difference to a run without it; the line is marked invalid")
+    ap.add_argument("--no-key-cuts", action="store_true",
+                    help="measurement aid: small portions behind long prefixes are not cut along the keys (as before that "
+                         "was built); the line says so in `config`")
     ap.add_argument("--requests", type=int, default=32, help="stream workload: number of requests")
     ap.add_argument("--new-tokens", type=int, default=256, help="stream workload: tokens generated per request")
     a = ap.parse_args()
@@ -179,6 +185,8 @@ def main() -> int:
     t0 = time.time()
     model = random_model(cfg, "bfloat16", dev, seed=0, max_len=a.context)
     torch.cuda.synchronize()
+    if a.no_key_cuts:
+        model.ops.cut_prefill_keys = False
     left_out = [name for name in a.leave_out.split(",") if name]
     for name in left_out:
         if not callable(getattr(model.ops, name, None)):
@@ -287,11 +295,36 @@ def main() -> int:
         return {"value": round(tokens * 1000.0 / ms, 1), "tokens": tokens, "ms": round(ms, 3),
                 "frac": round(flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4), "flops": flops}
 
+    def chunked_prefill_run(prompt: int, portion: int) -> dict:
+        """A prompt longer than a step's portion: one engine step per portion, each timed; median of three prompts."""
+        eng = make_engine(1)
+        ids = rng.integers(0, V, prompt).tolist()
+        totals, lasts = [], []
+        for i in range(4):      # one warm-up prompt (it also records the by-shape graphs), then three timed ones
+            rid = eng.add_request(ids, SamplingParams(max_tokens=1, ignore_eos=True))
+            per_step = []
+            while not eng.requests[rid].generated:
+                torch.cuda.synchronize()
+                start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record()
+                eng.step()
+                end.record()
+                torch.cuda.synchronize()
+                per_step.append(start.elapsed_time(end))
+            eng.release(rid)
+            totals.append(sum(per_step))
+            lasts.append(per_step[-1])
+        total, last = sorted(totals[1:])[1], sorted(lasts[1:])[1]
+        return {"prompt": prompt, "portion": portion, "portions": len(per_step), "ms_total": round(total, 3),
+                "value": round(prompt * 1000.0 / total, 1), "ms_last_portion": round(last, 3),
+                "last_portion_tokens": prompt - (len(per_step) - 1) * portion}
+
     clocks = ClockSampler()
     clocks.start()
     main_run = decode_run(a.batch, a.steps, a.warmup, e2e=not a.no_e2e)
     clk = clocks.stop()
     pre = prefill_run(a.prefill_tokens)
+    chunked = chunked_prefill_run(a.prefill_prompt, a.prefill_tokens) if a.prefill_prompt > a.prefill_tokens else None
     points, points_frac = {}, {}
     if not a.no_points:
         def point(name: str, batch: int, ctx_end: int | None = None) -> None:
@@ -323,6 +356,10 @@ def main() -> int:
         "points": points,
         "points_frac": points_frac,
     }
+    if chunked is not None:
+        line["chunked_prefill"] = chunked
+    if a.no_key_cuts:
+        line["config"]["key_cuts"] = "off"
     if left_out:
         line["invalid"] = "operations left out: " + ", ".join(left_out)
     print(json.dumps(line))

@@ -31,7 +31,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // the host lists 128-row tiles; blockIdx.z picks the 64-row half this CTA serves
-  const int s_idx = tiles[2 * blockIdx.x], r_off = tiles[2 * blockIdx.x + 1] + BM * (int)blockIdx.z;
+  const int s_idx = tiles[3 * blockIdx.x], r_off = tiles[3 * blockIdx.x + 1] + BM * (int)blockIdx.z;
   if (s_idx < 0) return;
   const int h = blockIdx.y, kvh = h / (Hq / Hkv);
   const int row0 = seg[4 * s_idx], n_rows = seg[4 * s_idx + 1], pos0 = seg[4 * s_idx + 2];
@@ -197,7 +197,8 @@ FZ_API int fz_attn_prefill_check(int Hq, int Hkv, int hd) {
   return FZ_OK;
 }
 
-// tiles: int32 [n_tiles][2] = (segment index or -1, first row of the 128-row tile within the portion).
+// tiles: int32 [n_tiles][3] = (segment index or -1, first row of the 128-row tile within the portion, -1: this kernel
+// takes no tile that is cut along the keys).
 FZ_API int fz_attn_prefill(const void* q, const void* k_pool, const void* v_pool, const int* seg, const int* tiles,
                            int n_tiles, const int* table, int mb, long long page_stride, int page_size, void* out,
                            int Hq, int Hkv, int hd, float scale, int window, cudaStream_t stream) {

@@ -38,8 +38,22 @@ constexpr float RESCALE_STEP = 8.f;
 
 // One work item: a 128-row tile of a portion and one query head.
 struct Item {
-  int n_key_tiles, s_idx, h, row, valid_rows, qpos0, last_pos, lo_tile, k_begin;
+  int n_key_tiles, s_idx, h, row, valid_rows, qpos0, last_pos, lo_tile, k_begin, slot;
 };
+
+// An entry of the host's list is (portion or -1, first row of the 128-row tile within the portion, range). range < 0:
+// the entry covers all key tiles of its query tile and its items write the attention output. Otherwise the entry is a
+// piece of a query tile that has few rows and many keys, cut along the keys so that more SMs work on it: key tiles
+// (range & 0xffff) .. + (range >> 16) - 1 of the tile's, and its items leave the unnormalised output and (maximum, sum)
+// of their rows in the float32 scratch slot of the entry, which `attn_prefill_merge_kernel` merges in entry order.
+__device__ __forceinline__ void entry_range(int range, int entry, int& k_begin, int& n_key_tiles, int& slot) {
+  slot = -1;
+  if (range < 0) return;
+  const int lo = range & 0xffff, cnt = range >> 16;
+  n_key_tiles = max(0, min(cnt, n_key_tiles - lo));
+  k_begin += lo * BN;
+  slot = entry;
+}
 
 // Item number `i` of this block. Items are numbered with the tiles in the host's order (most keys first) and the heads
 // within a tile; the blocks take them in rows of gridDim.x items, every other row backwards, so that the block with the
@@ -51,9 +65,10 @@ __device__ __forceinline__ bool get_item(int i, int n_tiles, int Hq, const int* 
   if (k >= (long long)n_tiles * Hq) return false;
   const int ti = (int)(k / Hq);
   it.h = (int)(k - (long long)ti * Hq);
-  it.s_idx = tiles[2 * ti];
-  const int r_off = tiles[2 * ti + 1];
+  it.s_idx = tiles[3 * ti];
+  const int r_off = tiles[3 * ti + 1];
   it.n_key_tiles = 0;
+  it.slot = -1;
   if (it.s_idx >= 0) {
     const int n_rows = seg[4 * it.s_idx + 1], pos0 = seg[4 * it.s_idx + 2];
     it.row = seg[4 * it.s_idx] + r_off;
@@ -63,8 +78,28 @@ __device__ __forceinline__ bool get_item(int i, int n_tiles, int Hq, const int* 
     it.lo_tile = window > 0 ? max(0, it.qpos0 - window + 1) : 0;
     it.k_begin = it.lo_tile & ~(BN - 1);
     it.n_key_tiles = (it.last_pos - it.k_begin) / BN + 1;
+    entry_range(tiles[3 * ti + 2], ti, it.k_begin, it.n_key_tiles, it.slot);
   }
   return true;
+}
+
+// A row's share of an item's result that is a piece along the keys: this thread's `OD` dimensions of the unnormalised
+// output from tensor memory (every lane of the warp takes part in the loads) and, from the thread of the row's first
+// half, the maximum in use and the sum of weights.
+template <int HD, int OD>
+__device__ __forceinline__ void store_piece(uint32_t t_o, float* __restrict__ part_o, float* __restrict__ part_ml, size_t slot_row,
+                                            int hf, bool valid, float m_run, float l_run) {
+  float* dst = part_o + slot_row * HD + hf * OD;
+#pragma unroll
+  for (int c = 0; c < OD; c += 32) {
+    float ov[32];
+    tmem_ld32(t_o + (uint32_t)c, ov);
+    if (valid) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) *(float4*)(dst + c + j) = make_float4(ov[j], ov[j + 1], ov[j + 2], ov[j + 3]);
+    }
+  }
+  if (valid && hf == 0) *(float2*)(part_ml + slot_row * 2) = make_float2(m_run, l_run);
 }
 
 template <int HD, int BOX>
@@ -72,7 +107,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map,
                        const int* __restrict__ seg, const int* __restrict__ tiles, int n_tiles, const int* __restrict__ table,
                        int mb, int page_size, __nv_bfloat16* __restrict__ out, int Hq, int Hkv, float scale_log2, int window,
-                       int* err) {
+                       float* __restrict__ part_o, float* __restrict__ part_ml, int* err) {
   constexpr int HALVES = HD / 64;                     // 64-column halves of a head
   constexpr int KV_STAGES = HD <= 64 ? 4 : 3;         // key tiles and value tiles in flight (what shared memory holds)
   constexpr int HALF_BYTES = 128 * 128;               // 128 rows of 128 bytes
@@ -259,7 +294,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     int g0 = 0;
     Item it;
     for (int i = 0; ok && get_item(i, n_tiles, Hq, seg, tiles, window, it); ++i) {
-      if (it.n_key_tiles == 0) continue;
+      if (it.n_key_tiles == 0) {
+        // (a piece that a layer's window leaves without keys: its rows weigh nothing in the merge)
+        if (it.slot >= 0 && hf == 0 && r < it.valid_rows)
+          *(float2*)(part_ml + (((size_t)it.slot * Hq + it.h) * BM + r) * 2) = make_float2(-INFINITY, 0.f);
+        continue;
+      }
       const int T = it.n_key_tiles, qpos = it.qpos0 + r;
       float m_run = -INFINITY, l_part = 0.f;      // the maximum in use (exp2 domain) and this thread's half of the row's sum
       for (int t = 0; t < T && ok; ++t) {
@@ -368,6 +408,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
       asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
       const float l_run = s_mx[r] + s_mx[BM + r];
       asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");    // both have read: the slots may be written again
+      if (it.slot >= 0) {      // a piece along the keys: the merge kernel finishes the rows
+        store_piece<HD, OD>(t_o, part_o, part_ml, ((size_t)it.slot * Hq + it.h) * BM + r, hf, r < it.valid_rows, m_run, l_run);
+        tc_fence_before();
+        continue;
+      }
       const float inv = 1.0f / l_run;
       __nv_bfloat16* orow = out + (size_t)(it.row + r) * Hq * HD + (size_t)it.h * HD + hf * OD;
       // (the loads from tensor memory are warp-wide instructions: every lane takes part, rows past the portion's end
@@ -424,7 +469,7 @@ __device__ unsigned long long fz_attn_prof[32];
 #define PROF_ADD(i, v)
 #endif
 struct PairItem {
-  int n_key_tiles, s_idx, h0, active1, kvh, row, valid_rows, qpos0, last_pos, lo_tile, k_begin;
+  int n_key_tiles, s_idx, h0, active1, kvh, row, valid_rows, qpos0, last_pos, lo_tile, k_begin, slot;
 };
 
 __device__ __forceinline__ bool get_pair_item(int i, int n_tiles, int Hq, int Hkv, const int* __restrict__ seg,
@@ -438,9 +483,10 @@ __device__ __forceinline__ bool get_pair_item(int i, int n_tiles, int Hq, int Hk
   const int j = pr - it.kvh * ppg;
   it.h0 = it.kvh * gq + 2 * j;
   it.active1 = 2 * j + 1 < gq;
-  it.s_idx = tiles[2 * ti];
-  const int r_off = tiles[2 * ti + 1];
+  it.s_idx = tiles[3 * ti];
+  const int r_off = tiles[3 * ti + 1];
   it.n_key_tiles = 0;
+  it.slot = -1;
   if (it.s_idx >= 0) {
     const int n_rows = seg[4 * it.s_idx + 1], pos0 = seg[4 * it.s_idx + 2];
     it.row = seg[4 * it.s_idx] + r_off;
@@ -450,6 +496,7 @@ __device__ __forceinline__ bool get_pair_item(int i, int n_tiles, int Hq, int Hk
     it.lo_tile = window > 0 ? max(0, it.qpos0 - window + 1) : 0;
     it.k_begin = it.lo_tile & ~(BN - 1);
     it.n_key_tiles = (it.last_pos - it.k_begin) / BN + 1;
+    entry_range(tiles[3 * ti + 2], ti, it.k_begin, it.n_key_tiles, it.slot);
   }
   return true;
 }
@@ -459,7 +506,7 @@ __global__ void __launch_bounds__(PAIR_THREADS, 1)
 attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map,
                          const int* __restrict__ seg, const int* __restrict__ tiles, int n_tiles, const int* __restrict__ table,
                          int mb, int page_size, __nv_bfloat16* __restrict__ out, int Hq, int Hkv, float scale_log2, int window,
-                         int* err) {
+                         float* __restrict__ part_o, float* __restrict__ part_ml, int* err) {
   constexpr int HALVES = HD / 64;
   constexpr int KV_STAGES = HD <= 64 ? 4 : 2;         // key tiles and value tiles in flight
   constexpr int HALF_BYTES = 128 * 128;
@@ -678,7 +725,13 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
     int n_s = 0, n_items = 0;      // key tiles and items this tile has gone through (the phases of s_ready and o_ready)
     PairItem it;
     for (int i = 0; ok && get_pair_item(i, n_tiles, Hq, Hkv, seg, tiles, window, it); ++i) {
-      if (it.n_key_tiles == 0 || tq > it.active1) continue;
+      if (tq > it.active1) continue;
+      if (it.n_key_tiles == 0) {
+        // (a piece that a layer's window leaves without keys: its rows weigh nothing in the merge)
+        if (it.slot >= 0 && hf == 0 && r < it.valid_rows)
+          *(float2*)(part_ml + (((size_t)it.slot * Hq + (it.h0 + tq)) * BM + r) * 2) = make_float2(-INFINITY, 0.f);
+        continue;
+      }
       const int T = it.n_key_tiles, qpos = it.qpos0 + r;
       const int lo_key = window > 0 ? max(it.lo_tile, qpos - window + 1) : it.lo_tile;
       float m_run = -INFINITY, l_part = 0.f;      // the maximum in use and this thread's half of the row's sum
@@ -803,6 +856,11 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
       asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
       const float l_run = s_mx[(tq * 2) * BM + r] + s_mx[(tq * 2 + 1) * BM + r];
       asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");    // both have read: the slots may be written again
+      if (it.slot >= 0) {      // a piece along the keys: the merge kernel finishes the rows
+        store_piece<HD, OD>(t_o, part_o, part_ml, ((size_t)it.slot * Hq + (it.h0 + tq)) * BM + r, hf, r < it.valid_rows, m_run, l_run);
+        tc_fence_before();
+        continue;
+      }
       const float inv = 1.0f / l_run;
       __nv_bfloat16* orow = out + (size_t)(it.row + r) * Hq * HD + (size_t)(it.h0 + tq) * HD + hf * OD;
       // (loads from tensor memory are warp-wide: every lane takes part, rows past the portion's end just do not store)
@@ -838,8 +896,8 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid
 
 template <int HD, int BOX>
 int launch_pair(const void* q, int N, const void* k_pool, long long pool_rows, const int* seg, const int* tiles, int n_tiles,
-                const int* table, int mb, int page_size, void* out, int Hq, int Hkv, float scale, int window, int* err,
-                cudaStream_t stream) {
+                const int* table, int mb, int page_size, void* out, int Hq, int Hkv, float scale, int window, float* part_o,
+                float* part_ml, int* err, cudaStream_t stream) {
   CUtensorMap qm, kvm;
   int st = get_map_bf16(q, N, Hq * HD, BM, &qm);
   if (st != FZ_OK) return st;
@@ -863,15 +921,15 @@ int launch_pair(const void* q, int N, const void* k_pool, long long pool_rows, c
   const long long items = (long long)n_tiles * Hkv * ((gq + 1) / 2);
   dim3 grid((unsigned)(items < sms ? items : sms));
   fz_launch(attn_prefill_pair_kernel<HD, BOX>, grid, dim3(PAIR_THREADS), smem, stream, qm, kvm, seg, tiles, n_tiles, table, mb,
-            page_size, (__nv_bfloat16*)out, Hq, Hkv, scale * 1.4426950408889634f, window, err);
+            page_size, (__nv_bfloat16*)out, Hq, Hkv, scale * 1.4426950408889634f, window, part_o, part_ml, err);
   FZ_LAUNCH_CHECK();
   return FZ_OK;
 }
 
 template <int HD, int BOX>
 int launch(const void* q, int N, const void* k_pool, long long pool_rows, const int* seg, const int* tiles, int n_tiles,
-           const int* table, int mb, int page_size, void* out, int Hq, int Hkv, float scale, int window, int* err,
-           cudaStream_t stream) {
+           const int* table, int mb, int page_size, void* out, int Hq, int Hkv, float scale, int window, float* part_o,
+           float* part_ml, int* err, cudaStream_t stream) {
   CUtensorMap qm, kvm;
   int st = get_map_bf16(q, N, Hq * HD, BM, &qm);
   if (st != FZ_OK) return st;
@@ -895,9 +953,54 @@ int launch(const void* q, int N, const void* k_pool, long long pool_rows, const 
   const long long items = (long long)n_tiles * Hq;
   dim3 grid((unsigned)(items < sms ? items : sms));
   fz_launch(attn_prefill_tc_kernel<HD, BOX>, grid, dim3(NUM_THREADS), smem, stream, qm, kvm, seg, tiles, n_tiles, table, mb, page_size,
-            (__nv_bfloat16*)out, Hq, Hkv, scale * 1.4426950408889634f, window, err);
+            (__nv_bfloat16*)out, Hq, Hkv, scale * 1.4426950408889634f, window, part_o, part_ml, err);
   FZ_LAUNCH_CHECK();
   return FZ_OK;
+}
+// Finishes the query tiles that were cut along the keys. splits: int32 [n_split][2] = (first entry, entries) of a tile,
+// whose entries stand one after the other in the list. One warp per row (grid: 32 groups of four rows, heads, tiles),
+// a lane owns HD / 32 neighbouring dimensions: the pieces' maxima first, then the pieces in entry order, each weighted
+// by 2^(its maximum - the row's), and one division.
+template <int HD>
+__global__ void __launch_bounds__(128)
+attn_prefill_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const int* __restrict__ seg,
+                          const int* __restrict__ tiles, const int* __restrict__ splits, __nv_bfloat16* __restrict__ out, int Hq) {
+  constexpr int PER = HD / 32;
+  fz_grid_launch_dependents();
+  fz_grid_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = blockIdx.x * 4 + warp, h = blockIdx.y;
+  const int first = splits[2 * blockIdx.z], cnt = splits[2 * blockIdx.z + 1];
+  const int s_idx = tiles[3 * first], r_off = tiles[3 * first + 1];
+  if (s_idx < 0 || cnt <= 0) return;
+  const int n_rows = seg[4 * s_idx + 1];
+  if (r >= min(BM, n_rows - r_off)) return;
+  const size_t row = (size_t)seg[4 * s_idx] + r_off + r;
+  auto slot_row = [&](int e) { return ((size_t)(first + e) * Hq + h) * BM + r; };
+  float M = -INFINITY;
+  for (int e = lane; e < cnt; e += 32) M = fmaxf(M, part_ml[slot_row(e) * 2]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+  float acc[PER], l = 0.f;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) acc[j] = 0.f;
+  for (int e = 0; e < cnt; ++e) {
+    const size_t sr = slot_row(e);
+    const float2 ml = *(const float2*)(part_ml + sr * 2);
+    const float f = ml.x == -INFINITY ? 0.f : exp2f(ml.x - M);      // a piece in which the row saw no key weighs nothing
+    if (f == 0.f) continue;
+    l += ml.y * f;
+    const float* src = part_o + sr * HD + lane * PER;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) acc[j] += src[j] * f;
+  }
+  const float inv = l > 0.f ? 1.0f / l : 0.f;
+  __nv_bfloat16* dst = out + row * Hq * HD + (size_t)h * HD + lane * PER;
+#pragma unroll
+  for (int j = 0; j < PER; j += 2) {
+    const __nv_bfloat162 pk = __floats2bfloat162_rn(acc[j] * inv, acc[j + 1] * inv);
+    *(__nv_bfloat162*)(dst + j) = pk;
+  }
 }
 }  // namespace
 
@@ -926,17 +1029,21 @@ FZ_API int fz_attn_prefill_prof(unsigned long long* host32) {
   return (int)e;
 }
 #endif
-// tiles: int32 [n_tiles][2] = (portion index or -1, first row of the 128-row tile within the portion). q: [N, Hq * hd].
+// tiles: int32 [n_tiles][3] = (portion index or -1, first row of the 128-row tile within the portion, range of key tiles or
+// -1: see `entry_range`). q: [N, Hq * hd]. splits: int32 [n_split][2] = (first entry, entries) of every query tile that
+// is cut along the keys; part_o / part_ml: float32 scratch of n_tiles * Hq * 128 * hd and n_tiles * Hq * 128 * 2 elements
+// (only the slots of cut tiles are used; both may be null when n_split is 0).
 FZ_API int fz_attn_prefill_tc(const void* q, int N, const void* k_pool, const void* v_pool, long long page_stride,
-                              int num_pages, const int* seg, const int* tiles, int n_tiles, const int* table, int mb,
-                              int page_size, void* out, int Hq, int Hkv, int hd, float scale, int window, int* err,
-                              cudaStream_t stream) {
+                              int num_pages, const int* seg, const int* tiles, int n_tiles, const int* splits, int n_split,
+                              float* part_o, float* part_ml, const int* table, int mb, int page_size, void* out, int Hq,
+                              int Hkv, int hd, float scale, int window, int* err, cudaStream_t stream) {
   if (n_tiles <= 0) return FZ_OK;
   if (fz_attn_prefill_tc_check(Hq, Hkv, hd, page_size) != FZ_OK || Hq > 65535) return FZ_BAD_SHAPE;
+  if (n_split < 0 || (n_split > 0 && (!splits || !part_o || !part_ml))) return FZ_BAD_SHAPE;
   if (page_stride != 2LL * Hkv * page_size * hd ||
       (const __nv_bfloat16*)v_pool != (const __nv_bfloat16*)k_pool + (long long)Hkv * page_size * hd)
     return FZ_BAD_SHAPE;
-  if ((((uintptr_t)q) | ((uintptr_t)k_pool) | ((uintptr_t)out)) & 15) return FZ_BAD_ALIGNMENT;
+  if ((((uintptr_t)q) | ((uintptr_t)k_pool) | ((uintptr_t)out) | ((uintptr_t)part_o) | ((uintptr_t)part_ml)) & 15) return FZ_BAD_ALIGNMENT;
   const long long pool_rows = (long long)num_pages * 2 * Hkv * page_size;
   // Which kernel: two heads per block where that fills the SMs (measured on a B200: it wins from about 1.5 items per SM
   // on at head size 128: 175 against 198 us for a 4,096-token portion of 32 / 8 heads, 8.4 against 10.1 ms for 32,768
@@ -950,17 +1057,24 @@ FZ_API int fz_attn_prefill_tc(const void* q, int N, const void* k_pool, const vo
   }
   const long long pair_items = (long long)n_tiles * Hkv * ((Hq / Hkv + 1) / 2);
   const bool single = g_prefill_mode == 1 || (g_prefill_mode == 0 && (hd != 128 || 2 * pair_items < 3LL * sms));
+  int st = FZ_OK;
 #define FZ_T(HD_, BOX_)                                                                                                          \
-  return single ? launch<HD_, BOX_>(q, N, k_pool, pool_rows, seg, tiles, n_tiles, table, mb, page_size, out, Hq, Hkv, scale,     \
-                                    window, err, stream)                                                                        \
-                : launch_pair<HD_, BOX_>(q, N, k_pool, pool_rows, seg, tiles, n_tiles, table, mb, page_size, out, Hq, Hkv,      \
-                                         scale, window, err, stream)
+  st = single ? launch<HD_, BOX_>(q, N, k_pool, pool_rows, seg, tiles, n_tiles, table, mb, page_size, out, Hq, Hkv, scale,       \
+                                  window, part_o, part_ml, err, stream)                                                          \
+              : launch_pair<HD_, BOX_>(q, N, k_pool, pool_rows, seg, tiles, n_tiles, table, mb, page_size, out, Hq, Hkv,         \
+                                       scale, window, part_o, part_ml, err, stream)
   // the largest box a page allows: a key tile of 128 keys is then 2, 8 or 16 boxes per column half
   if (hd == 64 && page_size == 8) FZ_T(64, 8);
-  if (hd == 64 && page_size % 64 == 0) FZ_T(64, 64);
-  if (hd == 64) FZ_T(64, 16);
-  if (page_size == 8) FZ_T(128, 8);
-  if (page_size % 64 == 0) FZ_T(128, 64);
-  FZ_T(128, 16);
+  else if (hd == 64 && page_size % 64 == 0) FZ_T(64, 64);
+  else if (hd == 64) FZ_T(64, 16);
+  else if (page_size == 8) FZ_T(128, 8);
+  else if (page_size % 64 == 0) FZ_T(128, 64);
+  else FZ_T(128, 16);
 #undef FZ_T
+  if (st != FZ_OK || n_split == 0) return st;
+  const dim3 grid(BM / 4, (unsigned)Hq, (unsigned)n_split);
+  if (hd == 64) fz_launch(attn_prefill_merge_kernel<64>, grid, dim3(128), 0, stream, (const float*)part_o, (const float*)part_ml, seg, tiles, splits, (__nv_bfloat16*)out, Hq);
+  else fz_launch(attn_prefill_merge_kernel<128>, grid, dim3(128), 0, stream, (const float*)part_o, (const float*)part_ml, seg, tiles, splits, (__nv_bfloat16*)out, Hq);
+  FZ_LAUNCH_CHECK();
+  return FZ_OK;
 }

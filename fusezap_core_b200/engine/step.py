@@ -100,6 +100,7 @@ class StepMeta:
         self.n_rows = self.n_wanted = self.n_segments = 0
         self.segments: list[Segment] = []
         self.max_context = 0      # the longest context (position + 1) among the step's rows
+        self.page_size = 0        # of the cache the step was packed against
         self.max_portion = 0      # the longest portion
         self.plan = None          # whatever the kernel table's `plan_step` keeps about this step (launch sizes and the like)
 
@@ -156,6 +157,7 @@ class StepMeta:
         tok[n:], pos[n:], row[n:], sel[r:] = 0, 0, -1, -1
         seg[len(portions):] = 0
         self.segments = []
+        self.page_size = cache.page_size
         at = w = 0
         self.max_context = self.max_portion = 0
         for s, (p, start) in enumerate(zip(portions, starts)):

@@ -32,26 +32,60 @@ class KernelError(RuntimeError):
     pass
 
 
-def attention_tiles(portions, n_rows: int) -> tuple[list[tuple[int, int]], int]:
+KEY_TILE = 128            # keys per key tile of the tile kernels
+PIECE_MIN_TILES = 8       # a piece of a query tile cut along the keys covers at least this many key tiles
+MAX_PIECES = 48           # pieces in a step at most (each has a float32 scratch slot per head)
+MAX_CUT_TILES = 16        # query tiles of a step that can be cut
+
+
+def attention_tiles(portions, n_rows: int, cut_keys: bool = True, heads: int = 32, items_per_entry: int = 16, sms: int = 148):
     """How the attention kernels split a step. `portions`: (row of the block table, rows, first position) per request
-    in the step. Returns the TILE_ROWS-row tiles of the portions with at least LONG_PORTION tokens as (block-table row,
-    first row within the portion), the ones that see the most keys first, and the number of the step's other rows
-    (short portions, single tokens and padding), which go to the split-key kernel."""
+    in the step. Returns (entries, cuts, short rows).
+
+    entries: the TILE_ROWS-row query tiles of the portions with at least LONG_PORTION tokens as (block-table row, first
+    row within the portion, range), the ones with the most keys first. range -1: the entry covers all keys its rows see.
+    A step with few query tiles and many keys behind them (a small portion of a long prompt) would leave most SMs
+    without work: where the tiles times `heads` (a block's work is a tile and a head) are fewer than three quarters of
+    the SMs, tiles are cut along the keys into pieces of equal length, at least PIECE_MIN_TILES key tiles each, range =
+    first key tile | key tiles << 16, whose partial results a merge kernel adds up. As many pieces are made as give two
+    rounds of items for the SMs (`items_per_entry`: heads, or pairs of heads for the kernel that takes two per block).
+    The pieces stand first in the list (their index is their scratch slot) and the pieces of one tile stand together.
+    cuts: (first entry, entries) per tile that was cut. short rows: the step's other rows (short portions, single tokens
+    and padding), which go to the split-key kernel."""
     tiles, long_rows = [], 0
     for seq_row, n, pos0 in portions:
         if n >= LONG_PORTION:
             long_rows += n
             tiles += [(pos0 + min(r + TILE_ROWS, n), seq_row, r) for r in range(0, n, TILE_ROWS)]
     tiles.sort(key=lambda t: -t[0])
-    return [(s, r) for _, s, r in tiles], n_rows - long_rows
+    short = n_rows - long_rows
+    key_tiles = [(last - 1) // KEY_TILE + 1 for last, _, _ in tiles]
+    total = sum(key_tiles)
+    if not cut_keys or not tiles or 4 * len(tiles) * heads >= 3 * sms or key_tiles[0] < 2 * PIECE_MIN_TILES or \
+            key_tiles[0] >= 1 << 15:
+        return [(s, r, -1) for _, s, r in tiles], [], short
+    target = min(MAX_PIECES, max(2, (2 * sms) // max(1, items_per_entry)))
+    pieces, cuts, whole = [], [], []
+    for (_, s, r), kt in zip(tiles, key_tiles):
+        n = min(kt // PIECE_MIN_TILES, max(1, round(target * kt / total)))
+        if n < 2 or len(pieces) + n > MAX_PIECES or len(cuts) >= MAX_CUT_TILES:
+            whole.append((s, r, -1))
+            continue
+        each = -(-kt // n)
+        cuts.append((len(pieces), -(-kt // each)))
+        pieces += [(s, r, lo | (min(each, kt - lo) << 16)) for lo in range(0, kt, each)]
+    return pieces + whole, cuts, short
 
 
 class AttentionPlan:
-    """What `plan_step` keeps about a step for the attention kernels."""
-    __slots__ = ("tiles", "n_tiles", "n_short_rows")
+    """What `plan_step` keeps about a step for the attention kernels: the device views of the entry list and of the list
+    of tiles cut along the keys, and the counts that size the launches."""
+    __slots__ = ("tiles", "n_tiles", "n_short_rows", "cuts", "n_cuts", "n_pieces")
 
-    def __init__(self, tiles: torch.Tensor | None, n_tiles: int, n_short_rows: int):
+    def __init__(self, tiles: torch.Tensor | None, n_tiles: int, n_short_rows: int, cuts: torch.Tensor | None = None,
+                 n_cuts: int = 0, n_pieces: int = 0):
         self.tiles, self.n_tiles, self.n_short_rows = tiles, n_tiles, n_short_rows
+        self.cuts, self.n_cuts, self.n_pieces = cuts, n_cuts, n_pieces
 
 
 def _p(t: torch.Tensor | None) -> c_void_p:
@@ -83,7 +117,12 @@ class CudaOps(Ops):
         self.fuse_swiglu = True            # gate/up product and SwiGLU in one kernel where the sizes allow it
         self.fuse_argmax = True            # lm_head product and argmax in one pass where no logits are asked for
         self.fuse_rope = True              # q/k/v product, rotation and cache write in one kernel (few-token steps)
+        self.cut_prefill_keys = True       # few query tiles with many keys behind them are cut along the keys
         self._profile = None               # a StepProfile while the engine profiles its steps
+        # the fewest query heads, and the fewest items of a query tile on the prompt kernel, among the attention layers
+        # that `check_attention` has seen (the plan of a step is shared by its layers)
+        self._attn_heads = self._attn_items = 0
+        self._sms = torch.cuda.get_device_properties(self.device).multi_processor_count
 
     # ---- plumbing
     def begin_step(self) -> None:
@@ -155,8 +194,12 @@ class CudaOps(Ops):
 
     # ---- per-step planning (the step function calls these; it knows nothing of the kernels' tiling)
     def step_extra_ints(self, needs: tuple, max_rows: int, max_segments: int) -> int:
-        """int32 this table wants in the step's metadata block for a model whose mixers need `needs`."""
-        return 2 * (max_rows // TILE_ROWS + max_segments) if "attention" in needs else 0
+        """int32 this table wants in the step's metadata block for a model whose mixers need `needs`: three per entry of
+        the attention tile list (a query tile per TILE_ROWS rows and one more per portion, plus the pieces of tiles cut
+        along the keys), two per tile that is cut."""
+        if "attention" not in needs:
+            return 0
+        return 3 * (max_rows // TILE_ROWS + max_segments + MAX_PIECES) + 2 * MAX_CUT_TILES
 
     def plan_step(self, meta, needs: tuple) -> None:
         """Called when a step has been packed on the host, before its one copy to the device: writes the attention
@@ -164,17 +207,28 @@ class CudaOps(Ops):
         if "attention" not in needs:
             meta.plan = None
             return
-        tiles, short = attention_tiles(((sg.seq_row, sg.n, sg.pos0) for sg in meta.segments), meta.n_rows)
-        host = meta.extra_host.reshape(-1, 2)
-        host[len(tiles):] = -1
-        if tiles:
-            host[:len(tiles)] = tiles
-        meta.plan = AttentionPlan(meta.extra.view(-1, 2), len(tiles), short)
+        # tiles are cut along the keys only for the kernel that can leave partial results (tcgen05, pages TMA can box)
+        page = getattr(meta, "page_size", 0)
+        can_cut = self.cut_prefill_keys and self.use_tensor_cores and self.prefill_tcgen05 and \
+            (page == 8 or (page > 0 and page % 16 == 0))
+        entries, cuts, short = attention_tiles(((sg.seq_row, sg.n, sg.pos0) for sg in meta.segments), meta.n_rows, can_cut,
+                                               self._attn_heads or 32, self._attn_items or 16, self._sms)
+        n_list = (meta.extra_host.size - 2 * MAX_CUT_TILES) // 3
+        host = meta.extra_host[:3 * n_list].reshape(-1, 3)
+        host[len(entries):] = -1
+        if entries:
+            host[:len(entries)] = entries
+        host_cuts = meta.extra_host[3 * n_list:].reshape(-1, 2)
+        host_cuts[len(cuts):] = 0
+        if cuts:
+            host_cuts[:len(cuts)] = cuts
+        meta.plan = AttentionPlan(meta.extra[:3 * n_list].view(-1, 3), len(entries), short, meta.extra[3 * n_list:].view(-1, 2),
+                                  len(cuts), sum(c for _, c in cuts))
 
     def step_signature(self, meta) -> tuple:
         """What, beside the row counts, fixes the kernel launches of a step (two steps that agree in it launch alike)."""
         plan = meta.plan
-        return (plan.n_tiles, plan.n_short_rows > 0) if plan is not None else ()
+        return (plan.n_tiles, plan.n_short_rows > 0, plan.n_cuts) if plan is not None else ()
 
     def check_attention(self, num_heads: int, num_kv_heads: int, head_dim: int) -> None:
         if head_dim % 16:
@@ -182,6 +236,10 @@ class CudaOps(Ops):
         if self.core.fz_attn_simt_check(c_int(num_heads), c_int(num_kv_heads), c_int(head_dim)) != 0:
             raise ValueError(f"attention sizes not supported: {num_heads} heads, {num_kv_heads} kv heads, head_dim "
                              f"{head_dim} (need heads % kv_heads == 0 and head_dim <= 512)")
+        # (the prompt kernel takes two heads of a kv head per block at head size 128, else one)
+        items = num_kv_heads * ((num_heads // num_kv_heads + 1) // 2) if head_dim == 128 else num_heads
+        self._attn_heads = min(self._attn_heads or num_heads, num_heads)
+        self._attn_items = min(self._attn_items or items, items)
 
     # ---- kernels
     def embed(self, table, tokens, x, src=None, prev_ids=None, scale: float = 1.0) -> None:
@@ -383,12 +441,23 @@ class CudaOps(Ops):
                 self.launches += 1    # the combine kernel
             if plan.n_tiles > 0 and self.prefill_tcgen05 and \
                     self.tc.fz_attn_prefill_tc_check(c_int(hq), c_int(hkv), c_int(hd), c_int(cache.page_size)) == 0:
-                # rows of long portions on the tcgen05 flash-attention kernel
+                # rows of long portions on the tcgen05 flash-attention kernel; the pieces of tiles that the plan cut along
+                # the keys leave partial results in float32 scratch (a slot per piece and head), merged by a second kernel
+                piece_o = piece_ml = None
+                if plan.n_cuts > 0:
+                    rows = plan.n_pieces * hq * TILE_ROWS
+                    piece_o = self._scratch("prefill pieces", rows * (hd + 2), torch.float32)
+                    piece_ml = piece_o[rows * hd:]
                 self._check(self.tc.fz_attn_prefill_tc(
                     _p(q), c_int(n), _p(k), _p(v), c_longlong(page_stride), c_int(k.shape[0]), _p(meta.seg), _p(plan.tiles),
-                    c_int(plan.n_tiles), _p(table), c_int(table.shape[1]), c_int(cache.page_size), _p(out), c_int(hq),
+                    c_int(plan.n_tiles), _p(plan.cuts), c_int(plan.n_cuts), _p(piece_o), _p(piece_ml), _p(table),
+                    c_int(table.shape[1]), c_int(cache.page_size), _p(out), c_int(hq),
                     c_int(hkv), c_int(hd), c_float(scale), c_int(window), _p(self.err), self._stream()),
                     "paged_attention (prefill, tcgen05)", kv_tiles)
+                if plan.n_cuts > 0:
+                    self.launches += 1    # the merge kernel
+            elif plan.n_tiles > 0 and plan.n_cuts > 0:
+                raise KernelError("paged_attention: the step's tiles are cut along the keys, which only the tcgen05 kernel takes")
             elif plan.n_tiles > 0:
                 self._check(self.tc.fz_attn_prefill(
                     _p(q), _p(k), _p(v), _p(meta.seg), _p(plan.tiles), c_int(plan.n_tiles), _p(table),

@@ -34,12 +34,16 @@ def run_both(Hq, Hkv, hd, bs, window, lengths, rows, seed=0, prefill_mode=0):
     q = torch.randn(n, Hq * hd, generator=g).to(BF)
     o, op = torch.full((n, Hq * hd), float("nan"), dtype=BF, device="cuda"), torch.empty(n, Hq * hd, dtype=BF)
     scale = hd ** -0.5
+    # (tiles are cut along the keys only where the tcgen05 prompt kernel runs: pages that TMA can box)
+    meta = Meta(pos, seq_row, table, "cuda", cut_keys=bs == 8 or bs % 16 == 0, heads=Hq,
+                items=Hkv * ((Hq // Hkv + 1) // 2) if hd == 128 else Hq)
     try:
-        cu.paged_attention(q.cuda(), cc, Meta(pos, seq_row, table, "cuda"), o, Hq, Hkv, hd, scale, window)
+        cu.paged_attention(q.cuda(), cc, meta, o, Hq, Hkv, hd, scale, window)
     finally:
         cu.tc.fz_attn_prefill_tc_mode(0)
     pl.paged_attention(q, cp, Meta(pos, seq_row, table, "cpu"), op, Hq, Hkv, hd, scale, window)
     cu.check_errors()
+    run_both.last_plan = meta.plan
     return o.float().cpu(), op.float(), seq_row
 
 
@@ -78,10 +82,10 @@ def test_decode_rows_past_4096_keys(Hq, Hkv, hd, bs, window):
 def test_prefill_portions(Hq, Hkv, hd, bs, window, mode):
     """Both prompt kernels (one head per block, two heads of a kv head per block) on the same inputs: groups of 1, 2, 3,
     4, 5 and 7 query heads per kv head (odd groups leave a block with a single head), both head sizes."""
-    lengths = [400, 70, 200]
-    # a first portion from position 0 (three tiles), a later portion that continues a request (ragged last tile),
+    lengths = [400, 70, 200, 400, 31]
+    # a first portion from position 0 (two tiles), a later portion that continues a request (ragged last tile),
     # a portion of exactly 8 rows, and single tokens beside them (mixed step)
-    rows = [(0, 0, 150), (2, 61, 139), (1, 62, 8), (0, 399, 1), (1, 30, 1)]
+    rows = [(0, 0, 150), (2, 61, 139), (1, 62, 8), (3, 399, 1), (4, 30, 1)]
     o, op, _ = run_both(Hq, Hkv, hd, bs, window, lengths, rows, prefill_mode=mode)
     close(o, op, "prefill")
 
@@ -98,6 +102,21 @@ def test_prefill_kernels_agree_on_long_portions(Hq, Hkv, hd, window):
     close(one, ref, "one head per block")
     close(two, ref, "two heads per block")
     assert torch.equal(one, two)
+
+
+@pytest.mark.parametrize("mode", [1, 2])
+@pytest.mark.parametrize("Hq,Hkv,hd,bs", [(8, 2, 128, 16), (14, 2, 64, 8), (3, 1, 128, 64)])
+@pytest.mark.parametrize("window", [0, 1500])
+def test_small_portions_behind_long_prefixes(Hq, Hkv, hd, bs, window, mode):
+    """Few query tiles with thousands of keys behind them: the plan cuts the tiles along the keys (pieces of at least
+    eight key tiles, merged by a second kernel), in both prompt kernels; with a window the first pieces of a tile see no
+    key at all. A portion that is not cut and single tokens share the step."""
+    lengths = [5000, 3000, 400, 2000, 77]
+    rows = [(0, 4700, 300), (1, 2950, 50), (2, 0, 130), (3, 1999, 1), (4, 70, 7)]
+    o, op, _ = run_both(Hq, Hkv, hd, bs, window, lengths, rows, seed=3, prefill_mode=mode)
+    plan = run_both.last_plan
+    assert plan.n_cuts >= 2 and plan.n_pieces >= 6, "the long tiles of this step are cut along the keys"
+    close(o, op, "pieces along the keys")
 
 
 def test_padding_rows_and_row_independence():

@@ -10,7 +10,7 @@ import pytest
 import torch
 
 import plain_model
-from util import ROOT, lookahead_scenario, make_model_dir, plain_logits, prompts, random_traffic, read_weights
+from util import ROOT, STD_SCALE, lookahead_scenario, make_model_dir, plain_logits, prompts, random_traffic, read_weights
 
 pytestmark = pytest.mark.gpu
 
@@ -181,6 +181,49 @@ def test_the_serving_path_at_tensor_core_head_sizes(folders, name):
     assert few.stats["preemptions"] > 0 and few.cache.num_free_pages == few.cache.num_pages
     for p, t in zip(P, again):
         follows_plain_model(cfg, w, "bfloat16", p, t, 0.15)
+
+
+def test_small_portions_of_a_long_prompt(tmp_path):
+    """A prompt of 2,500 tokens run in portions of 160 behind one another (head size 128, bfloat16): from 2,048 cached
+    keys on, the one or two query tiles of a portion are cut along the keys into pieces that a second kernel merges,
+    inside steps that are replayed from by-shape graphs. The tokens that follow the prompt are those of the plain model,
+    with the cuts and with the cuts switched off."""
+    import copy
+    from fusezap_core_b200 import LLMEngine, SamplingParams, load_model
+    from fusezap_core_b200.weights import write_random_model
+    from tiny_configs import get
+    cfg, opts = get("tiny_hd128")
+    cfg = copy.deepcopy(cfg)
+    cfg["max_position_embeddings"] = 4096
+    d = str(tmp_path / "tiny_hd128_long")
+    write_random_model(cfg, d, opts["seed"], "float32", opts["norm_noise"], std_scale=STD_SCALE)
+    w = read_weights(d)
+    model = load_model(d, "bfloat16", "cuda:0", max_len=4096)
+    P = prompts(cfg, (2500,), seed=4)
+    sp = SamplingParams(max_tokens=6, ignore_eos=True)
+    outs, plans = {}, {}
+    try:
+        for cut in (True, False):
+            model.ops.cut_prefill_keys = cut
+            eng = LLMEngine(model, num_blocks=200, block_size=16, max_num_seqs=2, max_prefill_tokens=160, max_model_len=4096)
+            seen = []
+            launch = eng._launch
+            def spy(portions, rows, decode_only, all_produce, kind="decode_steps", eng=eng, seen=seen, launch=launch):
+                out = launch(portions, rows, decode_only, all_produce, kind)
+                plan = eng.runner.meta.plan
+                seen.append((plan.n_tiles, plan.n_cuts, plan.n_pieces))
+                return out
+            eng._launch = spy
+            outs[cut] = eng.generate(P, sp)
+            plans[cut] = seen
+            model.ops.check_errors()
+            assert eng.stats["step_graph_replays"] > 0, "portions of equal shape replay a captured step"
+    finally:
+        model.ops.cut_prefill_keys = True
+    assert sum(1 for _, c, _ in plans[True] if c > 0) >= 2 and max(p for _, _, p in plans[True]) >= 4
+    assert all(c == 0 for _, c, _ in plans[False])
+    for toks in outs.values():
+        follows_plain_model(cfg, w, "bfloat16", P[0], toks[0], 0.15)
 
 
 @pytest.mark.parametrize("dtype,name", [("float32", "tiny_qwen2"), ("bfloat16", "tiny_hd128")])

@@ -28,8 +28,9 @@ def close(got: torch.Tensor, ref: torch.Tensor, dtype: str, scale: float | None 
 
 class Meta:
     """Step metadata for kernel tests: the views the kernels read, on any device."""
-    def __init__(self, pos, seq_row, table, device):
+    def __init__(self, pos, seq_row, table, device, cut_keys=True, heads=32, items=16):
         from fusezap_core_b200.kernels.table import AttentionPlan, attention_tiles
+        self.cut_keys, self.heads, self.items = cut_keys, heads, items
         self.pos = torch.tensor(pos, dtype=torch.int32, device=device)
         self.seq_row = torch.tensor(seq_row, dtype=torch.int32, device=device)
         self._table = torch.tensor(table, dtype=torch.int32, device=device)
@@ -43,14 +44,16 @@ class Meta:
                 segs[seq_row[i]] = (i, j - i + 1, pos[i], -1)
             i = j + 1
         seg = [segs.get(s, (0, 0, 0, -1)) for s in range(len(table))]
-        tiles, short = attention_tiles([(s, n, p0) for s, (r0, n, p0, _) in enumerate(seg)], len(pos))
+        tiles, cuts, short = attention_tiles([(s, n, p0) for s, (r0, n, p0, _) in enumerate(seg)], len(pos), cut_keys, heads, items)
         self.seg = torch.tensor(seg, dtype=torch.int32, device=device)
-        self.plan = AttentionPlan(torch.tensor(tiles or [(-1, 0)], dtype=torch.int32, device=device), len(tiles), short)
+        self.plan = AttentionPlan(torch.tensor(tiles or [(-1, 0, -1)], dtype=torch.int32, device=device), len(tiles), short,
+                                  torch.tensor(cuts or [(0, 0)], dtype=torch.int32, device=device), len(cuts),
+                                  sum(c for _, c in cuts))
         self.max_context = max(pos) + 1
     def table(self, group):
         return self._table
     def to(self, device):
-        return Meta(self.pos.tolist(), self.seq_row.tolist(), self._table.tolist(), device)
+        return Meta(self.pos.tolist(), self.seq_row.tolist(), self._table.tolist(), device, self.cut_keys, self.heads, self.items)
 
 
 def make_cache(pages, hkv, bs, hd, dtype, device, write=True):
