@@ -46,7 +46,8 @@ def attention_tiles(portions, n_rows: int, cut_keys: bool = True, heads: int = 3
     row within the portion, range), the ones with the most keys first. range -1: the entry covers all keys its rows see.
     A step with few query tiles and many keys behind them (a small portion of a long prompt) would leave most SMs
     without work: where the tiles times `heads` (a block's work is a tile and a head) are fewer than three quarters of
-    the SMs, tiles are cut along the keys into pieces of equal length, at least PIECE_MIN_TILES key tiles each, range =
+    the SMs and a tile has 2,048 keys and more behind it, or fewer than twice the SMs with 8,192 keys and more, tiles are
+    cut along the keys into pieces of equal length, at least PIECE_MIN_TILES key tiles each, range =
     first key tile | key tiles << 16, whose partial results a merge kernel adds up. As many pieces are made as give two
     rounds of items for the SMs (`items_per_entry`: heads, or pairs of heads for the kernel that takes two per block).
     The pieces stand first in the list (their index is their scratch slot) and the pieces of one tile stand together.
@@ -61,8 +62,12 @@ def attention_tiles(portions, n_rows: int, cut_keys: bool = True, heads: int = 3
     short = n_rows - long_rows
     key_tiles = [(last - 1) // KEY_TILE + 1 for last, _, _ in tiles]
     total = sum(key_tiles)
-    if not cut_keys or not tiles or 4 * len(tiles) * heads >= 3 * sms or key_tiles[0] < 2 * PIECE_MIN_TILES or \
-            key_tiles[0] >= 1 << 15:
+    # (measured through the engine at 32 heads and 8 layers: with at least 0.75 items per SM the cuts pay from about
+    # 8,192 keys on: a 32,000-token prompt in portions of 768 took 226 ms without them and 198 ms with them, in portions
+    # of 1,024 198 and 189 ms; a 7,680-token prompt in portions of 512 38.0 ms without and 38.8 ms with)
+    items = len(tiles) * heads
+    enough = 2 * PIECE_MIN_TILES if 4 * items < 3 * sms else 8 * PIECE_MIN_TILES
+    if not cut_keys or not tiles or items >= 2 * sms or key_tiles[0] < enough or key_tiles[0] >= 1 << 15:
         return [(s, r, -1) for _, s, r in tiles], [], short
     target = min(MAX_PIECES, max(2, (2 * sms) // max(1, items_per_entry)))
     pieces, cuts, whole = [], [], []

@@ -55,8 +55,10 @@ def test_a_small_portion_of_a_long_prompt_is_cut_along_the_keys():
 
 def test_short_contexts_and_many_tiles_stay_whole():
     assert not check([(0, 256, 1000)], 256)[1]                      # 10 key tiles: too few for two pieces of eight
-    assert not check([(0, 512, 50000)], 512)[1], "4 tiles x 32 heads keep most SMs busy"
-    assert check([(0, 512, 50000)], 512, heads=8, items=4)[1], "4 tiles x 8 heads do not"
+    assert not check([(0, 512, 5000)], 512)[1], "4 tiles x 32 heads keep most SMs busy, and the keys are few"
+    assert check([(0, 512, 50000)], 512)[1], "with many keys behind them the cuts pay all the same"
+    assert check([(0, 512, 5000)], 512, heads=8, items=4)[1], "4 tiles x 8 heads leave most SMs without work"
+    assert not check([(0, 1280, 50000)], 1280)[1], "10 tiles x 32 heads are more than two items per SM"
 
 
 def test_random_steps():
