@@ -22,6 +22,11 @@
 //               O stays in tensor memory and is rescaled there only when a row's maximum has grown by more than 2^8
 //               over the maximum in use, so it costs no registers; at the item's end normalise and store the rows.
 // Key tiles start at multiples of 128 in absolute position, so a row's sums do not depend on how the prompt was cut.
+// `attn_prefill_pair_kernel` is the same with two query heads of one kv head per block (608 threads: each head its own
+// score / P and output columns and eight softmax warps, one MMA lane alternating between them, key and value stages
+// fetched once for both). An entry of the host's list may be a PIECE of a query tile along the keys (a small portion
+// behind a long prefix would otherwise leave most SMs idle): its items leave unnormalised rows in float32 scratch and
+// `attn_prefill_merge_kernel` adds a tile's pieces up in entry order.
 // Waits on the CTA's own mbarriers are bounded; a wait that gives up sets the error bit. No multicast.
 // (The reference's paged prefill kernel is an mma.sync kernel with 64-row tiles: fusezap/device/cuda_kernels/
 // attention.py:255-326; `attn_prefill.cu` here is its counterpart and serves the page sizes this kernel refuses.)

@@ -7,9 +7,13 @@
 //                             from HBM once), the instruction's N (BN = 16..128) are the token rows; the tile is stored
 //                             transposed. Nothing is padded to 128 tokens. (The reference's decode GEMM swaps operands the
 //                             same way on sm_90a wgmma: fusezap/device/cuda_kernels/wgmma.py:182-317.)
-// Rows mode is persistent: one CTA per SM walks the 128 x 256 output tiles (token tiles fastest, so the CTAs running at one
-// time share a few weight tiles in L2), the MMA lane alternates between two TMEM accumulators, and the epilogue warps
-// store one tile while the next one is being computed. Swap mode: a CTA computes one 128 x BN tile over one range of K:
+// Rows mode is persistent: the output tiles are walked token tiles fastest (so the CTAs running at one time share a few
+// weight tiles in L2), the MMA lane alternates between two TMEM accumulators, and the epilogue warps store one tile
+// while the next one is being computed. Where the token rows fill them, a PAIR of CTAs (a cluster of two) works on each
+// 256 x 256 tile with `tcgen05.mma.cta_group::2` (`gemm_tc_rows_pair_kernel`); else one CTA per SM walks 128 x 256 tiles
+// (`gemm_tc_rows_kernel`). Products of a few hundred rows with too few tiles for the SMs have their tiles' K ranges cut
+// over a cluster (`gemm_tc_rows_split_kernel`, in both forms). Swap mode: a CTA computes one 128 x BN tile over one
+// range of K:
 //   warp 0  one lane issues the TMA loads (cp.async.bulk.tensor.2d, 128-byte swizzle, 64 k per stage) into a ring of
 //           shared-memory stages guarded by full/empty mbarriers; no multicast;
 //   warp 1  allocates the TMEM accumulator; one lane issues tcgen05.mma (128 x BN x 16, 4 per stage) and commits each
