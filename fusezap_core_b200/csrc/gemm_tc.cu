@@ -312,7 +312,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const float bv = (p.bias && feat < p.feats) ? p.bias[feat] : 0.f;
       const uint32_t base = smem_u32(smem) + (uint32_t)r * 4u;
       float* ex = (float*)smem + BN * BM;            // [16][128]: a group of columns, for the gate / up exchange
-      const int n_my = cols > (int)rank ? (cols - (int)rank + p.splits - 1) / p.splits : 0;   // columns rank, rank + S, ...
+      int n_my = cols > (int)rank ? (cols - (int)rank + p.splits - 1) / p.splits : 0;   // columns rank, rank + S, ...
+      if (p.swiglu && p.splits == 1) {
+        // K not split: the tile is complete in this CTA's shared memory as [token][feature]. Thread r and thread r + 64
+        // share feature r of the tile's 64 (gate in row r, up in row r + 64) and take every other token; the loop is
+        // unrolled so that the loads, exponentials and divisions of eight tokens are in flight together (two of the
+        // four warps walking the tokens one by one took 14 us of a 58 us product at 64 tokens).
+        const int f = r & 63, par = r >> 6, gate_feat = tile_a * BM + f;
+        if (gate_feat < p.feats) {
+          const float bg = p.bias ? p.bias[gate_feat] : 0.f, bu = p.bias ? p.bias[gate_feat + 64] : 0.f;
+          const float* tile = (const float*)smem;
+          __nv_bfloat16* dst = p.c_bf16 + (size_t)(tile_b * BN) * (p.feats >> 1) + tile_a * 64 + f;
+#pragma unroll 8
+          for (int c = par; c < cols; c += 2)
+            dst[(size_t)c * (p.feats >> 1)] = __float2bfloat16_rn(silu_mul(tile[c * BM + f] + bg, tile[c * BM + f + 64] + bu));
+        }
+        n_my = 0;
+      }
       for (int i0 = 0; i0 < n_my; i0 += 16) {
         const int ni = min(16, n_my - i0);
 #pragma unroll 2
