@@ -329,6 +329,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         n_my = 0;
       }
+      if (p.splits > 1 && !p.swiglu && !p.rope) {
+        // the plain sum over the splits: four columns' partial results asked for before the first is added up
+#pragma unroll 4
+        for (int i = 0; i < n_my; ++i) {
+          const int c = (int)rank + i * p.splits;
+          float v[8];
+#pragma unroll
+          for (int sp = 0; sp < 8; ++sp) v[sp] = sp < p.splits ? ld_dsmem(base + (uint32_t)(c * BM) * 4u, (uint32_t)sp) : 0.f;
+          float acc = 0.f;
+#pragma unroll
+          for (int sp = 0; sp < 8; ++sp) acc += v[sp];
+          if (feat < p.feats) {
+            const int m = tile_b * BN + c;
+            if (p.c_f32) p.c_f32[(size_t)m * p.feats + feat] = acc + bv;
+            else p.c_bf16[(size_t)m * p.feats + feat] = __float2bfloat16_rn(acc + bv);
+          }
+        }
+        n_my = 0;
+      }
       for (int i0 = 0; i0 < n_my; i0 += 16) {
         const int ni = min(16, n_my - i0);
 #pragma unroll 2
