@@ -152,6 +152,10 @@ def main() -> int:
                     help="measurement aid, NOT a benchmark: comma-separated kernel-table operations turned into no-ops "
                          "(e.g. paged_attention, add_rmsnorm, linear_swiglu), to read an operation's cost inside the "
                          "captured step off the difference to a run without it; the line is marked invalid")
+    ap.add_argument("--timeline", action="store_true",
+                    help="measurement aid: with libraries built with FZB200_NVCC_EXTRA=-DFZ_TIMELINE, print to stderr what "
+                         "every kernel of the captured decode step costs on the step's critical path (medians over the "
+                         "timed steps); the timestamps cost a little time, so the line is marked invalid")
     ap.add_argument("--no-key-cuts", action="store_true",
                     help="measurement aid: small portions behind long prefixes are not cut along the keys (as before that "
                          "was built); the line says so in `config`")
@@ -242,6 +246,9 @@ def main() -> int:
         torch.cuda.synchronize()
         launches0 = model.ops.launches
         ctx0 = seqs[0].cached
+        if a.timeline:
+            from fusezap_core_b200.kernels import timeline
+            timeline.read(model.ops)
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
         for i in range(steps):
@@ -249,6 +256,14 @@ def main() -> int:
         end.record()
         torch.cuda.synchronize()
         ms = start.elapsed_time(end) / steps
+        if a.timeline:
+            events = timeline.read(model.ops)
+            per = len(events) // steps
+            rows = timeline.per_launch_costs(events[: per * steps], per)
+            print(f"timeline: batch {batch}, {steps} steps of {per} launches; per launch in step order: source file, cost on "
+                  f"the critical path, first block resident before its dependency was met", file=sys.stderr)
+            for i, r in enumerate(rows):
+                print(f"  {i:4d} {r['file']:16s} {r['cost_us']:8.2f} us {r['resident_before_us']:8.2f} us", file=sys.stderr)
         ctx_mean = ctx0 + steps / 2
         out.update(ms=ms, tok_s=batch * 1000.0 / ms, context=ctx_mean,
                    launches=steps * eng.launches_per_graph.get(graph_key(), 0) + (model.ops.launches - launches0),
@@ -360,6 +375,8 @@ def main() -> int:
         line["chunked_prefill"] = chunked
     if a.no_key_cuts:
         line["config"]["key_cuts"] = "off"
+    if a.timeline:
+        line["invalid"] = "timeline timestamps in every kernel"
     if left_out:
         line["invalid"] = "operations left out: " + ", ".join(left_out)
     print(json.dumps(line))

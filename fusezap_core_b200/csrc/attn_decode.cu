@@ -865,3 +865,7 @@ FZ_API int fz_attn_decode(const void* q, const void* k_pool, const void* v_pool,
     return launch<64>(q, k_pool, v_pool, pos, seq_row, seg, table, mb, page_stride, page_size, out, part_o, part_ml, N, Hq, Hkv, scale, window, NP, long_from, stream);
   return launch<128>(q, k_pool, v_pool, pos, seq_row, seg, table, mb, page_stride, page_size, out, part_o, part_ml, N, Hq, Hkv, scale, window, NP, long_from, stream);
 }
+
+#ifdef FZ_TIMELINE
+FZ_TIMELINE_READER(attn_decode)
+#endif

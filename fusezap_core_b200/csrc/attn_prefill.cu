@@ -208,3 +208,7 @@ FZ_API int fz_attn_prefill(const void* q, const void* k_pool, const void* v_pool
     return launch<64>(q, k_pool, v_pool, seg, tiles, n_tiles, table, mb, page_stride, page_size, out, Hq, Hkv, scale, window, stream);
   return launch<128>(q, k_pool, v_pool, seg, tiles, n_tiles, table, mb, page_stride, page_size, out, Hq, Hkv, scale, window, stream);
 }
+
+#ifdef FZ_TIMELINE
+FZ_TIMELINE_READER(attn_prefill)
+#endif

@@ -1083,3 +1083,7 @@ FZ_API int fz_attn_prefill_tc(const void* q, int N, const void* k_pool, const vo
   FZ_LAUNCH_CHECK();
   return FZ_OK;
 }
+
+#ifdef FZ_TIMELINE
+FZ_TIMELINE_READER(attn_prefill_tc)
+#endif

@@ -175,3 +175,7 @@ FZ_API int fz_attn_simt(const void* q, const void* k_pool, const void* v_pool, c
     return dispatch<__nv_bfloat16>(q, k_pool, v_pool, pos, seq_row, table, mb, page_stride, page_size, out, N, Hq, Hkv, hd, scale, window, err, stream);
   return FZ_BAD_DTYPE;
 }
+
+#ifdef FZ_TIMELINE
+FZ_TIMELINE_READER(attn_simt)
+#endif

@@ -48,8 +48,51 @@ __device__ __forceinline__ void fz_rope_pair(float x1, float x2, float c, float 
 // package therefore calls `fz_grid_wait()` before it reads or writes anything another kernel of the step touches (on
 // every path, also the early-exit ones: a grid that finished without waiting would let its successor's wait return
 // while an older grid still runs), and `fz_grid_launch_dependents()` to let its own successor come in early.
+#ifndef FZ_TIMELINE
 __device__ __forceinline__ void fz_grid_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void fz_grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#else
+// Measurement aid (a library built with -DFZ_TIMELINE): thread 0 of block (0, 0, 0) of every launch notes the global
+// timer when the block starts and when its wait on the kernels before returns, two numbers per launch in launch order,
+// in a buffer of the source file the kernel is compiled in (`fz_timeline_<file>` reads and clears it). The difference of
+// two successive launches' second numbers is what the earlier kernel costs on the step's critical path; the first
+// number says how early a kernel's blocks were resident.
+static __device__ unsigned long long fz_tl_buf[2 * 4096];
+static __device__ unsigned int fz_tl_n;
+__device__ __forceinline__ unsigned long long fz_tl_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ bool fz_tl_me() { return (blockIdx.x | blockIdx.y | blockIdx.z | threadIdx.x | threadIdx.y) == 0; }
+__device__ __forceinline__ unsigned int& fz_tl_slot() {
+  __shared__ unsigned int slot;
+  return slot;
+}
+__device__ __forceinline__ void fz_grid_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (fz_tl_me()) {
+    const unsigned int s = atomicAdd(&fz_tl_n, 1u);
+    fz_tl_slot() = s;
+    if (s < 4096u) { fz_tl_buf[2 * s] = fz_tl_now(); fz_tl_buf[2 * s + 1] = 0; }
+  }
+}
+__device__ __forceinline__ void fz_grid_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (fz_tl_me()) {
+    const unsigned int s = fz_tl_slot();
+    if (s < 4096u && fz_tl_buf[2 * s + 1] == 0) fz_tl_buf[2 * s + 1] = fz_tl_now();
+  }
+}
+#define FZ_TIMELINE_READER(name)                                                                          \
+  extern "C" __attribute__((visibility("default"))) int fz_timeline_##name(unsigned long long* host, unsigned int* n) { \
+    cudaError_t e = cudaMemcpyFromSymbol(n, fz_tl_n, sizeof(unsigned int));                               \
+    if (e == cudaSuccess) e = cudaMemcpyFromSymbol(host, fz_tl_buf, sizeof(fz_tl_buf));                   \
+    const unsigned int zero = 0;                                                                          \
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(fz_tl_n, &zero, sizeof(unsigned int));                   \
+    return (int)e;                                                                                        \
+  }
+#endif
 
 // FZB200_PDL=0 in the environment turns programmatic dependent launch off (plain stream order).
 inline bool fz_pdl_enabled() {

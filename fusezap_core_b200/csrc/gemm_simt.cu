@@ -147,3 +147,7 @@ FZ_API int fz_gemm_simt(const void* A, const void* W, const float* bias, void* C
   if (in_dtype == FZ_BF16 && out_dtype == FZ_BF16) return launch<__nv_bfloat16, __nv_bfloat16>(A, W, bias, C, M, N, K, stream);
   return FZ_BAD_DTYPE;
 }
+
+#ifdef FZ_TIMELINE
+FZ_TIMELINE_READER(gemm_simt)
+#endif

@@ -1441,3 +1441,7 @@ static int gemm_tc_impl(const void* x, const void* w, const float* bias, void* c
     default: return launch_rows<64>(ma, mb, p, tiles_m, tiles_n, stream);
   }
 }
+
+#ifdef FZ_TIMELINE
+FZ_TIMELINE_READER(gemm_tc)
+#endif

@@ -967,3 +967,7 @@ FZ_API int fz_argmax_no_alloc(const float* logits, int* out, int rows, int vocab
   }
   return FZ_OK;
 }
+
+#ifdef FZ_TIMELINE
+FZ_TIMELINE_READER(rowwise)
+#endif
