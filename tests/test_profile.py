@@ -45,3 +45,20 @@ def test_ideal_bytes_helpers():
         def __init__(self, n, pos0): self.n, self.pos0 = n, pos0
     # one decoded token at position 99 sees 100 keys; a portion of 3 from position 10 sees 11 + 12 + 13
     assert contexts([Seg(1, 99), Seg(3, 10)]) == 100 + 36
+
+
+def test_timeline_costs_from_timestamps():
+    """`per_launch_costs`: per position in a step, the median over the steps of (next launch's dependency met - this
+    launch's dependency met) and of (dependency met - first block started)."""
+    from fusezap_core_b200.kernels.timeline import per_launch_costs
+    events = []
+    t = 1000
+    for step in range(3):
+        # three launches per step: costs 5, 7 + step (so the median is 8) and a last one that has no successor in its step
+        for name, start_before, cost in (("rowwise", 2, 5), ("gemm_tc", 10, 7 + step), ("attn_decode", 4, 30)):
+            events.append((t - start_before * 1000, t, name))
+            t += cost * 1000
+    rows = per_launch_costs(events, 3)
+    assert [r["file"] for r in rows] == ["rowwise", "gemm_tc", "attn_decode"]
+    assert rows[0]["cost_us"] == 5.0 and rows[1]["cost_us"] == 8.0 and rows[2]["cost_us"] != rows[2]["cost_us"]      # nan
+    assert [r["resident_before_us"] for r in rows] == [2.0, 10.0, 4.0]
