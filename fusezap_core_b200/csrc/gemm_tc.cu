@@ -38,6 +38,7 @@ constexpr int BM = 128;           // TMEM lanes = rows of the 128-row operand
 constexpr int BK = 64;            // k per stage: 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int NUM_THREADS = 192;  // warp 0 TMA, warp 1 MMA, warps 2..5 epilogue
+constexpr int PAIR_THREADS_G = 320;      // the many-token kernels: warps 2..9 epilogue (two per quarter of the tensor-memory lanes)
 
 // ---------------------------------------------------------------------------------------------- cluster helpers
 __device__ __forceinline__ void cluster_sync_all() {
@@ -640,6 +641,8 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       ok = __all_sync(0xffffffffu, mbar_wait(&acc_full[acc], (j >> 1) & 1));
       if (!ok) { flag[0] = 1; break; }
       tc_fence_after();
+      // (Four epilogue warps here. Eight, as in the two-SM kernel, were measured on this kernel and did not pay: the tiles
+      // it gets are narrow or few, and 2,048 tokens at Qwen2.5-0.5B sizes took 3.94 ms with them against 3.77 ms.)
       const uint32_t taddr = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(quad * 32) << 16);
       rows_store_tile<BN>(p, taddr, tm * BM + r, tn * BN);
       tc_fence_before();
@@ -691,7 +694,7 @@ int launch_rows(const CUtensorMap& mx, const CUtensorMap& mw, const Params& p, i
 // leader (cluster rank 0), whose producer expects both CTAs' bytes. The leader's MMA lane issues the instructions for
 // the pair and commits them to the `empty` (and, per tile, `acc_full`) barriers of BOTH CTAs (`tcgen05.commit` with a CTA
 // mask), so each producer refills its own ring and each CTA's epilogue warps read their own tensor memory. One lane of
-// each epilogue warp of both CTAs then arrives on the leader's `acc_empty` barrier (count 8). Every wait is bounded;
+// each epilogue warp of both CTAs then arrives on the leader's `acc_empty` barrier (count 16). Every wait is bounded;
 // both CTAs pass a cluster barrier after the barriers' initialisation and before they leave.
 constexpr int PAIR_BN = 256;
 
@@ -730,7 +733,7 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
 
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(PAIR_THREADS_G, 1)
 gemm_tc_rows_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const Params p,
                          int tiles_m, int tiles_n) {
   constexpr int BN = PAIR_BN;
@@ -754,7 +757,7 @@ gemm_tc_rows_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 8); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 16); }
     flag[0] = 0;
     mbar_init_fence();
   }
@@ -838,8 +841,12 @@ gemm_tc_rows_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
       ok = __all_sync(0xffffffffu, mbar_wait(&acc_full[acc], (j >> 1) & 1));
       if (!ok) { flag[0] = 1; break; }
       tc_fence_after();
-      const uint32_t taddr = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(quad * 32) << 16);
-      rows_store_tile<BN>(p, taddr, (2 * tm + (int)rank) * BM + r, tn * BN);
+      // (warps 2..5 take the tile's first 128 columns, warps 6..9 the other 128: two warps per scheduler, so that one
+      // computes while the other waits; with four warps the epilogue of a tile took longer than the products of a tile
+      // with a short K: 13 us per tile at K = 896, where the products take 5)
+      const int col0 = warp >= 6 ? BN / 2 : 0;
+      const uint32_t taddr = tmem_base + (uint32_t)(acc * BN + col0) + ((uint32_t)(quad * 32) << 16);
+      rows_store_tile<BN / 2>(p, taddr, (2 * tm + (int)rank) * BM + r, tn * BN + col0);
       tc_fence_before();
       __syncwarp();      // every lane of the warp has read its lane of the accumulator
       if (lane == 0) mbar_arrive_cluster(acc_empty0 + 8u * (uint32_t)acc);
@@ -867,7 +874,7 @@ int launch_rows_pair(const CUtensorMap& mx, const CUtensorMap& mw, const Params&
   const int total = tiles_m * tiles_n, most = sms / 2;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * (unsigned)(total < most ? total : most));
-  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.blockDim = dim3(PAIR_THREADS_G);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
