@@ -917,6 +917,54 @@ __device__ __forceinline__ float4 ld_dsmem_v4(uint32_t addr, uint32_t rank) {
   return v;
 }
 
+// The reduction of the K-cut many-token kernel for one token row: the column groups g0 .. g1 - 1 (four columns each) of
+// the tile, every group the sum over the S splits' partial tiles in split order (read through distributed shared
+// memory; U groups' loads are in flight together), plus the bias, stored.
+template <bool PAIR, int S, int U>
+__device__ __forceinline__ void split_reduce_rows(const Params& p, uint32_t base, int g0, int g1, int n0, int row, uint32_t half) {
+  for (int gb = g0; gb < g1; gb += U) {
+    float4 v[U][S];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int sp = 0; sp < S; ++sp)      // the CTA of split sp that holds the same rows: cluster rank sp, or 2 sp + half
+        v[u][sp] = gb + u < g1 ? ld_dsmem_v4(base + (uint32_t)(4 * (gb + u)) * 4u, PAIR ? 2u * (uint32_t)sp + half : (uint32_t)sp)
+                               : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int g = gb + u;
+      if (g >= g1) break;
+      const int n = n0 + 4 * g;
+      if (n >= p.feats) break;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int sp = 0; sp < S; ++sp) { acc.x += v[u][sp].x; acc.y += v[u][sp].y; acc.z += v[u][sp].z; acc.w += v[u][sp].w; }
+      float y[4] = {acc.x, acc.y, acc.z, acc.w};
+      if (p.vec_ok && n + 4 <= p.feats) {
+        if (p.bias) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) y[j] += p.bias[n + j];
+        }
+        if (p.c_f32) {
+          *(float4*)(p.c_f32 + (size_t)row * p.feats + n) = make_float4(y[0], y[1], y[2], y[3]);
+        } else {
+          const __nv_bfloat162 lo = __floats2bfloat162_rn(y[0], y[1]), hi = __floats2bfloat162_rn(y[2], y[3]);
+          *(uint2*)(p.c_bf16 + (size_t)row * p.feats + n) = make_uint2(*(const uint32_t*)&lo, *(const uint32_t*)&hi);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (n + j < p.feats) {
+            const float yj = y[j] + (p.bias ? p.bias[n + j] : 0.f);
+            if (p.c_f32) p.c_f32[(size_t)row * p.feats + n + j] = yj;
+            else p.c_bf16[(size_t)row * p.feats + n + j] = __float2bfloat16_rn(yj);
+          }
+        }
+      }
+    }
+  }
+}
+
 // PAIR: the tile is 256 token rows by 256 features on a pair of CTAs (`tcgen05.mma.cta_group::2`, as in
 // `gemm_tc_rows_pair_kernel`: each CTA loads its 128 rows of X and 128 of the 256 features of W, so a CTA draws 32 KB per
 // k-block instead of 48 KB), the cluster is (2, 1, splits) with the two CTAs of a pair at neighbouring ranks, and a CTA
@@ -1039,41 +1087,11 @@ gemm_tc_rows_split_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
     const int g0 = (int)((long long)groups * split / p.splits), g1 = (int)((long long)groups * (split + 1) / p.splits);
     const uint32_t base = smem_u32(smem) + (uint32_t)r * (uint32_t)(SPLIT_LD * 4);
     if (row < p.rows) {
-#pragma unroll 2
-      for (int g = g0; g < g1; ++g) {
-        const int c = 4 * g, n = tn * BN + c;
-        if (n >= p.feats) break;
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        float4 v[8];
-#pragma unroll
-        for (int sp = 0; sp < 8; ++sp)      // the CTA of split sp that holds the same rows: cluster rank sp, or 2 sp + half
-          v[sp] = sp < p.splits ? ld_dsmem_v4(base + (uint32_t)c * 4u, PAIR ? 2u * (uint32_t)sp + half : (uint32_t)sp)
-                                : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-        for (int sp = 0; sp < 8; ++sp) { acc.x += v[sp].x; acc.y += v[sp].y; acc.z += v[sp].z; acc.w += v[sp].w; }
-        float y[4] = {acc.x, acc.y, acc.z, acc.w};
-        if (p.vec_ok && n + 4 <= p.feats) {
-          if (p.bias) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) y[j] += p.bias[n + j];
-          }
-          if (p.c_f32) {
-            *(float4*)(p.c_f32 + (size_t)row * p.feats + n) = make_float4(y[0], y[1], y[2], y[3]);
-          } else {
-            const __nv_bfloat162 lo = __floats2bfloat162_rn(y[0], y[1]), hi = __floats2bfloat162_rn(y[2], y[3]);
-            *(uint2*)(p.c_bf16 + (size_t)row * p.feats + n) = make_uint2(*(const uint32_t*)&lo, *(const uint32_t*)&hi);
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            if (n + j < p.feats) {
-              const float yj = y[j] + (p.bias ? p.bias[n + j] : 0.f);
-              if (p.c_f32) p.c_f32[(size_t)row * p.feats + n + j] = yj;
-              else p.c_bf16[(size_t)row * p.feats + n + j] = __float2bfloat16_rn(yj);
-            }
-          }
-        }
-      }
+      // (with two splits a thread has 32 groups: eight groups' partial tiles are asked for at once, which took 1 to 2 us
+      // off products of 28 to 61 us; with four splits and 16 groups the same was measured and lost a little)
+      if (p.splits == 2) split_reduce_rows<PAIR, 2, 8>(p, base, g0, g1, tn * BN, row, half);
+      else if (p.splits == 4) split_reduce_rows<PAIR, 4, 2>(p, base, g0, g1, tn * BN, row, half);
+      else split_reduce_rows<PAIR, 8, 2>(p, base, g0, g1, tn * BN, row, half);
     }
   }
   cluster_sync_all();      // nobody leaves while its shared memory may still be read
