@@ -343,13 +343,13 @@ def main() -> int:
     points, points_frac = {}, {}
     if not a.no_points:
         def point(name: str, batch: int, ctx_end: int | None = None) -> None:
-            r = decode_run(batch, max(16, a.steps), max(8, a.warmup), e2e=False, ctx_end=ctx_end)
+            r = decode_run(batch, max(48, a.steps), max(8, a.warmup), e2e=False, ctx_end=ctx_end)
             points[name] = round(r["tok_s"], 1)
             points_frac[name] = round(r["bytes"] / (r["ms"] * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
         point("decode_b1", 1)
         point("decode_b64", 64)
         # the main batch where generation starts (after a prompt of half the context) and half-way through it
-        point(f"decode_b{a.batch}_ctx_start", a.batch, a.context // 2 + max(16, a.steps) + max(8, a.warmup) + 2)
+        point(f"decode_b{a.batch}_ctx_start", a.batch, a.context // 2 + max(48, a.steps) + max(8, a.warmup) + 2)
         point(f"decode_b{a.batch}_ctx_mean", a.batch, 3 * a.context // 4)
     achieved = main_run["bytes"] / (main_run["ms"] * 1e-3) / 1e9
     line = {
