@@ -733,6 +733,18 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
 
+// Tensor memory for a pair: allocated for the pair as one (`cta_group::2`, executed by a warp of each CTA), so that both
+// CTAs hold the same columns whatever else is resident on their SMs (measured with two CTAs per SM: separate
+// `cta_group::1` allocations gave the CTAs of a pair different columns, this gives them the same); the kernels still
+// compare the two addresses before they compute anything.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* slot, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+
 __global__ void __launch_bounds__(PAIR_THREADS_G, 1)
 gemm_tc_rows_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const Params p,
                          int tiles_m, int tiles_n) {
@@ -761,14 +773,14 @@ gemm_tc_rows_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
     flag[0] = 0;
     mbar_init_fence();
   }
-  if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+  if (warp == 1) tmem_alloc_pair(tmem_slot, TMEM_COLS);
   tc_fence_before();
   __syncthreads();
   cluster_sync_all();      // the pair's barriers exist and its tensor memory is allocated before anything crosses over
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // One instruction writes the same tensor-memory address in both CTAs: each allocated all of it once, so the two bases
-  // are equal; if they ever were not, nothing is computed and the error is reported.
+  // One instruction writes the same tensor-memory address in both CTAs: the pair's allocation gives both the same
+  // columns; if the two addresses ever differed, nothing is computed and the error is reported.
   const bool same_base = ld_dsmem_u32(map_to_cta(smem_u32(tmem_slot), rank ^ 1u)) == tmem_base;
   fz_grid_launch_dependents();
   if (warp != 0) fz_grid_wait();
@@ -857,7 +869,7 @@ gemm_tc_rows_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
   cluster_sync_all();      // nobody leaves while the other CTA may still signal its barriers or write its tensor memory
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, TMEM_COLS);
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
   }
   if (threadIdx.x == 0 && flag[0]) atomicOr(p.err, FZ_ERR_WAIT_TIMEOUT);
 }
@@ -998,7 +1010,9 @@ gemm_tc_rows_split_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
     flag[0] = 0;
     mbar_init_fence();
   }
-  if (warp == 1) tmem_alloc(tmem_slot, BN);
+  if (warp == 1) {
+    if constexpr (PAIR) tmem_alloc_pair(tmem_slot, BN); else tmem_alloc(tmem_slot, BN);
+  }
   tc_fence_before();
   __syncthreads();
   if constexpr (PAIR) cluster_sync_all();      // the pair's barriers and tensor memory exist before anything crosses over
@@ -1099,7 +1113,7 @@ gemm_tc_rows_split_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_d, BN);
+    if constexpr (PAIR) tmem_dealloc_pair(tmem_d, BN); else tmem_dealloc(tmem_d, BN);
   }
   if (threadIdx.x == 0 && flag[0]) atomicOr(p.err, FZ_ERR_WAIT_TIMEOUT);
 }
