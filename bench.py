@@ -138,7 +138,9 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
-    ap.add_argument("--preset", default="llama-3.1-8b")
+    ap.add_argument("--preset", default=None,
+                    help="layer sizes: llama-3.1-8b (the default of the decode workload), qwen2.5-0.5b (the default of the "
+                         "stream workload), qwen2.5-32b, or another preset of the package")
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--prefill-prompt", type=int, default=0,
                     help="also time a prompt of this many tokens taken in portions of --prefill-tokens (chunked prefill): "
@@ -162,6 +164,8 @@ def main() -> int:
     ap.add_argument("--requests", type=int, default=32, help="stream workload: number of requests")
     ap.add_argument("--new-tokens", type=int, default=256, help="stream workload: tokens generated per request")
     a = ap.parse_args()
+    if a.preset is None and a.workload != "stream":
+        a.preset = "llama-3.1-8b"
     if a.impl == "reference":
         return reference_arm(a)
     if a.gpus != 1:
@@ -390,7 +394,7 @@ def stream_workload(a) -> int:
     from fusezap_core_b200 import LLMEngine, SamplingParams
     from fusezap_core_b200.cli import load_preset
     from fusezap_core_b200.engine.model import random_model
-    preset = a.preset if a.preset != "llama-3.1-8b" else "qwen2.5-0.5b"
+    preset = a.preset or "qwen2.5-0.5b"
     cfg = load_preset(preset)
     full_layers = cfg["num_hidden_layers"]
     if a.layers:
