@@ -197,6 +197,13 @@ class CacheManager:
         """Back positions [computed, n_tokens) of `req` with pages in every group (all or nothing)."""
         if n_tokens > self.max_model_len:
             raise ValueError(f"{n_tokens} tokens exceed max_model_len {self.max_model_len}")
+        # the common case of a decode step: the request's last page still has room in every group (and it has its state)
+        if req in self.computed and (not self.has_state or req in self.states.owner):
+            for g in self.groups:
+                if g.lens.get(req, 0) * g.page_size < n_tokens:
+                    break
+            else:
+                return
         if not self.can_ensure(req, n_tokens):
             raise OutOfPages(f"request {req!r} needs {self.pages_needed(req, n_tokens)} more pages per group for "
                              f"{n_tokens} tokens; free: {[g.allocator.num_free for g in self.groups]}")
