@@ -79,6 +79,8 @@ class LLMEngine:
         self._unif_h = torch.zeros(2, R, dtype=torch.float64, pin_memory=pin)
         self._topk_h = torch.zeros(2, R, dtype=torch.int32, pin_memory=pin)
         self._topp_h = torch.ones(2, R, dtype=torch.float32, pin_memory=pin)
+        # (numpy views of the same pinned memory: writing an element of a tensor costs microseconds, of an array not)
+        self._sampling_np = tuple(t.numpy() for t in (self._temp_h, self._unif_h, self._topk_h, self._topp_h))
         self._ids_h = torch.zeros(2, R, dtype=torch.int32, pin_memory=pin)
         self._events = [torch.cuda.Event() for _ in range(2)] if pin else None
         self._slot = 0
@@ -280,14 +282,13 @@ class LLMEngine:
         temp_h, unif_h, topk_h, topp_h = self._temp_h[slot], self._unif_h[slot], self._topk_h[slot], self._topp_h[slot]
         R = len(rows)
         filtered = False
+        temp_a, unif_a, topk_a, topp_a = (a[slot] for a in self._sampling_np)
+        temp_a[:R], unif_a[:R], topk_a[:R], topp_a[:R] = 0.0, 0.0, 0, 1.0      # greedy rows and rows sampled on the host
         for req, i in rows:
             p = req.params
-            device_row = p.on_device and not p.greedy
-            temp_h[i] = p.temperature if device_row else 0.0
-            unif_h[i] = req.sampler.next_uniform() if device_row else 0.0
-            topk_h[i] = p.top_k if device_row else 0
-            topp_h[i] = p.top_p if device_row else 1.0
-            filtered = filtered or (device_row and p.filtered)
+            if p.on_device and not p.greedy:
+                temp_a[i], unif_a[i], topk_a[i], topp_a[i] = p.temperature, req.sampler.next_uniform(), p.top_k, p.top_p
+                filtered = filtered or p.filtered
         # all rows greedy: the row-split argmax kernel picks the tokens; else a sampling kernel (argmax for its greedy
         # rows): the plain one, or the one with the top-k and top-p filters if some row has them
         self._greedy_step = all(s.params.greedy or not s.params.on_device for s, _ in rows)
