@@ -92,11 +92,14 @@ def test_continuous_batching_stream_equals_running_alone(qwen_small):
         assert alone.generate([prompts[i]], params)[0] == done[rids[i]], f"request {i}"
 
 
+@pytest.mark.parametrize("preset", ["llama-3.1-8b", "qwen2.5-7b"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_llama8b_layer_sizes(tmp_path, dtype):
+def test_real_layer_sizes(tmp_path, dtype, preset):
+    """One layer at a real model's sizes (Llama-3.1-8B; Qwen2.5-7B: a width of 3,584, 28 heads in 4 groups, 18,944
+    intermediate features, biases), as a portion of more than 128 rows, one of fewer, and a single token."""
     from fusezap_core_b200.cache import CacheManager
     from fusezap_core_b200.engine import Portion, StepRunner, load_model
-    cfg = load_preset("llama-3.1-8b")
+    cfg = load_preset(preset)
     cfg["num_hidden_layers"] = 1
     cfg["vocab_size"] = 2048            # the vocabulary only sizes the embedding and the output matrix
     d = str(tmp_path / "l8b")
@@ -111,7 +114,7 @@ def test_llama8b_layer_sizes(tmp_path, dtype):
     a = run.run([Portion("x", ids[:130], list(range(130)))]).float().cpu().numpy().copy()
     b = run.run([Portion("x", ids[130:199], list(range(69)))]).float().cpu().numpy().copy()
     c = run.run([Portion("x", ids[199:], [0])]).float().cpu().numpy().copy()
-    assert_close(np.concatenate([a, b, c]), ref, dtype, f"llama 8B sizes {dtype}", longest_sum=cfg["intermediate_size"])
+    assert_close(np.concatenate([a, b, c]), ref, dtype, f"{preset} sizes {dtype}", longest_sum=cfg["intermediate_size"])
     model.ops.check_errors()
 
 
