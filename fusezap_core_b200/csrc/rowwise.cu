@@ -99,19 +99,44 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restric
 
 // The same for D % 4 == 0 and D <= 4 * 512 * VPT: 512 threads, a thread keeps its VPT float4 groups of the row in
 // registers (all loads are issued before anything depends on them), so the row is read once.
-template <typename TW, typename TH, int VPT>
+__device__ __forceinline__ float4 load4f(const float* p) { return *(const float4*)p; }
+__device__ __forceinline__ float4 load4f(const __nv_bfloat16* p) {
+  const uint2 u = *(const uint2*)p;
+  const float2 a = __bfloat1622float2(*(const __nv_bfloat162*)&u.x), b = __bfloat1622float2(*(const __nv_bfloat162*)&u.y);
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store4f(float* d, float a, float b, float c, float e) { *(float4*)d = make_float4(a, b, c, e); }
+__device__ __forceinline__ void store4f(__nv_bfloat16* d, float a, float b, float c, float e) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, e);
+  *(uint2*)d = make_uint2(*(const uint32_t*)&lo, *(const uint32_t*)&hi);
+}
+
+template <typename TW, typename TH, int VPT, bool EARLY>
 __global__ void __launch_bounds__(512)
 add_rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ delta, const TW* __restrict__ w,
                        TH* __restrict__ h, const int* __restrict__ rows, int n_src, int D, float eps, int* err) {
   fz_grid_launch_dependents();
-  fz_grid_wait();
-  __shared__ float scratch[32];
   const int r = blockIdx.x;
   const int D4 = D >> 2;
+  // EARLY (w and h 16-byte aligned): the norm's weights, and which row the block reads, depend on nothing a kernel before
+  // this one writes (weights; the step's metadata, packed by the host before the step's first kernel), so they are
+  // asked for ahead of the wait on that kernel instead of after the reduction. Two engines alternating in one process,
+  // Llama-3.1-8B sizes: a batch-1 decode step 3.175 -> 3.128 ms, batch 8 and 64 unchanged.
+  float4 g[VPT];
   int src = r;
+  if constexpr (EARLY) {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int c = threadIdx.x + i * 512;
+      g[i] = c < D4 ? load4f(w + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (rows != nullptr) src = rows[r];
+  }
+  fz_grid_wait();
+  __shared__ float scratch[32];
   TH* hr = h + (size_t)r * D;
   if (rows != nullptr) {
-    src = rows[r];
+    if constexpr (!EARLY) src = rows[r];
     if (src < 0 || src >= n_src) {
       if (src >= n_src && threadIdx.x == 0) atomicOr(err, FZ_ERR_ROW_RANGE);
       for (int d = threadIdx.x; d < D; d += blockDim.x) hr[d] = Cvt<TH>::from_f(0.f);
@@ -156,6 +181,10 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ delta, c
     const int c = threadIdx.x + i * 512;
     if (c < D4) {
       const int d = c * 4;
+      if constexpr (EARLY) {
+        store4f(hr + d, g[i].x * (v[i].x * scale), g[i].y * (v[i].y * scale), g[i].z * (v[i].z * scale), g[i].w * (v[i].w * scale));
+        continue;
+      }
       hr[d] = Cvt<TH>::from_f(Cvt<TW>::to_f(w[d]) * (v[i].x * scale));
       hr[d + 1] = Cvt<TH>::from_f(Cvt<TW>::to_f(w[d + 1]) * (v[i].y * scale));
       hr[d + 2] = Cvt<TH>::from_f(Cvt<TW>::to_f(w[d + 2]) * (v[i].z * scale));
@@ -168,9 +197,11 @@ template <typename TW, typename TH>
 static int launch_norm(float* x, const float* delta, const void* w, void* h, const int* rows, int n_out, int n_src, int D,
                        float eps, int* err, cudaStream_t stream) {
   const bool vec = D % 4 == 0 && D <= 4 * 512 * 8 && (((uintptr_t)x | (uintptr_t)delta) & 15) == 0;
+  const bool early = (((uintptr_t)w | (uintptr_t)h) & 15) == 0;      // vector loads of the weights, vector stores of h
   if (vec) {
     const int groups = (D / 4 + 511) / 512;
-#define FZ_V(V) fz_launch(add_rmsnorm_vec_kernel<TW, TH, V>, dim3(n_out), dim3(512), 0, stream, x, delta, (const TW*)w, (TH*)h, rows, n_src, D, eps, err)
+#define FZ_V(V) do { if (early) fz_launch(add_rmsnorm_vec_kernel<TW, TH, V, true>, dim3(n_out), dim3(512), 0, stream, x, delta, (const TW*)w, (TH*)h, rows, n_src, D, eps, err); \
+    else fz_launch(add_rmsnorm_vec_kernel<TW, TH, V, false>, dim3(n_out), dim3(512), 0, stream, x, delta, (const TW*)w, (TH*)h, rows, n_src, D, eps, err); } while (0)
     if (groups <= 1) FZ_V(1); else if (groups <= 2) FZ_V(2); else if (groups <= 4) FZ_V(4); else FZ_V(8);
 #undef FZ_V
   } else {

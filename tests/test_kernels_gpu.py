@@ -104,6 +104,11 @@ def test_add_rmsnorm(dtype, D):
         cu.add_rmsnorm(xc, None, w.cuda(), 1e-5, h)
         pl.add_rmsnorm(xp, None, w, 1e-5, hp)
         close(h, hp, dtype)
+        # weights that do not start on a 16-byte boundary: the kernel that reads them one by one, with the same bits
+        w_off = torch.cat([w[:1], w]).cuda()[1:]
+        h_off = torch.empty_like(h)
+        cu.add_rmsnorm(xc, None, w_off, 1e-5, h_off)
+        assert torch.equal(h_off, h), "unaligned weights"
         rows = torch.tensor([18, 0, -1, 7], dtype=torch.int32)
         hr, hrp = torch.empty(4, D, dtype=DT[dtype], device="cuda"), torch.empty(4, D, dtype=DT[dtype])
         before = xc.clone()
