@@ -321,7 +321,7 @@ attn_decode_units_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_
                          const int* __restrict__ pos, const int* __restrict__ seq_row, const int* __restrict__ seg,
                          const int* __restrict__ table, int mb, int page_size, float* __restrict__ part_o,
                          float* __restrict__ part_ml, int N, int Hq, int Hkv, int NPU, float scale_log2, int window,
-                         int long_from, int* err) {
+                         int long_from, int single, int* err) {
   // SMALLG (at most 8 query heads per kv head): the transposed products of `attend16_small`
   constexpr int KSTEPS = HD / 16, OB = SMALLG ? HD / 16 : HD / 8, QW = SMALLG ? 2 : 4, HALVES = HD / 64;
   constexpr int HALF_BYTES = 16 * 128;                 // one column half of a 16-key group
@@ -334,15 +334,12 @@ attn_decode_units_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_
   uint64_t* bars = (uint64_t*)(smem + 4 * WARP_BYTES);                   // [4 warps][NSTAGE]
   int* s_pre = (int*)(bars + 4 * NSTAGE);                                // [N + 1]: units before row n
 
-  // Prologue that depends on nothing another kernel writes: barriers, and zeros in the staging buffers (a box that is
-  // not fetched because it lies past the row's position must hold finite bits: P = 0 times NaN is NaN).
+  // Prologue that depends on nothing another kernel writes: the barriers.
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
     for (int i = 0; i < 4 * NSTAGE; ++i) fztma::mbar_init(&bars[i], 1);
     fztma::mbar_init_fence();
   }
-  for (int e = tid; e < 4 * WARP_BYTES / 16; e += THREADS) ((uint4*)smem)[e] = make_uint4(0u, 0u, 0u, 0u);
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   __syncthreads();
   fz_grid_launch_dependents();
   // What follows up to the wait reads only the step's metadata (positions, rows, block tables): the host wrote it before
@@ -351,10 +348,12 @@ attn_decode_units_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_
   const int G = Hq / Hkv;
   // units of every row (0 for padding rows and for rows of long portions), then their running sum
   for (int n = tid; n < N; n += THREADS) {
+    // `single`: every portion of the step is one token, so no row belongs to a long portion and the portion's record
+    // need not be asked for (a load that could only start when the row number has arrived)
     const int row = seq_row[n];
+    const int p = pos[n];
     int cnt = 0;
-    if (row >= 0 && seg[row * 4 + 1] < long_from) {
-      const int p = pos[n];
+    if (row >= 0 && (single || seg[row * 4 + 1] < long_from)) {
       const int lo = window > 0 ? max(0, p - window + 1) : 0;
       cnt = (unit_of(p) - unit_of(lo) + 1) * Hkv;
     }
@@ -408,10 +407,11 @@ attn_decode_units_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_
     // the unit's block-table entries, one per lane (at most 32: 256 keys in pages of 8), asked for now and used
     // when the unit's loads are issued
     if (!with_pages) return;
-    c.first_new = seg[seq_row[n] * 4 + 2];
+    const int row = seq_row[n];
+    c.first_new = single ? c.p : seg[row * 4 + 2];      // a single token is its portion's first
     c.page0 = (c.key0 + 16 * c.g) / page_size;
     const int pi = c.page0 + lane;
-    c.pages = (pi < mb && pi * page_size <= c.p) ? __ldg(table + (size_t)seq_row[n] * mb + pi) : -1;
+    c.pages = (pi < mb && pi * page_size <= c.p) ? __ldg(table + (size_t)row * mb + pi) : -1;
   };
 
   const uint32_t s_warp = s_base + warp * WARP_BYTES;
@@ -424,16 +424,32 @@ attn_decode_units_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_
     uint64_t* bar = &wbars[stage];
     int rows[16 / BOX];
     uint32_t bytes = 0;
+    bool zeroed = false;
 #pragma unroll
     for (int sub = 0; sub < 16 / BOX; ++sub) {
       const int key = key0 + sub * BOX;
       rows[sub] = -1;
       const int pi = key / page_size;
       const int page = __shfl_sync(0xffffffffu, c.pages, (pi - c.page0) & 31);
-      if (key > c.p || key + BOX - 1 < c.lo) continue;       // nothing visible in this box
-      if (page < 0) { if (lane == 0) atomicOr(err, FZ_ERR_NO_PAGE); continue; }
+      const bool unseen = key > c.p || key + BOX - 1 < c.lo;     // nothing visible in this box
+      if (unseen || page < 0) {
+        if (!unseen && lane == 0) atomicOr(err, FZ_ERR_NO_PAGE);
+        // The box is not fetched: its part of the stage must hold finite bits (P = 0 times NaN is NaN), so the warp
+        // writes zeros there. (Zeroing all stages when the block starts took 0.6 us of every block's start, which
+        // counts for the blocks that become resident only when the kernel before this one leaves their SM.)
+        uint8_t* st = smem + (size_t)warp * WARP_BYTES + (size_t)stage * STAGE_BYTES;
+#pragma unroll
+        for (int h = 0; h < 2 * HALVES; ++h)            // the K halves, then the V halves
+          for (int e = lane; e < BOX * 128 / 16; e += 32) ((uint4*)(st + h * HALF_BYTES + sub * BOX * 128))[e] = make_uint4(0u, 0u, 0u, 0u);
+        zeroed = true;
+        continue;
+      }
       rows[sub] = page * rows_per_page + c.kvh * page_size + (key - pi * page_size);
       bytes += 2 * HALVES * BOX * 128;
+    }
+    if (zeroed) {       // (warp-uniform) ordinary stores before later bulk copies into the same bytes
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
     }
     if (lane != 0) return;
     fztma::mbar_expect_tx(bar, bytes);
@@ -452,8 +468,8 @@ attn_decode_units_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_
   // where the arithmetic stands, where the loads stand, and the unit after that one (its block-table entries are on
   // their way while the loads of the unit before it are issued)
   UnitCursor cc, ci, cn;
-  load_unit(cc, u_begin, 0, false);
   load_unit(ci, u_begin, 0, true);
+  cc = ci;             // (the arithmetic never looks at the pages)
   load_unit(cn, u_begin + 1, ci.n, true);
   auto advance_loads = [&]() {
     if (++ci.g >= ci.g_end) {
@@ -737,7 +753,7 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
 template <int HD, int BOX, int NSTAGE, int MINB, bool SMALLG>
 int launch_units(const void* q, const void* k_pool, long long pool_rows, const int* pos, const int* seq_row, const int* seg,
                  const int* table, int mb, int page_size, void* out, float* part_o, float* part_ml, int N, int Hq, int Hkv,
-                 float scale, int window, int NPU, int long_from, int* err, cudaStream_t stream) {
+                 float scale, int window, int NPU, int long_from, int single, int* err, cudaStream_t stream) {
   CUtensorMap map;
   int st = fztma::get_map_bf16(k_pool, pool_rows, HD, BOX, &map);
   if (st != FZ_OK) return st;
@@ -763,7 +779,7 @@ int launch_units(const void* q, const void* k_pool, long long pool_rows, const i
   if (ctas > (long long)sms * MINB) ctas = (long long)sms * MINB;
   fz_launch(attn_decode_units_kernel<HD, BOX, NSTAGE, MINB, SMALLG>, dim3((unsigned)ctas), dim3(THREADS), smem, stream, map,
             (const __nv_bfloat16*)q, pos, seq_row, seg, table, mb, page_size, part_o, part_ml, N, Hq, Hkv, NPU,
-            scale * 1.4426950408889634f, window, long_from, err);
+            scale * 1.4426950408889634f, window, long_from, single, err);
   FZ_LAUNCH_CHECK();
   dim3 cgrid(Hq, N);
   // shared memory: the row's (max, sum) pairs, then 128 float4 and up to 8 float2 of the groups' results
@@ -785,8 +801,8 @@ inline int units_sms() {
 template <int HD, int BOX>
 int launch_tma(const void* q, const void* k_pool, long long pool_rows, const int* pos, const int* seq_row, const int* seg,
                const int* table, int mb, int page_size, void* out, float* part_o, float* part_ml, int N, int Hq, int Hkv,
-               float scale, int window, int NPU, int long_from, int* err, cudaStream_t stream) {
-#define FZ_U(NS_, MB_, SG_) return launch_units<HD, BOX, NS_, MB_, SG_>(q, k_pool, pool_rows, pos, seq_row, seg, table, mb, page_size, out, part_o, part_ml, N, Hq, Hkv, scale, window, NPU, long_from, err, stream)
+               float scale, int window, int NPU, int long_from, int single, int* err, cudaStream_t stream) {
+#define FZ_U(NS_, MB_, SG_) return launch_units<HD, BOX, NS_, MB_, SG_>(q, k_pool, pool_rows, pos, seq_row, seg, table, mb, page_size, out, part_o, part_ml, N, Hq, Hkv, scale, window, NPU, long_from, single, err, stream)
   // three stages of 16 keys per warp and two CTAs per SM (eight warps with 24 KB in flight each) measured best
   if (Hq / Hkv > 8) FZ_U(3, 2, false);
   // So few units that every warp of one CTA per SM gets at most one (a single row at 4,096 keys): four stages, so that
@@ -836,13 +852,15 @@ FZ_API int fz_attn_decode_check(int Hq, int Hkv, int hd) {
 FZ_API int fz_attn_partitions(int max_context) { return max_context <= 0 ? 1 : unit_of(max_context - 1) + 1; }
 
 // Float32 scratch the call needs: part_o N * Hq * NP * hd floats, part_ml N * Hq * NP * 2 floats.
+// single_tokens != 0: every portion of the step is one token (the caller knows; the kernel then reads no portion records).
 // num_pages > 0 and a pool laid out as (pages, 2, Hkv, page_size, hd) with v_pool = k_pool + Hkv * page_size * hd select
 // the TMA variant where the page size allows it (8, 16 or a multiple of 16); otherwise the cp.async variant runs.
 FZ_API int fz_attn_decode(const void* q, const void* k_pool, const void* v_pool, const int* pos, const int* seq_row,
                           const int* seg, const int* table, int mb, long long page_stride, int page_size, void* out,
                           float* part_o, float* part_ml, int N, int Hq, int Hkv, int hd, float scale, int window,
-                          int max_context, int long_from, int num_pages, int* err, cudaStream_t stream) {
+                          int max_context, int long_from, int single_tokens, int num_pages, int* err, cudaStream_t stream) {
   if (N <= 0) return FZ_OK;
+  const int single = single_tokens ? 1 : 0;
   if (fz_attn_decode_check(Hq, Hkv, hd) != FZ_OK || page_size <= 0) return FZ_BAD_SHAPE;
   if (N > 65535 || Hkv > 65535) return FZ_TOO_LARGE;
   const int NP = max_context <= 0 ? 1 : (max_context + PART - 1) / PART;
@@ -854,7 +872,7 @@ FZ_API int fz_attn_decode(const void* q, const void* k_pool, const void* v_pool,
                       (long long)N * Hkv * NPU < (1LL << 30) && (size_t)NPU * 8 < 40 * 1024 && !getenv("FZB200_NO_TMA_ATTN");
   if (tma_ok) {
     const long long pool_rows = (long long)num_pages * 2 * Hkv * page_size;
-#define FZ_T(HD_, BOX_) return launch_tma<HD_, BOX_>(q, k_pool, pool_rows, pos, seq_row, seg, table, mb, page_size, out, part_o, part_ml, N, Hq, Hkv, scale, window, NPU, long_from, err, stream)
+#define FZ_T(HD_, BOX_) return launch_tma<HD_, BOX_>(q, k_pool, pool_rows, pos, seq_row, seg, table, mb, page_size, out, part_o, part_ml, N, Hq, Hkv, scale, window, NPU, long_from, single, err, stream)
     if (hd == 64 && page_size == 8) FZ_T(64, 8);
     if (hd == 64) FZ_T(64, 16);
     if (page_size == 8) FZ_T(128, 8);

@@ -85,12 +85,14 @@ def attention_tiles(portions, n_rows: int, cut_keys: bool = True, heads: int = 3
 class AttentionPlan:
     """What `plan_step` keeps about a step for the attention kernels: the device views of the entry list and of the list
     of tiles cut along the keys, and the counts that size the launches."""
-    __slots__ = ("tiles", "n_tiles", "n_short_rows", "cuts", "n_cuts", "n_pieces")
+    __slots__ = ("tiles", "n_tiles", "n_short_rows", "cuts", "n_cuts", "n_pieces", "single_tokens")
 
     def __init__(self, tiles: torch.Tensor | None, n_tiles: int, n_short_rows: int, cuts: torch.Tensor | None = None,
-                 n_cuts: int = 0, n_pieces: int = 0):
+                 n_cuts: int = 0, n_pieces: int = 0, single_tokens: bool = False):
         self.tiles, self.n_tiles, self.n_short_rows = tiles, n_tiles, n_short_rows
         self.cuts, self.n_cuts, self.n_pieces = cuts, n_cuts, n_pieces
+        # every portion of the step is one token (a decode step): the kernel for short rows then asks for no portion records
+        self.single_tokens = single_tokens
 
 
 def _p(t: torch.Tensor | None) -> c_void_p:
@@ -228,12 +230,12 @@ class CudaOps(Ops):
         if cuts:
             host_cuts[:len(cuts)] = cuts
         meta.plan = AttentionPlan(meta.extra[:3 * n_list].view(-1, 3), len(entries), short, meta.extra[3 * n_list:].view(-1, 2),
-                                  len(cuts), sum(c for _, c in cuts))
+                                  len(cuts), sum(c for _, c in cuts), single_tokens=all(sg.n == 1 for sg in meta.segments))
 
     def step_signature(self, meta) -> tuple:
         """What, beside the row counts, fixes the kernel launches of a step (two steps that agree in it launch alike)."""
         plan = meta.plan
-        return (plan.n_tiles, plan.n_short_rows > 0, plan.n_cuts) if plan is not None else ()
+        return (plan.n_tiles, plan.n_short_rows > 0, plan.n_cuts, plan.single_tokens) if plan is not None else ()
 
     def check_attention(self, num_heads: int, num_kv_heads: int, head_dim: int) -> None:
         if head_dim % 16:
@@ -442,7 +444,8 @@ class CudaOps(Ops):
                     _p(q), _p(k), _p(v), _p(meta.pos), _p(meta.seq_row), _p(meta.seg), _p(table), c_int(table.shape[1]),
                     c_longlong(page_stride), c_int(cache.page_size), _p(out), _p(part_o), _p(part_ml), c_int(n),
                     c_int(hq), c_int(hkv), c_int(hd), c_float(scale), c_int(window), c_int(meta.max_context),
-                    c_int(LONG_PORTION), c_int(k.shape[0]), _p(self.err), self._stream()), "paged_attention (decode)", kv)
+                    c_int(LONG_PORTION), c_int(1 if plan.single_tokens else 0), c_int(k.shape[0]), _p(self.err), self._stream()),
+                    "paged_attention (decode)", kv)
                 self.launches += 1    # the combine kernel
             if plan.n_tiles > 0 and self.prefill_tcgen05 and \
                     self.tc.fz_attn_prefill_tc_check(c_int(hq), c_int(hkv), c_int(hd), c_int(cache.page_size)) == 0:

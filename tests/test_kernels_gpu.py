@@ -48,7 +48,7 @@ class Meta:
         self.seg = torch.tensor(seg, dtype=torch.int32, device=device)
         self.plan = AttentionPlan(torch.tensor(tiles or [(-1, 0, -1)], dtype=torch.int32, device=device), len(tiles), short,
                                   torch.tensor(cuts or [(0, 0)], dtype=torch.int32, device=device), len(cuts),
-                                  sum(c for _, c in cuts))
+                                  sum(c for _, c in cuts), single_tokens=all(v[1] == 1 for v in segs.values()))
         self.max_context = max(pos) + 1
     def table(self, group):
         return self._table
