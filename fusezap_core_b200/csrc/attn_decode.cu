@@ -624,21 +624,22 @@ attn_decode_units_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_
   }
 }
 
-// One block of 128 threads per (token row, query head). A thread owns four neighbouring output dimensions (one float4 per
-// partial result); the HD / 4 threads that cover a row form a group, and the 128 / (HD / 4) groups share the row's blocks
+// One block of 128 or 256 threads per (token row, query head). A thread owns four neighbouring output dimensions (one float4 per
+// partial result); the HD / 4 threads that cover a row form a group, and the groups share the row's blocks
 // of the key axis out among themselves (a block: the up to four 64-key units of 256 keys below key 4096, either already
 // merged by the unit kernel or merged here in rising order with the same arithmetic; a 256-key unit above). The groups'
 // results are merged in group order, normalised and rounded to bf16. All (max, sum) pairs of the row are brought into
 // shared memory first, so that what a thread loads next never waits on a load before it. Which units a row has follows
 // from its position and the window alone, as in the kernel above.
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 attn_combine_units_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                           const int* __restrict__ pos, const int* __restrict__ seq_row, const int* __restrict__ seg,
                           __nv_bfloat16* __restrict__ out, int Hq, int HD, int NPU, int window, int long_from) {
   extern __shared__ float2 s_ml[];             // [units of the row], then the groups' results
   fz_grid_launch_dependents();
   const int n = blockIdx.y, h = blockIdx.x, tid = threadIdx.x;
-  const int per_row = HD >> 2, groups = 128 / per_row;          // threads per row, groups per block
+  const int CT = blockDim.x;
+  const int per_row = HD >> 2, groups = CT / per_row;           // threads per row, groups per block
   const int grp = tid / per_row, d4 = (tid - grp * per_row) * 4;
   const int row = seq_row[n];
   const bool skip = row >= 0 && seg[row * 4 + 1] >= long_from;
@@ -654,20 +655,25 @@ attn_combine_units_kernel(const float* __restrict__ part_o, const float* __restr
   const int u0 = unit_of(lo), u1 = unit_of(p), cnt = u1 - u0 + 1;
   const float2* ml = (const float2*)part_ml + ((size_t)n * Hq + h) * NPU + u0;
   const float* po = part_o + (((size_t)n * Hq + h) * NPU + u0) * HD + d4;
-  for (int i = tid; i < cnt; i += 128) s_ml[i] = ml[i];
+  for (int i = tid; i < cnt; i += CT) s_ml[i] = ml[i];
   __syncthreads();
-  float4* s_o = (float4*)(s_ml + cnt + (cnt & 1));              // [groups][per_row]
-  float2* s_g = (float2*)(s_o + groups * per_row);              // [groups]: (max, sum)
+  // The row's blocks are merged in VG chains (chain v: blocks v, v + VG, ...), and the chains then in rising order: VG
+  // is the group count of a block of 256 threads, and a block of 128 threads walks two chains per group, so the order
+  // of the merges, and with it every bit of the result, does not depend on the block's size.
+  const int VG = 256 / per_row, lane_in = tid - grp * per_row;
+  float4* s_o = (float4*)(s_ml + cnt + (cnt & 1));              // [VG][per_row]
+  float2* s_g = (float2*)(s_o + VG * per_row);                  // [VG]: (max, sum)
   const int n_small = u0 < SMALL_UNITS ? (min(u1, SMALL_UNITS - 1) >> 2) - (u0 >> 2) + 1 : 0;
   const int big0 = max(u0, SMALL_UNITS);
   const int n_items = n_small + (u1 >= SMALL_UNITS ? u1 - big0 + 1 : 0);
-  float M = -INFINITY, L = 0.f;
-  float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
   auto merge4 = [](float4& o, const float4& o2, float fa, float fb) {
     o.x = merge_unit_value(o.x, o2.x, fa, fb); o.y = merge_unit_value(o.y, o2.y, fa, fb);
     o.z = merge_unit_value(o.z, o2.z, fa, fb); o.w = merge_unit_value(o.w, o2.w, fa, fb);
   };
-  for (int k = grp; k < n_items; k += groups) {
+  for (int v = grp; v < VG; v += groups) {
+  float M = -INFINITY, L = 0.f;
+  float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int k = v; k < n_items; k += VG) {
     float Mb, Lb;
     float4 Ob;
     if (k < n_small) {
@@ -703,13 +709,16 @@ attn_combine_units_kernel(const float* __restrict__ part_o, const float* __restr
     merge_unit_scalars(M, L, Mb, Lb, fa, fb);
     merge4(O, Ob, fa, fb);
   }
-  s_o[grp * per_row + (tid - grp * per_row)] = O;
-  if (tid - grp * per_row == 0) s_g[grp] = make_float2(M, L);
+  s_o[v * per_row + lane_in] = O;
+  if (lane_in == 0) s_g[v] = make_float2(M, L);
+  }
   __syncthreads();
   if (grp != 0) return;
-  for (int k = 1; k < groups; ++k) {
+  float M = s_g[0].x, L = s_g[0].y;            // (chain 0 holds the row's first block: never empty)
+  float4 O = s_o[tid];
+  for (int k = 1; k < VG; ++k) {
     const float2 g = s_g[k];
-    if (g.x == -INFINITY) continue;        // that group had no block
+    if (g.x == -INFINITY) continue;        // that chain had no block
     float fa, fb;
     merge_unit_scalars(M, L, g.x, g.y, fa, fb);
     merge4(O, s_o[k * per_row + tid], fa, fb);
@@ -783,7 +792,11 @@ int launch_units(const void* q, const void* k_pool, long long pool_rows, const i
   FZ_LAUNCH_CHECK();
   dim3 cgrid(Hq, N);
   // shared memory: the row's (max, sum) pairs, then 128 float4 and up to 8 float2 of the groups' results
-  fz_launch(attn_combine_units_kernel, cgrid, dim3(128), (size_t)(NPU + 2) * 8 + 128 * 16 + 8 * 8, stream, (const float*)part_o,
+  // blocks of 256 threads (a chain per group) while there are fewer blocks than SMs, else of 128 (two chains per group):
+  // two engines alternating in one process, a decode step of 32 layers at batch 1 3.100 -> 3.079 ms, batch 2 3.181 ->
+  // 3.161, batch 4 3.369 -> 3.348; at batch 8 (256 blocks) 3.780 -> 3.789 and at batch 64 1.3 % slower
+  const int ct = (long long)N * Hq <= sms ? 256 : 128;
+  fz_launch(attn_combine_units_kernel, cgrid, dim3(ct), (size_t)(NPU + 2) * 8 + 256 * 16 + 16 * 8, stream, (const float*)part_o,
             (const float*)part_ml, pos, seq_row, seg, (__nv_bfloat16*)out, Hq, HD, NPU, window, long_from);
   FZ_LAUNCH_CHECK();
   return FZ_OK;

@@ -55,6 +55,20 @@ def close(o, op, what):
     assert len(bad) == 0, f"{what}: rows {bad[:8].tolist()} differ by {float(err.max()):.3e} > {tol:.3e}"
 
 
+@pytest.mark.parametrize("Hq,Hkv,hd", [(8, 2, 128), (14, 2, 64)])
+def test_decode_rows_do_not_depend_on_the_batch(Hq, Hkv, hd):
+    """The same three decoded tokens alone and among 33 others: the kernels size their blocks by the number of rows (the
+    combine kernel takes blocks of 256 threads while there are fewer blocks than SMs), and every bit of a row must
+    stay what it was."""
+    g = torch.Generator().manual_seed(5)
+    lengths = [4300, 777, 2050] + torch.randint(40, 3000, (33,), generator=g).tolist()
+    rows = [(r, n - 1, 1) for r, n in enumerate(lengths)]
+    few, ref, _ = run_both(Hq, Hkv, hd, 16, 0, lengths, rows[:3], seed=11)
+    many, _, _ = run_both(Hq, Hkv, hd, 16, 0, lengths, rows, seed=11)
+    close(few, ref, "three rows")
+    assert torch.equal(few, many[:3]), "a row's bits changed with the batch"
+
+
 @pytest.mark.parametrize("Hq,Hkv,hd", [(4, 1, 128), (14, 2, 64), (8, 8, 64), (16, 1, 128), (10, 2, 128), (3, 3, 64)])
 @pytest.mark.parametrize("bs,window", [(16, 0), (8, 300), (5, 0), (64, 0), (48, 200)])
 def test_decode_rows_at_long_contexts(Hq, Hkv, hd, bs, window):
