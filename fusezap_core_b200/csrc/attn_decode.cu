@@ -671,46 +671,46 @@ attn_combine_units_kernel(const float* __restrict__ part_o, const float* __restr
     o.z = merge_unit_value(o.z, o2.z, fa, fb); o.w = merge_unit_value(o.w, o2.w, fa, fb);
   };
   for (int v = grp; v < VG; v += groups) {
-  float M = -INFINITY, L = 0.f;
-  float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int k = v; k < n_items; k += VG) {
-    float Mb, Lb;
-    float4 Ob;
-    if (k < n_small) {
-      const int b = (u0 >> 2) + k;
-      const int i0 = max(u0, 4 * b) - u0, i1 = min(u1, 4 * b + 3) - u0;       // the block's units, relative to u0
-      const float2 first = s_ml[i0];
-      Mb = first.x; Lb = fabsf(first.y);
-      if (first.y < 0.f || i1 == i0) {
-        Ob = *(const float4*)(po + (size_t)i0 * HD);
-      } else {                        // not merged by the unit kernel: the block's units one by one, loads first
-        float4 v[4];
+    float M = -INFINITY, L = 0.f;
+    float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k = v; k < n_items; k += VG) {
+      float Mb, Lb;
+      float4 Ob;
+      if (k < n_small) {
+        const int b = (u0 >> 2) + k;
+        const int i0 = max(u0, 4 * b) - u0, i1 = min(u1, 4 * b + 3) - u0;       // the block's units, relative to u0
+        const float2 first = s_ml[i0];
+        Mb = first.x; Lb = fabsf(first.y);
+        if (first.y < 0.f || i1 == i0) {
+          Ob = *(const float4*)(po + (size_t)i0 * HD);
+        } else {                        // not merged by the unit kernel: the block's units one by one, loads first
+          float4 v[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-          if (i0 + j <= i1) v[j] = *(const float4*)(po + (size_t)(i0 + j) * HD);
-        Ob = v[0];
+          for (int j = 0; j < 4; ++j)
+            if (i0 + j <= i1) v[j] = *(const float4*)(po + (size_t)(i0 + j) * HD);
+          Ob = v[0];
 #pragma unroll
-        for (int j = 1; j < 4; ++j) {
-          if (i0 + j <= i1) {
-            const float2 next = s_ml[i0 + j];
-            float fa, fb;
-            merge_unit_scalars(Mb, Lb, next.x, next.y, fa, fb);
-            merge4(Ob, v[j], fa, fb);
+          for (int j = 1; j < 4; ++j) {
+            if (i0 + j <= i1) {
+              const float2 next = s_ml[i0 + j];
+              float fa, fb;
+              merge_unit_scalars(Mb, Lb, next.x, next.y, fa, fb);
+              merge4(Ob, v[j], fa, fb);
+            }
           }
         }
+      } else {
+        const int i = big0 + (k - n_small) - u0;
+        const float2 v = s_ml[i];
+        Mb = v.x; Lb = v.y;
+        Ob = *(const float4*)(po + (size_t)i * HD);
       }
-    } else {
-      const int i = big0 + (k - n_small) - u0;
-      const float2 v = s_ml[i];
-      Mb = v.x; Lb = v.y;
-      Ob = *(const float4*)(po + (size_t)i * HD);
+      float fa, fb;
+      merge_unit_scalars(M, L, Mb, Lb, fa, fb);
+      merge4(O, Ob, fa, fb);
     }
-    float fa, fb;
-    merge_unit_scalars(M, L, Mb, Lb, fa, fb);
-    merge4(O, Ob, fa, fb);
-  }
-  s_o[v * per_row + lane_in] = O;
-  if (lane_in == 0) s_g[v] = make_float2(M, L);
+    s_o[v * per_row + lane_in] = O;
+    if (lane_in == 0) s_g[v] = make_float2(M, L);
   }
   __syncthreads();
   if (grp != 0) return;
@@ -791,7 +791,7 @@ int launch_units(const void* q, const void* k_pool, long long pool_rows, const i
             scale * 1.4426950408889634f, window, long_from, single, err);
   FZ_LAUNCH_CHECK();
   dim3 cgrid(Hq, N);
-  // shared memory: the row's (max, sum) pairs, then 128 float4 and up to 8 float2 of the groups' results
+  // shared memory: the row's (max, sum) pairs, then 256 float4 and up to 16 float2 of the chains' results
   // blocks of 256 threads (a chain per group) while there are fewer blocks than SMs, else of 128 (two chains per group):
   // two engines alternating in one process, a decode step of 32 layers at batch 1 3.100 -> 3.079 ms, batch 2 3.181 ->
   // 3.161, batch 4 3.369 -> 3.348; at batch 8 (256 blocks) 3.780 -> 3.789 and at batch 64 1.3 % slower
