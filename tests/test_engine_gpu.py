@@ -156,6 +156,9 @@ def test_the_serving_path_at_tensor_core_head_sizes(folders, name):
             def spy(portions, rows, decode_only, all_produce, kind="decode_steps", eng=eng, seen=seen, launch=launch):
                 out = launch(portions, rows, decode_only, all_produce, kind)
                 m = eng.runner.meta
+                # (the plan tells the decode attention kernel when every portion is a single token)
+                assert m.plan.single_tokens == all(len(p.tokens) == 1 for p in portions)
+                assert m.plan.single_tokens or not decode_only
                 if not decode_only:
                     sig = (m.n_rows, m.n_wanted, *eng.ops.step_signature(m))
                     seen.setdefault(sig, set()).add(tuple((sg.row0, sg.n, sg.pos0) for sg in m.segments))
